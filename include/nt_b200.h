@@ -1,0 +1,181 @@
+/*
+ * nt_b200.h -- C ABI of the B200 (sm_100a) op-kernel library behind nanotorch's `_C` module.
+ *
+ * Every entry point mirrors one function or method of the reference's native module
+ * (`PYBIND11_MODULE(_C, m)`, src/cpp/_C.cpp:12-24, typed in src/nanotorch/_C.pyi:1-136).  The
+ * reference passes `TensorView` (storage + shape + strides + offset, strides in elements, 0 and
+ * negative allowed; src/cpp/tensor_view.cuh:10-15) and returns a fresh `Storage`; this ABI passes
+ * `const nt_view*` and returns `nt_storage*` through an out-parameter with an `int` status.
+ *
+ * Conventions
+ *   - return value: NT_OK or an nt_status error class; the message is in nt_last_error()
+ *     (thread-local).  The classes map one-to-one to the Python exception the reference raises:
+ *     NT_ERR_RUNTIME -> RuntimeError (std::runtime_error, CUDA failures),
+ *     NT_ERR_INVALID -> ValueError   (std::invalid_argument),
+ *     NT_ERR_TYPE    -> TypeError    (py::type_error).
+ *   - compute entry points accept CUDA storages only.  There is no CPU compute path in this
+ *     library: a CPU storage handed to an op is NT_ERR_RUNTIME ("requires Cuda").  CPU storages
+ *     exist as host staging buffers (construction, tolist/item, H2D/D2H).
+ *   - all work is enqueued on one non-blocking stream owned by the library; calls return without
+ *     synchronising unless stated; the sync entry point below waits for it.
+ *   - storages are reference counted; every `nt_storage**` result carries one reference owned by
+ *     the caller (release with nt_storage_release).
+ *   - nothing here names a torch type.
+ */
+#ifndef NT_B200_H
+#define NT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NT_MAX_DIMS 8 /* src/cpp/tensor_view.cuh:8 */
+
+/* src/cpp/dtype.h:21 -- enum order is the promotion order. */
+typedef enum { NT_BOOL = 0, NT_INT32 = 1, NT_INT64 = 2, NT_FLOAT32 = 3, NT_FLOAT64 = 4 } nt_dtype;
+/* src/cpp/allocator.h:10 */
+typedef enum { NT_CPU = 0, NT_CUDA = 1 } nt_device;
+
+typedef enum {
+  NT_OK = 0,
+  NT_ERR_RUNTIME = 1, /* RuntimeError */
+  NT_ERR_INVALID = 2, /* ValueError   */
+  NT_ERR_TYPE = 3     /* TypeError    */
+} nt_status;
+
+/* Opaque, reference-counted flat typed buffer (src/cpp/storage.h:34-66). */
+typedef struct nt_storage nt_storage;
+
+/* Strided view (src/cpp/tensor_view.cuh:10-21). */
+typedef struct {
+  nt_storage *storage;
+  int32_t ndim; /* 0..NT_MAX_DIMS */
+  int64_t shape[NT_MAX_DIMS];
+  int64_t strides[NT_MAX_DIMS]; /* in elements */
+  int64_t offset;               /* in elements */
+} nt_view;
+
+/* Scalar argument of pow/full (src/cpp/storage.h:68-101): the Python bool/int/float variant. */
+typedef struct {
+  int32_t kind; /* 0 = bool, 1 = int64, 2 = double */
+  int64_t i;
+  double d;
+} nt_scalar;
+
+/* ------------------------------------------------------------------ errors, device, stream */
+const char *nt_last_error(void);
+int nt_is_cuda_available(void);       /* src/cpp/cuda.h:20-24 */
+int nt_cuda_sync(void);               /* src/cpp/cuda.h:26 (cudaDeviceSynchronize there; the library stream here) */
+int nt_set_device(int ordinal);       /* no counterpart: the reference never calls cudaSetDevice */
+int nt_device_count(int *out);
+void *nt_stream(void);                /* the cudaStream_t every kernel is launched on */
+int nt_launch_count(uint64_t *out);   /* kernels launched by this library since load (bench evidence) */
+int nt_allocator_stats(uint64_t *bytes_reserved, uint64_t *bytes_in_use, uint64_t *n_cuda_malloc);
+int nt_allocator_trim(void);          /* return cached blocks to the driver */
+
+/* ------------------------------------------------------------------ storage (src/cpp/storage.cpp:4-70) */
+int nt_storage_allocate(int64_t n, int dtype, int device, nt_storage **out); /* Storage::allocate */
+int nt_storage_retain(nt_storage *s);
+int nt_storage_release(nt_storage *s);
+int64_t nt_storage_size(const nt_storage *s);
+int64_t nt_storage_itemsize(const nt_storage *s);
+int nt_storage_dtype(const nt_storage *s);
+int nt_storage_device(const nt_storage *s);
+uint64_t nt_storage_version(const nt_storage *s);
+void *nt_storage_data(nt_storage *s);                 /* host or device pointer */
+int nt_storage_clone(const nt_storage *s, nt_storage **out);            /* Storage::clone */
+int nt_storage_to(nt_storage *s, int device, nt_storage **out);         /* Storage::to; same device -> same storage, retained */
+int nt_storage_cast(nt_storage *s, int dtype, nt_storage **out);        /* Storage::cast; on device, no host round trip */
+int nt_storage_upload(nt_storage *dst, const void *host_src, int64_t nbytes);   /* H2D (or memcpy for CPU storages) */
+int nt_storage_download(const nt_storage *src, void *host_dst, int64_t nbytes); /* D2H, synchronises */
+
+/* ------------------------------------------------------------------ factories (src/cpp/factory.cu:35-83) */
+int nt_zeros(int64_t n, int dtype, int device, nt_storage **out);
+int nt_ones(int64_t n, int dtype, int device, nt_storage **out);
+int nt_full(int64_t n, const nt_scalar *value, int dtype, int device, nt_storage **out);
+int nt_eye(int64_t n, int dtype, int device, nt_storage **out);
+int nt_arange(int64_t n, int64_t start, int64_t step, int dtype, int device, nt_storage **out);
+int nt_manual_seed(uint64_t seed);                                       /* src/cpp/random.h:12 */
+int nt_uniform(int64_t n, int dtype, int device, nt_storage **out);      /* host mt19937_64 stream, then H2D */
+
+/* ------------------------------------------------------------------ pointwise binary (src/cpp/ops/binary_ops.cu:97-113) */
+int nt_add(const nt_view *x1, const nt_view *x2, nt_storage **out);
+int nt_subtract(const nt_view *x1, const nt_view *x2, nt_storage **out);
+int nt_multiply(const nt_view *x1, const nt_view *x2, nt_storage **out);
+int nt_divide(const nt_view *x1, const nt_view *x2, nt_storage **out);
+int nt_pw_equal(const nt_view *x1, const nt_view *x2, nt_storage **out);      /* Bool output */
+int nt_pw_greater(const nt_view *x1, const nt_view *x2, nt_storage **out);    /* Bool output */
+int nt_pw_greater_eq(const nt_view *x1, const nt_view *x2, nt_storage **out); /* Bool output */
+int nt_equals(const nt_view *x1, const nt_view *x2, int *out);                /* src/cpp/ops/binary_ops.cu:160-176; synchronises */
+
+/* ------------------------------------------------------------------ pointwise unary (src/cpp/ops/unary_ops.cu:58-107) */
+int nt_exp(const nt_view *x, nt_storage **out);
+int nt_log(const nt_view *x, nt_storage **out);
+int nt_sqrt(const nt_view *x, nt_storage **out);
+int nt_tanh(const nt_view *x, nt_storage **out);
+int nt_sigmoid(const nt_view *x, nt_storage **out);
+int nt_neg(const nt_view *x, nt_storage **out);
+int nt_relu(const nt_view *x, nt_storage **out);
+int nt_pow(const nt_view *x, const nt_scalar *exponent, nt_storage **out);
+
+/* ------------------------------------------------------------------ reductions (src/cpp/ops/reduction_ops.cu:225-259) */
+int nt_sum(const nt_view *x, const int64_t *axes, int32_t n_axes, int dtype, nt_storage **out);
+int nt_max(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out);
+int nt_min(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out);
+int nt_argmax(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out); /* Int64 output */
+int nt_argmin(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out); /* Int64 output */
+
+/* ------------------------------------------------------------------ matmul (src/cpp/ops/matmul.cu:236-273) */
+int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out);
+/* fp32 product mode.  0 = exact FP32 SIMT (FMA, sequential in k: the rounding of the reference's
+ * CUDA kernels); 1 = 3xTF32 on tcgen05 tensor cores (default); 2 = FP32 SIMT with separate
+ * multiply and add, sequential in k (bit-for-bit the reference's CPU loop, src/cpp/ops/matmul.cu:31-45). */
+int nt_set_matmul_mode(int mode);
+int nt_get_matmul_mode(void);
+
+/* ------------------------------------------------------------------ in-place (src/cpp/ops/inplace_ops.cu:75-79); bump the version */
+int nt_add_inplace(const nt_view *out, const nt_view *other);
+int nt_sub_inplace(const nt_view *out, const nt_view *other);
+int nt_mul_inplace(const nt_view *out, const nt_view *other);
+int nt_div_inplace(const nt_view *out, const nt_view *other);
+int nt_copy_inplace(const nt_view *out, const nt_view *other);
+
+/* ------------------------------------------------------------------ copies (src/cpp/ops/copy_ops.cu:172-217) */
+int nt_copy_view(const nt_view *src, const nt_view *out);                    /* copy_view: strided -> strided; bumps version */
+int nt_clone_contiguous_view_from(const nt_view *src, nt_storage **out);     /* also the materialising broadcast */
+
+/* ------------------------------------------------------------------ fused backward kernels
+ * No single counterpart in the reference: each replaces the chain of primitive kernels that the
+ * reference's Python `backward` composes, and reproduces that chain's per-step fp32 rounding.
+ * `g` is the upstream gradient view; results are fresh contiguous fp32 storages. */
+int nt_relu_backward(const nt_view *g, const nt_view *y, nt_storage **out);    /* g * float(y > 0)             autograd/ops_unary.py:287-289 */
+int nt_tanh_backward(const nt_view *g, const nt_view *t, nt_storage **out);    /* g * (1 - powf(t,2))          autograd/ops_unary.py:180-182 */
+int nt_sigmoid_backward(const nt_view *g, const nt_view *s, nt_storage **out); /* (g*s) * (1 - s)              autograd/ops_unary.py:218-220 */
+int nt_exp_backward(const nt_view *g, const nt_view *e, nt_storage **out);     /* g * e                        autograd/ops_unary.py:69-70   */
+int nt_log_backward(const nt_view *g, const nt_view *x, nt_storage **out);     /* g * powf(x,-1)               autograd/ops_unary.py:105-106 */
+int nt_sqrt_backward(const nt_view *g, const nt_view *r, nt_storage **out);    /* (g*0.5) * powf(r,-1)         autograd/ops_unary.py:142-144 */
+int nt_pow_backward(const nt_view *g, const nt_view *x, float exponent, nt_storage **out); /* (g*e) * powf(x,e-1)  autograd/ops_unary.py:264-266 */
+int nt_div_backward_x2(const nt_view *g, const nt_view *x1, const nt_view *x2, nt_storage **out); /* ((-x1)/powf(x2,2))*g  autograd/ops_binary.py:197-202 */
+/* Max/Min backward: g_expanded * mask where mask = (x == m_expanded) and zero on every tied slice
+ * (integer-division quirk of the reference, autograd/ops_reduction.py:201-212, 275-286). */
+int nt_extremum_backward(const nt_view *g_expanded, const nt_view *x, const nt_view *m_expanded,
+                         const int64_t *axes, int32_t n_axes, nt_storage **out);
+/* SGD update p <- p - (g*lr), the two rounded steps of `p -= p.grad * lr` (nn/optimizers.py:45-51); bumps the version.
+ * `grad_scale` multiplies g first when != 1 (data-parallel mean over ranks). */
+int nt_sgd_update(const nt_view *param, const nt_view *grad, float lr, float grad_scale);
+
+/* ------------------------------------------------------------------ data-parallel exchange (NCCL; no counterpart in the reference) */
+#define NT_COMM_ID_BYTES 128
+int nt_comm_unique_id(uint8_t id[NT_COMM_ID_BYTES]);
+int nt_comm_init(int rank, int world, const uint8_t id[NT_COMM_ID_BYTES]);
+int nt_comm_allreduce_sum(nt_storage *s);       /* in place, fp32, on the communication stream; ordered after prior work */
+int nt_comm_wait(void);                         /* make the compute stream wait for outstanding collectives */
+int nt_comm_destroy(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NT_B200_H */

@@ -1,0 +1,420 @@
+// Elementwise kernel framework for sm_100a: one functor, three kernels.
+//
+//   ew_contig   every operand is one contiguous run: 128-bit loads/stores, four vectors in flight
+//               per operand per thread, streaming cache hints.  HBM-bound: (NIN+1)*4 bytes/element.
+//   ew_strided  any strides (0 = broadcast, negative, transposed) over up to 8 collapsed dims;
+//               a thread owns 4 consecutive elements of the innermost dim when that dim allows
+//               it, so unit-stride operands still move as 128-bit vectors and stride-0 operands
+//               as one load.
+//   ew_tile2d   fp32, the last two collapsed dims: operands whose unit stride is on the *outer*
+//               of the two (transposed views) are staged through a 64x64 shared-memory tile so
+//               that both global sides stay coalesced.
+//
+// Operand 0 is always the output (fresh contiguous storage, or the `out` view of an in-place op).
+// Replaces _binary_kernel/_binary_kernel_contig_f4 (src/cpp/ops/binary_ops.cu:22-41),
+// _unary_kernel (src/cpp/ops/unary_ops.cu:19-26) and _inplace_apply_kernel
+// (src/cpp/ops/inplace_ops.cu:18-27) of the reference, whose strided path does a chain of int64
+// divisions per element per operand (src/cpp/tensor_view.cuh:43-52) with 4-byte accesses.
+#pragma once
+
+#include "nt_core.cuh"
+
+namespace ntb {
+
+constexpr int EW_MAX_IN = 3;
+
+struct EwParams {
+  int ndim;                               // collapsed dims, 0..8 (0 => single element)
+  int64_t numel;
+  int64_t shape[NT_MAX_DIMS];
+  int64_t strides[EW_MAX_IN + 1][NT_MAX_DIMS]; // [0] = output
+  void *out;                              // already advanced by the view offset
+  const void *in[EW_MAX_IN];              // already advanced by the view offsets
+  // per operand: 0 = four scalar accesses, 1 = one 128-bit access, 2 = one scalar access (stride 0)
+  int vec_mode[EW_MAX_IN + 1];
+  // tile2d only: non-zero => the operand is unit-stride along dim ndim-2 and is staged through
+  // shared-memory slot (value - 1)
+  int col_major[EW_MAX_IN + 1];
+};
+
+__device__ __forceinline__ float4 ld_stream(const float4 *p) { return __ldcs(p); }
+__device__ __forceinline__ void st_stream(float4 *p, float4 v) { __stcs(p, v); }
+
+// ---------------------------------------------------------------------------------------------
+// Contiguous fp32-sized kernel.  TI/TO are 4-byte types.
+template <class F, int NIN>
+__global__ void __launch_bounds__(256) ew_contig(F f, typename F::out_t *out, const typename F::in_t *a,
+                                                 const typename F::in_t *b, const typename F::in_t *c, int64_t n) {
+  // no __restrict__: in-place ops pass the same pointer as `out` and `a`
+  using TI = typename F::in_t;
+  using TO = typename F::out_t;
+  static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "vector path is for 4-byte types");
+  constexpr int UNROLL = 4;
+  const int64_t nvec = n >> 2;
+  const int64_t base = (int64_t(blockIdx.x) * UNROLL) * blockDim.x + threadIdx.x;
+  float4 va[UNROLL], vb[UNROLL], vc[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    int64_t i = base + int64_t(u) * blockDim.x;
+    if (i < nvec) {
+      va[u] = ld_stream(reinterpret_cast<const float4 *>(a) + i);
+      if constexpr (NIN >= 2) vb[u] = ld_stream(reinterpret_cast<const float4 *>(b) + i);
+      if constexpr (NIN >= 3) vc[u] = ld_stream(reinterpret_cast<const float4 *>(c) + i);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    int64_t i = base + int64_t(u) * blockDim.x;
+    if (i < nvec) {
+      const TI *pa = reinterpret_cast<const TI *>(&va[u]);
+      const TI *pb = reinterpret_cast<const TI *>(&vb[u]);
+      const TI *pc = reinterpret_cast<const TI *>(&vc[u]);
+      float4 r;
+      TO *pr = reinterpret_cast<TO *>(&r);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if constexpr (NIN == 1) pr[e] = f(pa[e]);
+        if constexpr (NIN == 2) pr[e] = f(pa[e], pb[e]);
+        if constexpr (NIN == 3) pr[e] = f(pa[e], pb[e], pc[e]);
+      }
+      st_stream(reinterpret_cast<float4 *>(out) + i, r);
+    }
+  }
+  // ragged tail (n % 4 elements) by the first threads of block 0
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    int64_t i = (nvec << 2) + threadIdx.x;
+    if constexpr (NIN == 1) out[i] = f(a[i]);
+    if constexpr (NIN == 2) out[i] = f(a[i], b[i]);
+    if constexpr (NIN == 3) out[i] = f(a[i], b[i], c[i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Strided kernel.  IDX is uint32_t when every extent and offset fits, else int64_t/uint64_t.
+template <class F, int NIN, int VEC, class IDX>
+__global__ void __launch_bounds__(256) ew_strided(F f, EwParams p) {
+  using TI = typename F::in_t;
+  using TO = typename F::out_t;
+  const int64_t nthreads_needed = p.numel / VEC;
+  int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (t >= nthreads_needed) return;
+  IDX lin = IDX(t) * VEC;
+  int64_t off[NIN + 1];
+#pragma unroll
+  for (int o = 0; o <= NIN; ++o) off[o] = 0;
+  for (int d = p.ndim - 1; d >= 0; --d) {
+    IDX ext = IDX(p.shape[d]);
+    IDX q = lin / ext;
+    IDX r = lin - q * ext;
+    lin = q;
+#pragma unroll
+    for (int o = 0; o <= NIN; ++o) off[o] += int64_t(r) * p.strides[o][d];
+  }
+  const TI *in[NIN];
+#pragma unroll
+  for (int o = 0; o < NIN; ++o) in[o] = static_cast<const TI *>(p.in[o]) + off[o + 1];
+  TO *out = static_cast<TO *>(p.out) + off[0];
+
+  if constexpr (VEC == 1) {
+    if constexpr (NIN == 1) *out = f(*in[0]);
+    if constexpr (NIN == 2) *out = f(*in[0], *in[1]);
+    if constexpr (NIN == 3) *out = f(*in[0], *in[1], *in[2]);
+  } else {
+    static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "vector path is for 4-byte types");
+    const int last = p.ndim - 1;
+    TI v[NIN][4];
+#pragma unroll
+    for (int o = 0; o < NIN; ++o) {
+      const int mode = p.vec_mode[o + 1];
+      if (mode == 1) {
+        float4 x = *reinterpret_cast<const float4 *>(in[o]);
+        const TI *px = reinterpret_cast<const TI *>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[o][e] = px[e];
+      } else if (mode == 2) {
+        TI x = *in[o];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[o][e] = x;
+      } else {
+        const int64_t s = p.strides[o + 1][last];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[o][e] = in[o][e * s];
+      }
+    }
+    TO r[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if constexpr (NIN == 1) r[e] = f(v[0][e]);
+      if constexpr (NIN == 2) r[e] = f(v[0][e], v[1][e]);
+      if constexpr (NIN == 3) r[e] = f(v[0][e], v[1][e], v[2][e]);
+    }
+    if (p.vec_mode[0] == 1) {
+      *reinterpret_cast<float4 *>(out) = *reinterpret_cast<const float4 *>(r);
+    } else {
+      const int64_t s = p.strides[0][last];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) out[e * s] = r[e];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 2-D tile kernel (fp32-sized types).  Grid: x = tiles along the last dim (J), y = tiles along the
+// second-to-last (I), z = product of the leading dims.  256 threads own a 64x64 tile; in output
+// order a thread holds rows ty+16r (r=0..3), columns 4*tx..4*tx+3.
+constexpr int TILE = 64;
+template <class F, int NIN>
+__global__ void __launch_bounds__(256) ew_tile2d(F f, EwParams p) {
+  using TI = typename F::in_t;
+  using TO = typename F::out_t;
+  static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "tile path is for 4-byte types");
+  constexpr int NSLOT = (NIN < 2) ? NIN : 2; // at most two staged operands (48 KB static limit)
+  __shared__ TI tile[NSLOT][TILE][TILE + 1];
+
+  const int dI = p.ndim - 2, dJ = p.ndim - 1;
+  const int64_t nI = p.shape[dI], nJ = p.shape[dJ];
+  const int64_t i0 = int64_t(blockIdx.y) * TILE, j0 = int64_t(blockIdx.x) * TILE;
+
+  // leading dims -> per-operand base offsets
+  int64_t base[NIN + 1];
+#pragma unroll
+  for (int o = 0; o <= NIN; ++o) base[o] = 0;
+  {
+    int64_t lin = blockIdx.z;
+    for (int d = p.ndim - 3; d >= 0; --d) {
+      int64_t q = lin / p.shape[d];
+      int64_t r = lin - q * p.shape[d];
+      lin = q;
+#pragma unroll
+      for (int o = 0; o <= NIN; ++o) base[o] += r * p.strides[o][d];
+    }
+  }
+
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+
+  // stage the column-major operands: read along I (their unit-stride dim), 4 elements per thread
+#pragma unroll
+  for (int o = 0; o < NIN; ++o) {
+    if (p.col_major[o + 1]) {
+      const int slot = p.col_major[o + 1] - 1;
+      const TI *src = static_cast<const TI *>(p.in[o]) + base[o + 1];
+      const int64_t sJ = p.strides[o + 1][dJ]; // stride along J; stride along I is 1
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int64_t j = j0 + ty + 16 * r;
+        const int64_t i = i0 + 4 * tx;
+        if (j < nJ) {
+          const TI *q = src + j * sJ + i;
+          if (p.vec_mode[o + 1] == 1 && i + 3 < nI) {
+            float4 x = *reinterpret_cast<const float4 *>(q);
+            const TI *px = reinterpret_cast<const TI *>(&x);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) tile[slot][ty + 16 * r][4 * tx + e] = px[e];
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (i + e < nI) tile[slot][ty + 16 * r][4 * tx + e] = q[e];
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  TO *dst = static_cast<TO *>(p.out) + base[0];
+  const int64_t oI = p.strides[0][dI], oJ = p.strides[0][dJ];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int64_t i = i0 + ty + 16 * r;
+    const int64_t j = j0 + 4 * tx;
+    if (i >= nI || j >= nJ) continue;
+    const bool full = (j + 3 < nJ);
+    TI v[NIN][4];
+#pragma unroll
+    for (int o = 0; o < NIN; ++o) {
+      if (p.col_major[o + 1]) {
+        const int slot = p.col_major[o + 1] - 1;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[o][e] = tile[slot][4 * tx + e][ty + 16 * r];
+      } else {
+        const TI *src = static_cast<const TI *>(p.in[o]) + base[o + 1] + i * p.strides[o + 1][dI];
+        const int64_t sJ = p.strides[o + 1][dJ];
+        if (sJ == 0) {
+          TI x = *src;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[o][e] = x;
+        } else if (p.vec_mode[o + 1] == 1 && full) {
+          float4 x = *reinterpret_cast<const float4 *>(src + j);
+          const TI *px = reinterpret_cast<const TI *>(&x);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[o][e] = px[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[o][e] = (j + e < nJ) ? src[(j + e) * sJ] : TI(0);
+        }
+      }
+    }
+    TO res[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      if constexpr (NIN == 1) res[e] = f(v[0][e]);
+      if constexpr (NIN == 2) res[e] = f(v[0][e], v[1][e]);
+      if constexpr (NIN == 3) res[e] = f(v[0][e], v[1][e], v[2][e]);
+    }
+    TO *q = dst + i * oI + j * oJ;
+    if (p.vec_mode[0] == 1 && full) {
+      *reinterpret_cast<float4 *>(q) = *reinterpret_cast<const float4 *>(res);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (j + e < nJ) q[e * oJ] = res[e];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host-side planner + launcher.
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+// views[0] is the output view (for fresh outputs: contiguous, offset 0).
+template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NIN + 1]) {
+  using TI = typename F::in_t;
+  using TO = typename F::out_t;
+  IterSpace<NIN + 1> it = collapse<NIN + 1>(views);
+  if (it.numel == 0) return;
+  cudaStream_t st = stream();
+
+  TO *out = static_cast<TO *>(views[0]->storage->data) + it.offset[0];
+  const TI *in[EW_MAX_IN] = {nullptr, nullptr, nullptr};
+  for (int o = 0; o < NIN; ++o) in[o] = static_cast<const TI *>(views[o + 1]->storage->data) + it.offset[o + 1];
+
+  constexpr bool VECTOR_TYPES = (sizeof(TI) == 4 && sizeof(TO) == 4);
+
+  // (1) every operand one contiguous run
+  bool all_contig = it.ndim <= 1;
+  if (all_contig && it.ndim == 1)
+    for (int o = 0; o <= NIN; ++o) all_contig = all_contig && it.strides[o][0] == 1;
+  if constexpr (VECTOR_TYPES) {
+    bool al = aligned16(out);
+    for (int o = 0; o < NIN; ++o) al = al && aligned16(in[o]);
+    if (all_contig && al && it.numel >= 4) {
+      int64_t nvec = it.numel >> 2;
+      int64_t blocks = ceil_div(nvec, 256 * 4);
+      ew_contig<F, NIN><<<unsigned(blocks), 256, 0, st>>>(f, out, in[0], in[1], in[2], it.numel);
+      check_launch("ew_contig");
+      return;
+    }
+  }
+
+  EwParams p{};
+  p.ndim = it.ndim;
+  p.numel = it.numel;
+  for (int d = 0; d < it.ndim; ++d) {
+    p.shape[d] = it.shape[d];
+    for (int o = 0; o <= NIN; ++o) p.strides[o][d] = it.strides[o][d];
+  }
+  p.out = out;
+  for (int o = 0; o < NIN; ++o) p.in[o] = in[o];
+
+  // 128-bit access along the last dim is legal for an operand when that dim has unit stride, the
+  // base is 16-byte aligned and every other stride keeps rows 16-byte aligned.
+  auto vec_ok = [&](int o, int unit_dim) {
+    const void *base = (o == 0) ? static_cast<const void *>(out) : static_cast<const void *>(in[o - 1]);
+    if (!aligned16(base)) return false;
+    if (it.strides[o][unit_dim] != 1) return false;
+    for (int d = 0; d < it.ndim; ++d)
+      if (d != unit_dim && (it.strides[o][d] & 3) != 0) return false;
+    return true;
+  };
+
+  if constexpr (VECTOR_TYPES) {
+    // (2) a transposed operand: unit stride on the second-to-last dim, not on the last
+    if (it.ndim >= 2) {
+      const int dI = it.ndim - 2, dJ = it.ndim - 1;
+      bool any_col = false, ok = true;
+      int n_col = 0;
+      for (int o = 1; o <= NIN; ++o) {
+        bool col = it.strides[o][dI] == 1 && it.strides[o][dJ] != 1 && it.strides[o][dJ] != 0;
+        p.col_major[o] = col ? ++n_col : 0; // 1-based shared-memory slot
+        any_col = any_col || col;
+      }
+      if (n_col > 2) ok = false;
+      // the output must be written along J for the tile mapping to pay off
+      if (it.strides[0][dJ] != 1) ok = false;
+      int64_t lead = 1;
+      for (int d = 0; d < it.ndim - 2; ++d) lead *= it.shape[d];
+      if (lead > 65535 || ceil_div(it.shape[dI], TILE) > 65535) ok = false;
+      if (any_col && ok && it.shape[dI] >= 16 && it.shape[dJ] >= 16) {
+        for (int o = 0; o <= NIN; ++o) {
+          if (o > 0 && p.col_major[o])
+            p.vec_mode[o] = vec_ok(o, dI) ? 1 : 0;
+          else
+            p.vec_mode[o] = vec_ok(o, dJ) ? 1 : 0;
+        }
+        dim3 grid(unsigned(ceil_div(it.shape[dJ], TILE)), unsigned(ceil_div(it.shape[dI], TILE)), unsigned(lead));
+        ew_tile2d<F, NIN><<<grid, 256, 0, st>>>(f, p);
+        check_launch("ew_tile2d");
+        return;
+      }
+      for (int o = 0; o <= NIN; ++o) p.col_major[o] = 0;
+    }
+  }
+
+  // (3) general strided
+  bool idx32 = it.numel < (int64_t(1) << 31);
+  bool vec4 = false;
+  if constexpr (VECTOR_TYPES) {
+    if (it.ndim >= 1 && (it.shape[it.ndim - 1] & 3) == 0) {
+      vec4 = true;
+      const int last = it.ndim - 1;
+      for (int o = 0; o <= NIN; ++o) {
+        if (o > 0 && it.strides[o][last] == 0)
+          p.vec_mode[o] = 2;
+        else
+          p.vec_mode[o] = vec_ok(o, last) ? 1 : 0;
+      }
+      // an output that aliases itself along the vector (stride 0) cannot be written 4-wide
+      if (it.strides[0][last] == 0) vec4 = false;
+    }
+  }
+  if (it.ndim == 0) { // single element
+    p.ndim = 1;
+    p.shape[0] = 1;
+    for (int o = 0; o <= NIN; ++o) p.strides[o][0] = 1;
+  }
+  if constexpr (VECTOR_TYPES) {
+    if (vec4) {
+      int64_t blocks = ceil_div(it.numel / 4, 256);
+      if (idx32)
+        ew_strided<F, NIN, 4, uint32_t><<<unsigned(blocks), 256, 0, st>>>(f, p);
+      else
+        ew_strided<F, NIN, 4, uint64_t><<<unsigned(blocks), 256, 0, st>>>(f, p);
+      check_launch("ew_strided");
+      return;
+    }
+  }
+  int64_t blocks = ceil_div(it.numel, 256);
+  if (blocks > 0x7fffffffLL) fail_runtime("elementwise: tensor too large for one launch.");
+  if (idx32)
+    ew_strided<F, NIN, 1, uint32_t><<<unsigned(blocks), 256, 0, st>>>(f, p);
+  else
+    ew_strided<F, NIN, 1, uint64_t><<<unsigned(blocks), 256, 0, st>>>(f, p);
+  check_launch("ew_strided");
+}
+
+// Builds the contiguous view of a freshly allocated result with the shape of `like`.
+inline nt_view fresh_view(nt_storage *s, const nt_view &like) {
+  nt_view v{};
+  v.storage = s;
+  v.ndim = like.ndim;
+  int64_t st = 1;
+  for (int d = like.ndim - 1; d >= 0; --d) {
+    v.shape[d] = like.shape[d];
+    v.strides[d] = st;
+    st *= like.shape[d];
+  }
+  v.offset = 0;
+  return v;
+}
+
+} // namespace ntb

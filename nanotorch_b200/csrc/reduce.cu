@@ -1,0 +1,600 @@
+// Reductions of the C ABI: sum / max / min / argmax / argmin over any set of axes of a strided view.
+//
+// fp32 sum/max/min take one of two single-launch kernels, both HBM-bound at 4 bytes per input
+// element (the reference's accounting, autograd/ops_reduction.py:80-82):
+//   reduce_rows  the dropped dims collapse to one unit-stride run (last-dim and full reductions):
+//                128-bit loads, four accumulators per thread, warp shuffles, then shared memory
+//                across the CTA's warps.  Long rows are split over several CTAs; each writes one
+//                partial and the CTA that draws the last ticket folds the partials in index order
+//                and writes the result -- one launch, deterministic, no (index,value) payload.
+//   reduce_cols  the innermost kept dim has unit stride and one strided dim is dropped (dim-0
+//                reductions, bias gradients): lanes run along the kept columns so every row read
+//                is coalesced; row ranges are split over CTAs with the same ticket finish.
+// Everything else (other dtypes, argmax/argmin, exotic views) takes reduce_generic, a direct
+// restatement of the reference's combiner with its (index,value) items.
+//
+// Replaces _reduce_kernel/_extract_kernel and their multi-pass host loop
+// (src/cpp/ops/reduction_ops.cu:86-171), which re-launches over 16-byte partial items, reads one
+// element per thread for dim-1 and strides lanes by a whole row for dim-0.
+#include <cuda/std/limits>
+
+#include "elementwise.cuh"
+
+namespace ntb {
+
+// ---------------------------------------------------------------------------------------------
+// fp32 combiners.  Neutral elements are the reference's: 0, lowest() and max() -- not infinities
+// (src/cpp/ops/reduction_ops.cu:15-50), so max over an all -inf slice is -FLT_MAX there and here.
+struct RSum {
+  static __device__ __forceinline__ float neutral() { return 0.0f; }
+  static __device__ __forceinline__ float combine(float a, float b) { return a + b; }
+};
+struct RMax {
+  static __device__ __forceinline__ float neutral() { return -3.402823466e+38f; }
+  static __device__ __forceinline__ float combine(float a, float b) { return (a > b) ? a : b; }
+};
+struct RMin {
+  static __device__ __forceinline__ float neutral() { return 3.402823466e+38f; }
+  static __device__ __forceinline__ float combine(float a, float b) { return (a < b) ? a : b; }
+};
+
+template <class Op> __device__ __forceinline__ float warp_reduce(float v) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v = Op::combine(v, __shfl_xor_sync(0xffffffffu, v, s));
+  return v;
+}
+
+struct KeepIndex { // kept dims of the input view, outermost first
+  int ndim;
+  int64_t shape[NT_MAX_DIMS];
+  int64_t strides[NT_MAX_DIMS];
+};
+__device__ __forceinline__ int64_t keep_offset(const KeepIndex &k, int64_t lin) {
+  int64_t off = 0;
+  for (int d = k.ndim - 1; d >= 0; --d) {
+    int64_t q = lin / k.shape[d];
+    off += (lin - q * k.shape[d]) * k.strides[d];
+    lin = q;
+  }
+  return off;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Row reduction.  Block b handles split (b % S) of row (b / S); elements [lo, hi) of the row.
+template <class Op>
+__global__ void __launch_bounds__(256) reduce_rows(const float *__restrict__ in, float *__restrict__ out,
+                                                   float *__restrict__ partials, unsigned *__restrict__ tickets,
+                                                   KeepIndex keep, int64_t L, int S, int64_t chunk) {
+  __shared__ float warp_part[8];
+  __shared__ bool is_last;
+  const int64_t row = blockIdx.x / S;
+  const int split = int(blockIdx.x - row * S);
+  const float *p = in + keep_offset(keep, row);
+  const int64_t lo = int64_t(split) * chunk;
+  int64_t hi = lo + chunk;
+  if (hi > L) hi = L;
+
+  float a0 = Op::neutral(), a1 = Op::neutral(), a2 = Op::neutral(), a3 = Op::neutral();
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p) & 15) == 0); // lo is a multiple of 4
+  if (aligned) {
+    const int64_t nvec = (hi - lo) >> 2;
+    const float4 *pv = reinterpret_cast<const float4 *>(p + lo);
+    int64_t i = threadIdx.x;
+    // four vectors in flight per thread
+    for (; i + 3 * 256 < nvec; i += 4 * 256) {
+      float4 v0 = __ldcs(pv + i), v1 = __ldcs(pv + i + 256), v2 = __ldcs(pv + i + 512), v3 = __ldcs(pv + i + 768);
+      a0 = Op::combine(a0, Op::combine(Op::combine(v0.x, v0.y), Op::combine(v0.z, v0.w)));
+      a1 = Op::combine(a1, Op::combine(Op::combine(v1.x, v1.y), Op::combine(v1.z, v1.w)));
+      a2 = Op::combine(a2, Op::combine(Op::combine(v2.x, v2.y), Op::combine(v2.z, v2.w)));
+      a3 = Op::combine(a3, Op::combine(Op::combine(v3.x, v3.y), Op::combine(v3.z, v3.w)));
+    }
+    for (; i < nvec; i += 256) {
+      float4 v = __ldcs(pv + i);
+      a0 = Op::combine(a0, Op::combine(Op::combine(v.x, v.y), Op::combine(v.z, v.w)));
+    }
+    for (int64_t j = lo + (nvec << 2) + threadIdx.x; j < hi; j += 256) a1 = Op::combine(a1, p[j]);
+  } else {
+    int64_t j = lo + threadIdx.x;
+    for (; j + 3 * 256 < hi; j += 4 * 256) {
+      float v0 = p[j], v1 = p[j + 256], v2 = p[j + 512], v3 = p[j + 768];
+      a0 = Op::combine(a0, v0);
+      a1 = Op::combine(a1, v1);
+      a2 = Op::combine(a2, v2);
+      a3 = Op::combine(a3, v3);
+    }
+    for (; j < hi; j += 256) a0 = Op::combine(a0, p[j]);
+  }
+  float v = Op::combine(Op::combine(a0, a1), Op::combine(a2, a3));
+  v = warp_reduce<Op>(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) warp_part[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    v = (lane < 8) ? warp_part[lane] : Op::neutral();
+    v = warp_reduce<Op>(v);
+  }
+  if (S == 1) {
+    if (threadIdx.x == 0) out[row] = v;
+    return;
+  }
+  // single-pass grid finish
+  if (threadIdx.x == 0) {
+    partials[row * S + split] = v;
+    __threadfence();
+    unsigned t = atomicAdd(&tickets[row], 1u);
+    is_last = (t == unsigned(S - 1));
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // fold the S partials in index order: fixed thread->index map, fixed tree => deterministic
+  float acc = Op::neutral();
+  for (int i = threadIdx.x; i < S; i += 256) acc = Op::combine(acc, __ldcg(partials + row * S + i));
+  acc = warp_reduce<Op>(acc);
+  if (lane == 0) warp_part[warp] = acc;
+  __syncthreads();
+  if (warp == 0) {
+    acc = (lane < 8) ? warp_part[lane] : Op::neutral();
+    acc = warp_reduce<Op>(acc);
+    if (lane == 0) {
+      out[row] = acc;
+      tickets[row] = 0; // leave the counter ready for the next launch
+    }
+  }
+}
+
+// Short rows: one warp per row, eight rows per CTA.
+template <class Op>
+__global__ void __launch_bounds__(256) reduce_rows_warp(const float *__restrict__ in, float *__restrict__ out,
+                                                        KeepIndex keep, int64_t n_rows, int64_t L) {
+  const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const float *p = in + keep_offset(keep, row);
+  float a = Op::neutral();
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    const int64_t nvec = L >> 2;
+    const float4 *pv = reinterpret_cast<const float4 *>(p);
+    for (int64_t i = lane; i < nvec; i += 32) {
+      float4 v = pv[i];
+      a = Op::combine(a, Op::combine(Op::combine(v.x, v.y), Op::combine(v.z, v.w)));
+    }
+    for (int64_t j = (nvec << 2) + lane; j < L; j += 32) a = Op::combine(a, p[j]);
+  } else {
+    for (int64_t j = lane; j < L; j += 32) a = Op::combine(a, p[j]);
+  }
+  a = warp_reduce<Op>(a);
+  if (lane == 0) out[row] = a;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Column reduction over a [Z][R][C] view with strides (keep-outer, sR, 1).
+// grid.x = column tile, grid.y = row split, grid.z = outer kept index.  VEC = 4: a warp spans 128
+// columns; VEC = 1: 32 columns.  The 8 warps of the CTA interleave over the rows of the split.
+template <class Op, int VEC>
+__global__ void __launch_bounds__(256) reduce_cols(const float *__restrict__ in, float *__restrict__ out,
+                                                   float *__restrict__ partials, unsigned *__restrict__ tickets,
+                                                   KeepIndex keep_outer, int64_t R, int64_t C, int64_t sR,
+                                                   int64_t rows_per_split) {
+  constexpr int TW = 32 * VEC; // tile width in columns
+  __shared__ float part[8][TW];
+  __shared__ bool is_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t c0 = int64_t(blockIdx.x) * TW + lane * VEC;
+  const int S = gridDim.y, split = blockIdx.y;
+  const int64_t z = blockIdx.z;
+  const float *base = in + keep_offset(keep_outer, z);
+  int64_t r_lo = int64_t(split) * rows_per_split, r_hi = r_lo + rows_per_split;
+  if (r_hi > R) r_hi = R;
+
+  float acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = Op::neutral();
+  if (c0 < C) {
+    if constexpr (VEC == 4) {
+      float4 b0, b1, b2, b3;
+      int64_t r = r_lo + warp;
+      for (; r + 24 < r_hi; r += 32) { // four rows in flight per thread
+        b0 = __ldcs(reinterpret_cast<const float4 *>(base + r * sR + c0));
+        b1 = __ldcs(reinterpret_cast<const float4 *>(base + (r + 8) * sR + c0));
+        b2 = __ldcs(reinterpret_cast<const float4 *>(base + (r + 16) * sR + c0));
+        b3 = __ldcs(reinterpret_cast<const float4 *>(base + (r + 24) * sR + c0));
+        acc[0] = Op::combine(acc[0], Op::combine(Op::combine(b0.x, b1.x), Op::combine(b2.x, b3.x)));
+        acc[1] = Op::combine(acc[1], Op::combine(Op::combine(b0.y, b1.y), Op::combine(b2.y, b3.y)));
+        acc[2] = Op::combine(acc[2], Op::combine(Op::combine(b0.z, b1.z), Op::combine(b2.z, b3.z)));
+        acc[3] = Op::combine(acc[3], Op::combine(Op::combine(b0.w, b1.w), Op::combine(b2.w, b3.w)));
+      }
+      for (; r < r_hi; r += 8) {
+        b0 = __ldcs(reinterpret_cast<const float4 *>(base + r * sR + c0));
+        acc[0] = Op::combine(acc[0], b0.x);
+        acc[1] = Op::combine(acc[1], b0.y);
+        acc[2] = Op::combine(acc[2], b0.z);
+        acc[3] = Op::combine(acc[3], b0.w);
+      }
+    } else {
+      int64_t r = r_lo + warp;
+      for (; r + 24 < r_hi; r += 32) {
+        float b0 = base[r * sR + c0], b1 = base[(r + 8) * sR + c0], b2 = base[(r + 16) * sR + c0],
+              b3 = base[(r + 24) * sR + c0];
+        acc[0] = Op::combine(acc[0], Op::combine(Op::combine(b0, b1), Op::combine(b2, b3)));
+      }
+      for (; r < r_hi; r += 8) acc[0] = Op::combine(acc[0], base[r * sR + c0]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) part[warp][lane * VEC + e] = acc[e];
+  __syncthreads();
+  // 8 warps -> 1, in warp order; thread t owns column t of the tile
+  float v = Op::neutral();
+  const int64_t c = int64_t(blockIdx.x) * TW + threadIdx.x;
+  const bool owner = (threadIdx.x < TW) && (c < C);
+  if (threadIdx.x < TW) {
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v = Op::combine(v, part[w][threadIdx.x]);
+  }
+  const int64_t out_base = z * C;
+  if (S == 1) {
+    if (owner) out[out_base + c] = v;
+    return;
+  }
+  if (owner) partials[(z * S + split) * C + c] = v;
+  __threadfence();
+  __syncthreads();
+  const int64_t tile_id = z * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 0) {
+    unsigned t = atomicAdd(&tickets[tile_id], 1u);
+    is_last = (t == unsigned(S - 1));
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (owner) {
+    float a = Op::neutral();
+    for (int s = 0; s < S; ++s) a = Op::combine(a, __ldcg(partials + (z * S + s) * C + c));
+    out[out_base + c] = a;
+  }
+  if (threadIdx.x == 0) tickets[tile_id] = 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Generic path: the reference's (index, value) combiner, any dtype pair.
+template <class O> struct Item {
+  int64_t idx;
+  O value;
+};
+struct GSum {
+  static constexpr bool returns_idx = false;
+  template <class O> static __device__ Item<O> neutral() { return Item<O>{-1, O(0)}; }
+  template <class O> static __device__ Item<O> combine(Item<O> a, Item<O> b) { return Item<O>{-1, O(a.value + b.value)}; }
+};
+struct GArgMin {
+  static constexpr bool returns_idx = true;
+  template <class O> static __device__ Item<O> neutral() {
+    return Item<O>{cuda::std::numeric_limits<int64_t>::max(), cuda::std::numeric_limits<O>::max()};
+  }
+  template <class O> static __device__ Item<O> combine(Item<O> a, Item<O> b) {
+    return (a.value < b.value || (a.value == b.value && a.idx < b.idx)) ? a : b;
+  }
+};
+struct GArgMax {
+  static constexpr bool returns_idx = true;
+  template <class O> static __device__ Item<O> neutral() {
+    return Item<O>{cuda::std::numeric_limits<int64_t>::max(), cuda::std::numeric_limits<O>::lowest()};
+  }
+  template <class O> static __device__ Item<O> combine(Item<O> a, Item<O> b) {
+    return (a.value > b.value || (a.value == b.value && a.idx < b.idx)) ? a : b;
+  }
+};
+struct GMin : GArgMin {
+  static constexpr bool returns_idx = false;
+};
+struct GMax : GArgMax {
+  static constexpr bool returns_idx = false;
+};
+
+// One CTA of 256 threads per kept element (GROUP = 256) or one warp (GROUP = 32).
+template <class T, class O, class Op, int GROUP>
+__global__ void __launch_bounds__(256) reduce_generic(const T *__restrict__ in, void *__restrict__ out_raw,
+                                                      KeepIndex keep, KeepIndex drop, int64_t n_keep,
+                                                      int64_t n_drop) {
+  constexpr int PER_CTA = 256 / GROUP;
+  __shared__ Item<O> buf[256];
+  const int sub = threadIdx.x / GROUP, t = threadIdx.x % GROUP;
+  const int64_t k = int64_t(blockIdx.x) * PER_CTA + sub;
+  Item<O> acc = Op::template neutral<O>();
+  if (k < n_keep) {
+    const T *p = in + keep_offset(keep, k);
+    for (int64_t j = t; j < n_drop; j += GROUP)
+      acc = Op::template combine<O>(acc, Item<O>{j, static_cast<O>(p[keep_offset(drop, j)])});
+  }
+  buf[threadIdx.x] = acc;
+  __syncthreads();
+  for (int s = GROUP / 2; s > 0; s >>= 1) {
+    if (t < s) buf[threadIdx.x] = Op::template combine<O>(buf[threadIdx.x], buf[threadIdx.x + s]);
+    __syncthreads();
+  }
+  if (t == 0 && k < n_keep) {
+    if constexpr (Op::returns_idx)
+      static_cast<int64_t *>(out_raw)[k] = buf[threadIdx.x].idx;
+    else
+      static_cast<O *>(out_raw)[k] = buf[threadIdx.x].value;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+struct Ticket {
+  unsigned *ptr = nullptr;
+  int64_t capacity = 0;
+};
+// Zero-initialised once; every kernel leaves the counters it used at zero.
+static unsigned *tickets(int64_t need) {
+  static Ticket t;
+  if (need > t.capacity) {
+    int64_t cap = need < 65536 ? 65536 : need;
+    size_t rounded;
+    void *p = device_alloc(size_t(cap) * sizeof(unsigned), &rounded);
+    NT_CUDA_CHECK(cudaMemsetAsync(p, 0, size_t(cap) * sizeof(unsigned), stream()));
+    // the previous block (if any) stays allocated: kernels in flight may still hold it
+    t.ptr = static_cast<unsigned *>(p);
+    t.capacity = cap;
+  }
+  return t.ptr;
+}
+
+struct Plan {
+  KeepIndex keep{}, drop{};
+  int64_t n_keep = 1, n_drop = 1;
+};
+
+static void collapse_group(KeepIndex &g) {
+  KeepIndex r{};
+  for (int d = 0; d < g.ndim; ++d) {
+    if (g.shape[d] == 1) continue;
+    if (r.ndim > 0 && r.strides[r.ndim - 1] == g.strides[d] * g.shape[d]) {
+      r.shape[r.ndim - 1] *= g.shape[d];
+      r.strides[r.ndim - 1] = g.strides[d];
+    } else {
+      r.shape[r.ndim] = g.shape[d];
+      r.strides[r.ndim] = g.strides[d];
+      ++r.ndim;
+    }
+  }
+  g = r;
+}
+
+static Plan make_plan(const nt_view *x, const int64_t *axes, int32_t n_axes) {
+  Plan pl;
+  bool dropped[NT_MAX_DIMS] = {};
+  for (int i = 0; i < n_axes; ++i) {
+    if (axes[i] < 0 || axes[i] >= x->ndim) fail_runtime("reduction: axis out of range.");
+    if (dropped[axes[i]]) fail_runtime("reduction: repeated axis.");
+    dropped[axes[i]] = true;
+  }
+  for (int d = 0; d < x->ndim; ++d) {
+    KeepIndex &g = dropped[d] ? pl.drop : pl.keep;
+    g.shape[g.ndim] = x->shape[d];
+    g.strides[g.ndim] = x->strides[d];
+    ++g.ndim;
+    (dropped[d] ? pl.n_drop : pl.n_keep) *= x->shape[d];
+  }
+  collapse_group(pl.keep);
+  collapse_group(pl.drop);
+  return pl;
+}
+
+template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, float *out) {
+  const float *in = static_cast<const float *>(x->storage->data) + x->offset;
+  cudaStream_t st = stream();
+  const int sms = sm_count();
+  const int64_t target_ctas = int64_t(sms) * 8;
+
+  // rows: dropped dims are one unit-stride run
+  if (pl.drop.ndim == 1 && pl.drop.strides[0] == 1) {
+    const int64_t L = pl.n_drop, n_rows = pl.n_keep;
+    if (L < 1024 && n_rows >= 64) {
+      int64_t blocks = ceil_div(n_rows, 8);
+      if (blocks > 0x7fffffffLL) return false;
+      reduce_rows_warp<Op><<<unsigned(blocks), 256, 0, st>>>(in, out, pl.keep, n_rows, L);
+      check_launch("reduce_rows_warp");
+      return true;
+    }
+    int64_t S = ceil_div(target_ctas, n_rows);
+    int64_t max_s = ceil_div(L, 8192);
+    if (S > max_s) S = max_s;
+    if (S > 1024) S = 1024;
+    if (S < 1) S = 1;
+    int64_t chunk = ceil_div(ceil_div(L, S), 1024) * 1024;
+    S = ceil_div(L, chunk);
+    if (n_rows * S > 0x7fffffffLL) return false;
+    float *partials = nullptr;
+    unsigned *tk = nullptr;
+    size_t rounded = 0;
+    if (S > 1) {
+      partials = static_cast<float *>(device_alloc(size_t(n_rows * S) * sizeof(float), &rounded));
+      tk = tickets(n_rows);
+    }
+    reduce_rows<Op><<<unsigned(n_rows * S), 256, 0, st>>>(in, out, partials, tk, pl.keep, L, int(S), chunk);
+    if (partials) device_free(partials, rounded); // stream-ordered reuse: later work queues behind this launch
+    check_launch("reduce_rows");
+    return true;
+  }
+
+  // columns: innermost kept dim has unit stride, exactly one strided dim is dropped
+  if (pl.drop.ndim == 1 && pl.keep.ndim >= 1 && pl.keep.strides[pl.keep.ndim - 1] == 1) {
+    const int64_t R = pl.n_drop, sR = pl.drop.strides[0];
+    const int64_t C = pl.keep.shape[pl.keep.ndim - 1];
+    KeepIndex outer = pl.keep;
+    outer.ndim -= 1;
+    int64_t Z = 1;
+    for (int d = 0; d < outer.ndim; ++d) Z *= outer.shape[d];
+    if (Z > 65535) return false;
+    bool vec = (C % 4 == 0) && (sR % 4 == 0) && aligned16(in);
+    for (int d = 0; d < outer.ndim; ++d) vec = vec && (outer.strides[d] % 4 == 0);
+    const int TW = vec ? 128 : 32;
+    const int64_t tiles = ceil_div(C, TW);
+    if (tiles > 0x7fffffffLL) return false;
+    int64_t S = ceil_div(target_ctas, tiles * Z);
+    int64_t max_s = ceil_div(R, 64);
+    if (S > max_s) S = max_s;
+    if (S > 65535) S = 65535;
+    if (S < 1) S = 1;
+    int64_t rows_per_split = ceil_div(R, S);
+    S = ceil_div(R, rows_per_split);
+    float *partials = nullptr;
+    unsigned *tk = nullptr;
+    size_t rounded = 0;
+    if (S > 1) {
+      partials = static_cast<float *>(device_alloc(size_t(Z * S * C) * sizeof(float), &rounded));
+      tk = tickets(Z * tiles);
+    }
+    dim3 grid{unsigned(tiles), unsigned(S), unsigned(Z)};
+    if (vec)
+      reduce_cols<Op, 4><<<grid, 256, 0, st>>>(in, out, partials, tk, outer, R, C, sR, rows_per_split);
+    else
+      reduce_cols<Op, 1><<<grid, 256, 0, st>>>(in, out, partials, tk, outer, R, C, sR, rows_per_split);
+    if (partials) device_free(partials, rounded);
+    check_launch("reduce_cols");
+    return true;
+  }
+  return false;
+}
+
+template <class T, class O, class Op> static void launch_generic(const nt_view *x, const Plan &pl, void *out) {
+  const T *in = static_cast<const T *>(x->storage->data) + x->offset;
+  cudaStream_t st = stream();
+  if (pl.n_drop > 256) {
+    if (pl.n_keep > 0x7fffffffLL) fail_runtime("reduction: too many kept elements.");
+    reduce_generic<T, O, Op, 256><<<unsigned(pl.n_keep), 256, 0, st>>>(in, out, pl.keep, pl.drop, pl.n_keep, pl.n_drop);
+  } else {
+    int64_t blocks = ceil_div(pl.n_keep, 8);
+    if (blocks > 0x7fffffffLL) fail_runtime("reduction: too many kept elements.");
+    reduce_generic<T, O, Op, 32><<<unsigned(blocks), 256, 0, st>>>(in, out, pl.keep, pl.drop, pl.n_keep, pl.n_drop);
+  }
+  check_launch("reduce_generic");
+}
+
+template <class GOp, class FastOp>
+static nt_storage *reduce_impl(const nt_view *x, const int64_t *axes, int32_t n_axes, int out_dtype, const char *fname) {
+  check_view(x, fname);
+  require_cuda(x, fname);
+  if (n_axes < 0 || n_axes > x->ndim) fail_runtime(std::string(fname) + ": bad axis list.");
+  Plan pl = make_plan(x, axes, n_axes);
+  const int in_dtype = x->storage->dtype;
+  if (out_dtype == NT_BOOL) fail_invalid("Invalid dtype.");
+  dtype_itemsize(out_dtype);
+  const int storage_dtype = GOp::returns_idx ? NT_INT64 : out_dtype;
+  StorageRef out(storage_new(pl.n_keep, storage_dtype, NT_CUDA));
+  if (pl.n_keep == 0) return out.release();
+
+  if constexpr (!std::is_same_v<FastOp, void>) {
+    if (in_dtype == NT_FLOAT32 && out_dtype == NT_FLOAT32 && pl.n_drop > 0) {
+      if (try_fast_f32<FastOp>(x, pl, static_cast<float *>(out->data))) return out.release();
+    }
+  }
+  dispatch_all(in_dtype, [&]<class T>() {
+    dispatch_arith(out_dtype, [&]<class O>() { launch_generic<T, O, GOp>(x, pl, out->data); });
+  });
+  return out.release();
+}
+
+// mask helpers of the extremum backward
+struct EqMaskF { // float(x == m)
+  using in_t = float;
+  using out_t = float;
+  __device__ __forceinline__ float operator()(float x, float m) const { return (x == m) ? 1.0f : 0.0f; }
+};
+struct UniqueMaskMulF { // g * float(mask && count == 1)
+  using in_t = float;
+  using out_t = float;
+  __device__ __forceinline__ float operator()(float g, float mask, float count) const {
+    return g * ((mask != 0.0f && count == 1.0f) ? 1.0f : 0.0f);
+  }
+};
+
+} // namespace ntb
+
+using namespace ntb;
+
+extern "C" {
+
+int nt_sum(const nt_view *x, const int64_t *axes, int32_t n_axes, int dtype, nt_storage **out) {
+  NT_API_BEGIN
+  *out = reduce_impl<GSum, RSum>(x, axes, n_axes, dtype, "sum");
+  NT_API_END
+}
+int nt_max(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out) {
+  NT_API_BEGIN
+  check_view(x, "max");
+  *out = reduce_impl<GMax, RMax>(x, axes, n_axes, x->storage->dtype, "max");
+  NT_API_END
+}
+int nt_min(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out) {
+  NT_API_BEGIN
+  check_view(x, "min");
+  *out = reduce_impl<GMin, RMin>(x, axes, n_axes, x->storage->dtype, "min");
+  NT_API_END
+}
+int nt_argmax(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out) {
+  NT_API_BEGIN
+  check_view(x, "argmax");
+  *out = reduce_impl<GArgMax, void>(x, axes, n_axes, x->storage->dtype, "argmax");
+  NT_API_END
+}
+int nt_argmin(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out) {
+  NT_API_BEGIN
+  check_view(x, "argmin");
+  *out = reduce_impl<GArgMin, void>(x, axes, n_axes, x->storage->dtype, "argmin");
+  NT_API_END
+}
+
+int nt_extremum_backward(const nt_view *g_expanded, const nt_view *x, const nt_view *m_expanded,
+                         const int64_t *axes, int32_t n_axes, nt_storage **out) {
+  NT_API_BEGIN
+  const char *fname = "extremum_backward";
+  const nt_view *chk[3] = {g_expanded, x, m_expanded};
+  for (int i = 0; i < 3; ++i) {
+    check_view(chk[i], fname);
+    require_cuda(chk[i], fname);
+    if (chk[i]->storage->dtype != NT_FLOAT32) fail_invalid(std::string(fname) + ": Float32 only.");
+    require_same_shape(chk[0], chk[i], fname);
+  }
+  const int64_t n = view_numel(*x);
+  // mask = float(x == m)
+  StorageRef mask(storage_new(n, NT_FLOAT32, NT_CUDA));
+  nt_view mv = fresh_view(mask.s, *x);
+  {
+    const nt_view *views[3] = {&mv, x, m_expanded};
+    ew_launch<EqMaskF, 2>(EqMaskF{}, views);
+  }
+  // count of extremal positions per slice, kept dims set to 1 and expanded back with stride 0
+  StorageRef count(reduce_impl<GSum, RSum>(&mv, axes, n_axes, NT_FLOAT32, fname));
+  nt_view cv{};
+  cv.storage = count.s;
+  cv.ndim = x->ndim;
+  cv.offset = 0;
+  {
+    bool dropped[NT_MAX_DIMS] = {};
+    for (int i = 0; i < n_axes; ++i) dropped[axes[i]] = true;
+    int64_t st = 1;
+    for (int d = x->ndim - 1; d >= 0; --d) {
+      cv.shape[d] = x->shape[d];
+      if (dropped[d]) {
+        cv.strides[d] = 0;
+      } else {
+        cv.strides[d] = st;
+        st *= x->shape[d];
+      }
+    }
+  }
+  StorageRef o(storage_new(n, NT_FLOAT32, NT_CUDA));
+  nt_view ov = fresh_view(o.s, *x);
+  {
+    const nt_view *views[4] = {&ov, g_expanded, &mv, &cv};
+    ew_launch<UniqueMaskMulF, 3>(UniqueMaskMulF{}, views);
+  }
+  *out = o.release();
+  NT_API_END
+}
+
+} // extern "C"

@@ -1,0 +1,593 @@
+// Runtime half of the C ABI: error string, stream, caching arena, storage lifecycle, host<->device
+// moves, on-device dtype cast, factories and the host RNG stream.
+// Replaces src/cpp/{storage.cpp,allocator.cpp,factory.cu,random.h,cuda.cpp} of the reference.
+#include <map>
+#include <mutex>
+#include <random>
+
+#include "nt_core.cuh"
+
+namespace ntb {
+
+static thread_local std::string g_last_error;
+void set_last_error(const std::string &m) { g_last_error = m; }
+
+// ------------------------------------------------------------------------------------------
+struct Runtime {
+  std::mutex mu;
+  bool probed = false;
+  bool have_cuda = false;
+  int device = 0;
+  int sms = 148;
+  cudaStream_t compute = nullptr;
+  cudaStream_t comm = nullptr;
+  std::map<size_t, std::vector<void *>> dev_cache;
+  std::map<size_t, std::vector<void *>> pin_cache;
+  uint64_t bytes_reserved = 0, bytes_in_use = 0, n_malloc = 0;
+  size_t pin_cached_bytes = 0;
+  std::atomic<uint64_t> launches{0};
+  std::mt19937_64 rng{std::random_device{}()};
+};
+static Runtime &rt() {
+  static Runtime r;
+  return r;
+}
+
+static void probe_locked(Runtime &r) {
+  if (r.probed) return;
+  r.probed = true;
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  if (e != cudaSuccess || count <= 0) {
+    cudaGetLastError();
+    r.have_cuda = false;
+    return;
+  }
+  r.have_cuda = true;
+}
+
+static void ensure_streams_locked(Runtime &r) {
+  probe_locked(r);
+  if (!r.have_cuda) fail_runtime("CUDA device required: no usable GPU found (this library has no CPU compute path).");
+  if (r.compute) return;
+  NT_CUDA_CHECK(cudaSetDevice(r.device));
+  NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.compute, cudaStreamNonBlocking));
+  NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.comm, cudaStreamNonBlocking));
+  cudaDeviceProp prop;
+  NT_CUDA_CHECK(cudaGetDeviceProperties(&prop, r.device));
+  r.sms = prop.multiProcessorCount;
+}
+
+bool cuda_ok() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  probe_locked(r);
+  return r.have_cuda;
+}
+cudaStream_t stream() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  ensure_streams_locked(r);
+  return r.compute;
+}
+cudaStream_t comm_stream() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  ensure_streams_locked(r);
+  return r.comm;
+}
+int sm_count() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  ensure_streams_locked(r);
+  return r.sms;
+}
+void count_launch(uint64_t n) { rt().launches.fetch_add(n, std::memory_order_relaxed); }
+
+static size_t round_block(size_t nbytes) {
+  if (nbytes == 0) nbytes = 1;
+  const size_t small = 256, big = size_t(1) << 20;
+  if (nbytes <= big) return (nbytes + small - 1) / small * small;
+  return (nbytes + big - 1) / big * big;
+}
+
+static void trim_locked(Runtime &r) {
+  for (auto &kv : r.dev_cache) {
+    for (void *p : kv.second) {
+      cudaFree(p);
+      r.bytes_reserved -= kv.first;
+    }
+    kv.second.clear();
+  }
+}
+
+void *device_alloc(size_t nbytes, size_t *rounded) {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  ensure_streams_locked(r);
+  size_t sz = round_block(nbytes);
+  *rounded = sz;
+  auto it = r.dev_cache.find(sz);
+  if (it != r.dev_cache.end() && !it->second.empty()) {
+    void *p = it->second.back();
+    it->second.pop_back();
+    r.bytes_in_use += sz;
+    return p;
+  }
+  void *p = nullptr;
+  cudaError_t e = cudaMalloc(&p, sz);
+  if (e == cudaErrorMemoryAllocation) {
+    cudaGetLastError();
+    // Everything cached was freed behind work on the compute stream: drain it, give the cache
+    // back to the driver, try once more.
+    cudaStreamSynchronize(r.compute);
+    trim_locked(r);
+    e = cudaMalloc(&p, sz);
+  }
+  if (e != cudaSuccess) fail_runtime(std::string("cudaMalloc failed: ") + cudaGetErrorString(e));
+  r.n_malloc += 1;
+  r.bytes_reserved += sz;
+  r.bytes_in_use += sz;
+  return p;
+}
+void device_free(void *p, size_t rounded) {
+  if (!p) return;
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  r.dev_cache[rounded].push_back(p);
+  r.bytes_in_use -= rounded;
+}
+
+void *host_alloc(size_t nbytes, bool *pinned) {
+  Runtime &r = rt();
+  size_t sz = round_block(nbytes);
+  {
+    std::lock_guard<std::mutex> lk(r.mu);
+    probe_locked(r);
+    if (r.have_cuda && nbytes >= (size_t(1) << 16)) {
+      auto it = r.pin_cache.find(sz);
+      if (it != r.pin_cache.end() && !it->second.empty()) {
+        void *p = it->second.back();
+        it->second.pop_back();
+        r.pin_cached_bytes -= sz;
+        *pinned = true;
+        return p;
+      }
+      void *p = nullptr;
+      if (cudaHostAlloc(&p, sz, cudaHostAllocDefault) == cudaSuccess) {
+        *pinned = true;
+        return p;
+      }
+      cudaGetLastError();
+    }
+  }
+  *pinned = false;
+  void *p = ::malloc(sz);
+  if (!p) fail_runtime("host allocation failed");
+  return p;
+}
+void host_free(void *p, bool pinned, size_t nbytes) {
+  if (!p) return;
+  if (!pinned) {
+    ::free(p);
+    return;
+  }
+  // pinned blocks are cached by size like device blocks (cudaFreeHost is slow and synchronising),
+  // up to a bound so that a long session does not pin the whole host.
+  Runtime &r = rt();
+  size_t sz = round_block(nbytes);
+  {
+    std::lock_guard<std::mutex> lk(r.mu);
+    if (r.pin_cached_bytes + sz <= (size_t(8) << 30)) {
+      r.pin_cache[sz].push_back(p);
+      r.pin_cached_bytes += sz;
+      return;
+    }
+  }
+  cudaFreeHost(p);
+}
+
+// ------------------------------------------------------------------------------------------
+nt_storage *storage_new(int64_t n, int dtype, int device) {
+  if (n < 0) fail_invalid("Storage size must be non-negative.");
+  if (device != NT_CPU && device != NT_CUDA) fail_invalid("Unknown device.");
+  size_t nbytes = size_t(n) * size_t(dtype_itemsize(dtype));
+  nt_storage *s = new nt_storage();
+  s->n = n;
+  s->dtype = dtype;
+  s->device = device;
+  try {
+    if (device == NT_CUDA) {
+      s->data = device_alloc(nbytes, &s->rounded);
+    } else {
+      s->data = host_alloc(nbytes, &s->pinned);
+      s->rounded = nbytes;
+    }
+  } catch (...) {
+    delete s;
+    throw;
+  }
+  return s;
+}
+void storage_release(nt_storage *s) {
+  if (!s) return;
+  if (s->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) {
+    if (s->device == NT_CUDA)
+      device_free(s->data, s->rounded);
+    else
+      host_free(s->data, s->pinned, s->rounded);
+    delete s;
+  }
+}
+
+void check_view(const nt_view *v, const char *fname) {
+  if (!v || !v->storage) fail_runtime(std::string(fname) + ": null view or storage.");
+  if (v->ndim < 0 || v->ndim > NT_MAX_DIMS)
+    fail_runtime(std::string(fname) + ": views of more than 8 dimensions are not supported on device.");
+  int64_t lo = v->offset, hi = v->offset, n = 1;
+  for (int i = 0; i < v->ndim; ++i) {
+    if (v->shape[i] < 0) fail_runtime(std::string(fname) + ": negative extent.");
+    n *= v->shape[i];
+  }
+  if (n == 0) return;
+  for (int i = 0; i < v->ndim; ++i) {
+    int64_t span = (v->shape[i] - 1) * v->strides[i];
+    if (span < 0) lo += span; else hi += span;
+  }
+  if (lo < 0 || hi >= v->storage->n)
+    fail_runtime(std::string(fname) + ": view exceeds its storage (index range [" + std::to_string(lo) + ", " +
+                 std::to_string(hi) + "], capacity " + std::to_string(v->storage->n) + ").");
+}
+void require_cuda(const nt_view *v, const char *fname) {
+  if (v->storage->device != NT_CUDA)
+    fail_runtime(std::string(fname) + ": requires Cuda (this library has no CPU compute path).");
+}
+void require_same_shape(const nt_view *a, const nt_view *b, const char *fname) {
+  bool same = a->ndim == b->ndim;
+  for (int i = 0; same && i < a->ndim; ++i) same = a->shape[i] == b->shape[i];
+  if (!same) fail_runtime(std::string(fname) + ": Expected two views of the same shape.");
+}
+void require_same_dtype(const nt_view *a, const nt_view *b, const char *fname) {
+  if (a->storage->dtype != b->storage->dtype)
+    fail_runtime(std::string(fname) + ": Expected two storages on the same dtype.");
+}
+void require_same_device(const nt_view *a, const nt_view *b, const char *fname) {
+  if (a->storage->device != b->storage->device)
+    fail_runtime(std::string(fname) + ": Expected two storages on the same device.");
+}
+
+// ------------------------------------------------------------------------------------------
+// kernels of this file
+template <class T> __global__ void fill_kernel(T *out, int64_t n, T value) {
+  int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  int64_t step = int64_t(gridDim.x) * blockDim.x;
+  for (; i < n; i += step) out[i] = value;
+}
+
+// Storage::cast semantics (src/cpp/storage.cpp:54-62): to Bool is `s != 0`, everything else static_cast.
+template <class S, class D> __global__ void cast_kernel(const S *in, D *out, int64_t n) {
+  int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  int64_t step = int64_t(gridDim.x) * blockDim.x;
+  for (; i < n; i += step) {
+    if constexpr (std::is_same_v<D, bool>)
+      out[i] = in[i] ? true : false;
+    else
+      out[i] = static_cast<D>(in[i]);
+  }
+}
+
+static int grid_for(int64_t n, int block) {
+  int64_t g = ceil_div(n, block);
+  int64_t cap = int64_t(sm_count()) * 16;
+  return int(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+template <class T> static void fill_device(nt_storage *s, T value) {
+  if (s->n == 0) return;
+  fill_kernel<T><<<grid_for(s->n, 256), 256, 0, stream()>>>(static_cast<T *>(s->data), s->n, value);
+  check_launch("fill");
+}
+
+template <class T> static T scalar_as(const nt_scalar *v) {
+  switch (v->kind) {
+  case 0: return static_cast<T>(v->i != 0);
+  case 1: return static_cast<T>(v->i);
+  case 2: return static_cast<T>(v->d);
+  default: fail_type("Unknown scalar type.");
+  }
+}
+
+static nt_storage *full_impl(int64_t n, const nt_scalar *value, int dtype, int device) {
+  StorageRef out(storage_new(n, dtype, device));
+  dispatch_all(dtype, [&]<class T>() {
+    T v = scalar_as<T>(value);
+    if (device == NT_CUDA) {
+      fill_device<T>(out.s, v);
+    } else {
+      T *p = static_cast<T *>(out->data);
+      for (int64_t i = 0; i < n; ++i) p[i] = v;
+    }
+  });
+  return out.release();
+}
+
+static nt_storage *to_device_impl(nt_storage *s, int device) {
+  if (s->device == device) {
+    storage_retain(s);
+    return s;
+  }
+  StorageRef out(storage_new(s->n, s->dtype, device));
+  size_t nbytes = size_t(s->n) * dtype_itemsize(s->dtype);
+  if (nbytes) {
+    cudaStream_t st = stream();
+    cudaMemcpyKind kind = (s->device == NT_CPU) ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost;
+    NT_CUDA_CHECK(cudaMemcpyAsync(out->data, s->data, nbytes, kind, st));
+    // The host side of either direction may be reused or read right after the call returns.
+    NT_CUDA_CHECK(cudaStreamSynchronize(st));
+  }
+  return out.release();
+}
+
+} // namespace ntb
+
+using namespace ntb;
+
+extern "C" {
+
+const char *nt_last_error(void) { return g_last_error.c_str(); }
+
+int nt_is_cuda_available(void) {
+  try {
+    return cuda_ok() ? 1 : 0;
+  } catch (...) {
+    return 0;
+  }
+}
+
+int nt_cuda_sync(void) {
+  NT_API_BEGIN
+  if (cuda_ok()) {
+    NT_CUDA_CHECK(cudaStreamSynchronize(stream()));
+    NT_CUDA_CHECK(cudaStreamSynchronize(comm_stream()));
+  }
+  NT_API_END
+}
+
+int nt_set_device(int ordinal) {
+  NT_API_BEGIN
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  if (r.compute && r.device != ordinal) fail_runtime("nt_set_device: the device is already initialised.");
+  probe_locked(r);
+  if (!r.have_cuda) fail_runtime("nt_set_device: no CUDA device.");
+  int count = 0;
+  NT_CUDA_CHECK(cudaGetDeviceCount(&count));
+  if (ordinal < 0 || ordinal >= count) fail_invalid("nt_set_device: ordinal out of range.");
+  r.device = ordinal;
+  NT_CUDA_CHECK(cudaSetDevice(ordinal));
+  NT_API_END
+}
+
+int nt_device_count(int *out) {
+  NT_API_BEGIN
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess) {
+    cudaGetLastError();
+    count = 0;
+  }
+  *out = count;
+  NT_API_END
+}
+
+void *nt_stream(void) {
+  try {
+    return (void *)stream();
+  } catch (...) {
+    return nullptr;
+  }
+}
+
+int nt_launch_count(uint64_t *out) {
+  NT_API_BEGIN
+  *out = rt().launches.load();
+  NT_API_END
+}
+
+int nt_allocator_stats(uint64_t *bytes_reserved, uint64_t *bytes_in_use, uint64_t *n_cuda_malloc) {
+  NT_API_BEGIN
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  if (bytes_reserved) *bytes_reserved = r.bytes_reserved;
+  if (bytes_in_use) *bytes_in_use = r.bytes_in_use;
+  if (n_cuda_malloc) *n_cuda_malloc = r.n_malloc;
+  NT_API_END
+}
+
+int nt_allocator_trim(void) {
+  NT_API_BEGIN
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  if (r.compute) NT_CUDA_CHECK(cudaStreamSynchronize(r.compute));
+  trim_locked(r);
+  NT_API_END
+}
+
+// ---------------------------------------------------------------- storage
+int nt_storage_allocate(int64_t n, int dtype, int device, nt_storage **out) {
+  NT_API_BEGIN
+  *out = storage_new(n, dtype, device);
+  NT_API_END
+}
+int nt_storage_retain(nt_storage *s) {
+  NT_API_BEGIN
+  if (!s) fail_runtime("null storage");
+  storage_retain(s);
+  NT_API_END
+}
+int nt_storage_release(nt_storage *s) {
+  NT_API_BEGIN
+  storage_release(s);
+  NT_API_END
+}
+int64_t nt_storage_size(const nt_storage *s) { return s->n; }
+int64_t nt_storage_itemsize(const nt_storage *s) {
+  try {
+    return dtype_itemsize(s->dtype);
+  } catch (...) {
+    return 0;
+  }
+}
+int nt_storage_dtype(const nt_storage *s) { return s->dtype; }
+int nt_storage_device(const nt_storage *s) { return s->device; }
+uint64_t nt_storage_version(const nt_storage *s) { return s->version; }
+void *nt_storage_data(nt_storage *s) { return s->data; }
+
+int nt_storage_clone(const nt_storage *s, nt_storage **out) {
+  NT_API_BEGIN
+  StorageRef o(storage_new(s->n, s->dtype, s->device));
+  size_t nbytes = size_t(s->n) * dtype_itemsize(s->dtype);
+  if (nbytes) {
+    if (s->device == NT_CPU)
+      std::memcpy(o->data, s->data, nbytes);
+    else
+      NT_CUDA_CHECK(cudaMemcpyAsync(o->data, s->data, nbytes, cudaMemcpyDeviceToDevice, stream()));
+  }
+  *out = o.release();
+  NT_API_END
+}
+
+int nt_storage_to(nt_storage *s, int device, nt_storage **out) {
+  NT_API_BEGIN
+  if (device != NT_CPU && device != NT_CUDA) fail_invalid("Unknown device.");
+  *out = to_device_impl(s, device);
+  NT_API_END
+}
+
+int nt_storage_cast(nt_storage *s, int dtype, nt_storage **out) {
+  NT_API_BEGIN
+  dtype_itemsize(dtype);
+  if (dtype == s->dtype) { // no copy on same dtype (src/cpp/storage.cpp:48-49)
+    storage_retain(s);
+    *out = s;
+    return NT_OK;
+  }
+  StorageRef o(storage_new(s->n, dtype, s->device));
+  if (s->n) {
+    dispatch_all(s->dtype, [&]<class S>() {
+      dispatch_all(dtype, [&]<class D>() {
+        const S *in = static_cast<const S *>(s->data);
+        D *dst = static_cast<D *>(o->data);
+        if (s->device == NT_CUDA) {
+          cast_kernel<S, D><<<grid_for(s->n, 256), 256, 0, stream()>>>(in, dst, s->n);
+          check_launch("cast");
+        } else {
+          // host staging buffers only: the cast of a CPU storage is bookkeeping for tensor
+          // construction (python scalars, index arrays), not a compute path.
+          for (int64_t i = 0; i < s->n; ++i) {
+            if constexpr (std::is_same_v<D, bool>)
+              dst[i] = in[i] ? true : false;
+            else
+              dst[i] = static_cast<D>(in[i]);
+          }
+        }
+      });
+    });
+  }
+  *out = o.release();
+  NT_API_END
+}
+
+int nt_storage_upload(nt_storage *dst, const void *host_src, int64_t nbytes) {
+  NT_API_BEGIN
+  if (nbytes < 0 || size_t(nbytes) > size_t(dst->n) * dtype_itemsize(dst->dtype))
+    fail_runtime("nt_storage_upload: byte count exceeds the storage.");
+  if (nbytes == 0) return NT_OK;
+  if (dst->device == NT_CPU) {
+    std::memcpy(dst->data, host_src, size_t(nbytes));
+  } else {
+    cudaStream_t st = stream();
+    NT_CUDA_CHECK(cudaMemcpyAsync(dst->data, host_src, size_t(nbytes), cudaMemcpyHostToDevice, st));
+    NT_CUDA_CHECK(cudaStreamSynchronize(st));
+  }
+  NT_API_END
+}
+
+int nt_storage_download(const nt_storage *src, void *host_dst, int64_t nbytes) {
+  NT_API_BEGIN
+  if (nbytes < 0 || size_t(nbytes) > size_t(src->n) * dtype_itemsize(src->dtype))
+    fail_runtime("nt_storage_download: byte count exceeds the storage.");
+  if (nbytes == 0) return NT_OK;
+  if (src->device == NT_CPU) {
+    std::memcpy(host_dst, src->data, size_t(nbytes));
+  } else {
+    cudaStream_t st = stream();
+    NT_CUDA_CHECK(cudaMemcpyAsync(host_dst, src->data, size_t(nbytes), cudaMemcpyDeviceToHost, st));
+    NT_CUDA_CHECK(cudaStreamSynchronize(st));
+  }
+  NT_API_END
+}
+
+// ---------------------------------------------------------------- factories
+int nt_zeros(int64_t n, int dtype, int device, nt_storage **out) {
+  NT_API_BEGIN
+  nt_scalar z{1, 0, 0.0};
+  *out = full_impl(n, &z, dtype, device);
+  NT_API_END
+}
+int nt_ones(int64_t n, int dtype, int device, nt_storage **out) {
+  NT_API_BEGIN
+  nt_scalar o{1, 1, 1.0};
+  *out = full_impl(n, &o, dtype, device);
+  NT_API_END
+}
+int nt_full(int64_t n, const nt_scalar *value, int dtype, int device, nt_storage **out) {
+  NT_API_BEGIN
+  *out = full_impl(n, value, dtype, device);
+  NT_API_END
+}
+
+int nt_eye(int64_t n, int dtype, int device, nt_storage **out) {
+  NT_API_BEGIN
+  StorageRef host(storage_new(n * n, dtype, NT_CPU));
+  dispatch_all(dtype, [&]<class T>() {
+    T *p = static_cast<T *>(host->data);
+    for (int64_t i = 0; i < n * n; ++i) p[i] = static_cast<T>(0);
+    for (int64_t i = 0; i < n; ++i) p[i * n + i] = static_cast<T>(1);
+  });
+  *out = to_device_impl(host.s, device);
+  NT_API_END
+}
+
+int nt_arange(int64_t n, int64_t start, int64_t step, int dtype, int device, nt_storage **out) {
+  NT_API_BEGIN
+  StorageRef host(storage_new(n, dtype, NT_CPU));
+  dispatch_all(dtype, [&]<class T>() {
+    T *p = static_cast<T *>(host->data);
+    for (int64_t i = 0; i < n; ++i) p[i] = static_cast<T>(start + i * step);
+  });
+  *out = to_device_impl(host.s, device);
+  NT_API_END
+}
+
+int nt_manual_seed(uint64_t seed) {
+  NT_API_BEGIN
+  rt().rng.seed(seed);
+  NT_API_END
+}
+
+// Same host generator and distribution as the reference (src/cpp/random.h:6-9, factory.cu:73-83),
+// so a seed reproduces the reference's parameter initialisation value for value.
+int nt_uniform(int64_t n, int dtype, int device, nt_storage **out) {
+  NT_API_BEGIN
+  StorageRef host(storage_new(n, dtype, NT_CPU));
+  dispatch_float(dtype, [&]<class T>() {
+    T *p = static_cast<T *>(host->data);
+    std::uniform_real_distribution<T> dist(0.0, 1.0);
+    auto &rng = rt().rng;
+    for (int64_t i = 0; i < n; ++i) p[i] = static_cast<T>(dist(rng));
+  });
+  *out = to_device_impl(host.s, device);
+  NT_API_END
+}
+
+} // extern "C"
