@@ -1,0 +1,479 @@
+"""Benchmark of the op-kernel hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--no-ops]
+
+Headline (the line's `metric`/`value`): training throughput, in samples/s, of the data-parallel MLP
+configuration -- 8 x Linear(4096, 4096) with Tanh between them, MSE loss against N(0,1) targets,
+global batch 16384 of N(0,1) rows sharded over N ranks, SGD lr 1e-3, Kaiming-uniform init from seed
+0, fp32 with 3xTF32 tensor-core products -- on synthetic data.  A step is forward + backward +
+gradient all-reduce + update on one global batch.  `value` is measured with the batch resident in
+HBM; `e2e` feeds every step's batch from pinned host memory (double-buffered host->device copies
+inside the timed region) and reads the loss back to the host every step.
+
+At N = 1 the same line also carries, under "ops", the per-op sweep of the other configurations
+(elementwise and reductions in GB/s against the measured HBM copy rate, matmul in TFLOP/s), the
+`roofline` of the dominant kernel of the step (the 3xTF32 GEMM) and `cpu_baseline`, the reference's
+own CPU path timed on this box on a bounded sample.
+
+`--impl reference` times the reference's CPU implementation of the same step (its native module
+built into oracle/_ref, else the C restatement) on a bounded sample and prints the same line shape.
+
+Under torchrun (N > 1) one process drives one GPU; torch.distributed (gloo) is used only for the
+host-side rendezvous, barriers and the max-over-ranks of the device timings.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WIDTH, LAYERS, GLOBAL_BATCH, LR = 4096, 8, 16384, 1e-3
+WORKLOAD = ("configs[4]: 8-layer MLP fp32 width 4096, tanh, MSE vs N(0,1) targets, global batch 16384 ~N(0,1) "
+            "sharded data-parallel, SGD lr 1e-3, Kaiming-uniform init seed 0")
+
+
+def measured_peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ---------------------------------------------------------------------------------------------
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                smax.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, cell in zip(names, r[5:9]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+def reference_arm(args, rank: int) -> None:
+    """The reference's CPU implementation of the step, on a bounded sample of the batch."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+
+    oracle = O.RefOracle() if O.ref_available() else O.PortOracle()
+    t0 = time.perf_counter()
+    stream = oracle.uniform(0, LAYERS * WIDTH * WIDTH)
+    params = []
+    for i in range(LAYERS):
+        w = O.kaiming(oracle, stream[i * WIDTH * WIDTH:(i + 1) * WIDTH * WIDTH], WIDTH, WIDTH)
+        params.append((w, np.zeros(WIDTH, np.float32)))
+    del stream
+    init_s = time.perf_counter() - t0
+    batch = 2
+    rng = np.random.default_rng(40)
+    X = rng.standard_normal((batch, WIDTH)).astype(np.float32)
+    Y = np.random.default_rng(41).standard_normal((batch, WIDTH)).astype(np.float32)
+    budget_s = 150.0
+    times = []
+    total = args.warmup + args.steps
+    for i in range(total):
+        t = time.perf_counter()
+        O.mlp_step(oracle, params, X, Y, LR, "tanh")
+        dt = time.perf_counter() - t
+        if i == 0 and dt * total > budget_s and batch > 1:
+            batch = 1
+            X, Y = X[:1], Y[:1]
+        if i >= args.warmup:
+            times.append((dt, X.shape[0]))
+    seconds = sum(t for t, _ in times)
+    samples = sum(b for _, b in times)
+    value = samples / seconds
+    cores = 1
+    line = {
+        "impl": "reference", "metric": "mlp_train_samples_per_s", "value": value, "unit": "samples/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * seconds / len(times),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "width": WIDTH, "layers": LAYERS},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": cores, "kind": oracle.kind,
+                         "sample": f"batch of {times[-1][1]} of the 16384 rows through the full 8x4096^2 model, "
+                                   f"forward+backward+SGD per step, single thread (the reference's CPU path has "
+                                   f"no threading); init {init_s:.1f}s not counted; host has {os.cpu_count()} cores"},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def cpu_baseline_sample(budget_s: float = 20.0) -> dict:
+    """Rank 0, N = 1: one step of the reference's CPU path on a batch of 2 rows of the workload."""
+    from oracle import oracle as O
+
+    oracle = O.RefOracle() if O.ref_available() else O.PortOracle()
+    stream = oracle.uniform(0, LAYERS * WIDTH * WIDTH)
+    params = []
+    for i in range(LAYERS):
+        w = O.kaiming(oracle, stream[i * WIDTH * WIDTH:(i + 1) * WIDTH * WIDTH], WIDTH, WIDTH)
+        params.append((w, np.zeros(WIDTH, np.float32)))
+    del stream
+    batch = 2
+    X = np.random.default_rng(40).standard_normal((batch, WIDTH)).astype(np.float32)
+    Y = np.random.default_rng(41).standard_normal((batch, WIDTH)).astype(np.float32)
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < 3 and (time.perf_counter() - t_start) < budget_s:
+        t = time.perf_counter()
+        O.mlp_step(oracle, params, X, Y, LR, "tanh")
+        times.append(time.perf_counter() - t)
+    best = min(times)
+    return {"value": batch / best, "unit": "samples/s", "cores": 1, "kind": oracle.kind,
+            "sample": f"best of {len(times)} steps on a batch of {batch} of the 16384 rows through the full "
+                      f"8x4096^2 model (forward+backward+SGD), single thread: the reference's CPU path has no "
+                      f"threading; host has {os.cpu_count()} cores"}
+
+
+# ---------------------------------------------------------------------------------------------
+def build_model(nt, nn):
+    nt.manual_seed(0)
+    layers = []
+    for i in range(LAYERS):
+        layers.append(nn.Linear(WIDTH, WIDTH))
+        if i < LAYERS - 1:
+            layers.append(nn.Tanh())
+    return nn.Sequential(*layers)
+
+
+def pinned(nt, array: np.ndarray):
+    """Copy `array` into a pinned host storage; returns (storage, numpy view)."""
+    s = nt._C.Storage.allocate(array.size, nt.float32, nt.Device.Cpu)
+    view = np.frombuffer(memoryview(s), dtype=np.float32)
+    view[:] = array.reshape(-1)
+    return s, view
+
+
+def time_ops(nt, peaks: dict) -> dict:
+    """Per-op sweep of the elementwise / reduction / matmul configurations at N = 1."""
+    _C = nt._C
+    dev = lambda a: nt.Tensor.from_numpy(a, "cuda")  # noqa: E731
+    r = np.random.default_rng
+    hbm = peaks["hbm_gbs"]
+    out: dict = {}
+
+    def flush():
+        _C.zeros(128 * 1024 * 1024, nt.float32, nt.Device.Cuda)  # 512 MB written: larger than L2
+
+    def timed(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        ms = []
+        for _ in range(iters):
+            flush()
+            e0 = _C.Event().record()
+            fn()
+            e1 = _C.Event().record()
+            ms.append(e0.elapsed_ms(e1))
+        return statistics.median(ms)
+
+    N = 4096
+    a, b = dev(r(10).uniform(-1, 1, (N, N)).astype(np.float32)), dev(r(11).uniform(-1, 1, (N, N)).astype(np.float32))
+    d = dev(r(12).uniform(0.5, 2, (N, N)).astype(np.float32))
+    v, dv = dev(r(13).uniform(-1, 1, (N,)).astype(np.float32)), dev(r(17).uniform(0.5, 2, (N,)).astype(np.float32))
+    n_, p_ = dev(r(14).standard_normal((N, N)).astype(np.float32)), dev(r(15).uniform(0.1, 10, (N, N)).astype(np.float32))
+    G = dev(r(16).standard_normal((N, N)).astype(np.float32))
+    numel = N * N
+
+    def record(name, ms, nbytes):
+        gbs = nbytes / ms / 1e6
+        out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm, 3)}
+
+    with nt.no_grad():
+        for name, fn in {"add": lambda x, y: x + y, "sub": lambda x, y: x - y, "mul": lambda x, y: x * y,
+                         "truediv": lambda x, y: x / y}.items():
+            y, yv = (d, dv) if name == "truediv" else (b, v)
+            record(f"{name}.contiguous", timed(lambda: fn(a, y)), 3 * numel * 4)
+            record(f"{name}.broadcast_row", timed(lambda: fn(a, yv)), (2 * numel + N) * 4)
+            yt = y.T
+            record(f"{name}.transposed", timed(lambda: fn(a, yt)), 3 * numel * 4)
+        for name, fn, src in [("pow2", lambda x: x ** 2.0, a), ("exp", lambda x: x.exp(), n_), ("neg", lambda x: -x, n_),
+                              ("relu", nt.relu, n_), ("tanh", nt.tanh, n_), ("sigmoid", nt.sigmoid, n_),
+                              ("log", lambda x: x.log(), p_), ("sqrt", nt.sqrt, p_)]:
+            record(f"{name}.forward", timed(lambda: fn(src)), 2 * numel * 4)
+        t_out = nt.tanh(n_)
+        for name, kern, saved in [("relu", _C.relu_backward, nt.relu(n_)), ("tanh", _C.tanh_backward, t_out),
+                                  ("sigmoid", _C.sigmoid_backward, nt.sigmoid(n_)), ("exp", _C.exp_backward, n_.exp()),
+                                  ("log", _C.log_backward, p_), ("sqrt", _C.sqrt_backward, nt.sqrt(p_))]:
+            gv, sv = G._C_view, saved._C_view
+            record(f"{name}.backward", timed(lambda: kern(gv, sv)), 3 * numel * 4)
+        record("pow2.backward", timed(lambda: _C.pow_backward(G._C_view, a._C_view, 2.0)), 3 * numel * 4)
+        del a, b, d, n_, p_, G, t_out
+
+        M = 8192
+        x = dev(r(20).standard_normal((M, M)).astype(np.float32))
+        y3 = dev(r(21).standard_normal((64, 1, 16384)).astype(np.float32))
+        for op in ("sum", "mean", "max", "min"):
+            for label, axes in (("dim0", (0,)), ("dim1", (1,)), ("full", None)):
+                record(f"{op}.{label}", timed(lambda: getattr(x, op)(axes)), M * M * 4)
+            record(f"{op}.[64,1,16384].last", timed(lambda: getattr(y3, op)(-1), iters=20), y3.numel * 4)
+        ones_row = dev(np.ones((M,), np.float32))
+        record("sum.backward_materialised", timed(lambda: ones_row.expand(M, M).clone()), M * M * 4)
+        m1 = x.max((1,))
+        g_full = ones_row.reshape(M, 1).expand(M, M)
+        m_full = m1.reshape(M, 1).expand(M, M)
+        record("max.backward", timed(lambda: _C.extremum_backward(g_full._C_view, x._C_view, m_full._C_view, [1])),
+               2 * M * M * 4)
+        del x, y3, m1, g_full, m_full
+
+        tf32_peak = peaks["bf16_tflops"] / 2
+        for label, (m, k, n, bt) in {"4096x4096x4096": (4096, 4096, 4096, 1), "8192x1024x4096": (8192, 1024, 4096, 1),
+                                     "32x512x512x512": (512, 512, 512, 32)}.items():
+            shape_a = (bt, m, k) if bt > 1 else (m, k)
+            shape_b = (bt, k, n) if bt > 1 else (k, n)
+            shape_c = (bt, m, n) if bt > 1 else (m, n)
+            A = dev(r(30).uniform(-1, 1, shape_a).astype(np.float32))
+            B = dev(r(31).uniform(-1, 1, shape_b).astype(np.float32))
+            Gc = dev(r(32).uniform(-1, 1, shape_c).astype(np.float32))
+            flops = 2.0 * bt * m * n * k
+            for mode, mname in ((1, "3xtf32"), (0, "fp32_simt")):
+                _C.set_matmul_mode(mode)
+                try:
+                    res = {}
+                    for which, fn in (("forward", lambda: A @ B), ("grad_a", lambda: Gc @ B.transpose(-2, -1)),
+                                      ("grad_b", lambda: A.transpose(-2, -1) @ Gc)):
+                        ms = timed(fn, iters=5 if mode == 0 else 10, warm=2)
+                        res[which] = {"ms": round(ms, 4), "TFLOP/s": round(flops / ms / 1e9, 2)}
+                        if mode == 1:
+                            res[which]["tensor_pipe_frac_of_tf32_peak"] = round(3 * flops / ms / 1e9 / tf32_peak, 3)
+                    out[f"matmul.{label}.{mname}"] = res
+                finally:
+                    _C.set_matmul_mode(1)
+            del A, B, Gc
+    out["_notes"] = ("L2 flushed between timed iterations by a 512 MB fill; median of 10 device-timed launches; "
+                     "bytes are the reference's mem_bytes() accounting; tf32 peak taken as measured bf16 / 2")
+    return out
+
+
+def product_arm(args, rank: int, local_rank: int, world: int) -> None:
+    import nanotorch_b200 as nt
+    import nanotorch_b200.nn as nn
+    from nanotorch_b200.dp import Communicator, DataParallelSGD, shard_bounds
+
+    _C = nt._C
+    _C.set_device(local_rank)
+    if not nt.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path in the product)")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # host-side plumbing only (gloo): rendezvous, barrier, max of timings
+
+        dist.init_process_group("gloo", init_method="env://", rank=rank, world_size=world)
+
+    def exchange_id(uid):
+        box = [uid]
+        dist.broadcast_object_list(box, src=0)
+        return box[0]
+
+    def barrier():
+        _C.cuda_sync()
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(x: float) -> float:
+        if dist is None:
+            return x
+        import torch
+
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    comm = Communicator(rank, world, exchange_id)
+    peaks = measured_peaks()
+    lo, hi = shard_bounds(GLOBAL_BATCH, rank, world)
+    local = hi - lo
+
+    model = build_model(nt, nn)
+    opt = DataParallelSGD(model.parameters(), LR, comm)
+    # two synthetic global batches (alternated by the end-to-end loop); this rank's rows only
+    host = []
+    for seed in (40, 42):
+        Xg = np.random.default_rng(seed).standard_normal((GLOBAL_BATCH, WIDTH), dtype=np.float32)
+        Yg = np.random.default_rng(seed + 1).standard_normal((GLOBAL_BATCH, WIDTH), dtype=np.float32)
+        host.append((pinned(nt, Xg[lo:hi]), pinned(nt, Yg[lo:hi])))
+        del Xg, Yg
+    Xd = [nt.Tensor._new_contiguous(_C.Storage.allocate(local * WIDTH, nt.float32, nt.Device.Cuda), (local, WIDTH))
+          for _ in range(2)]
+    Yd = [nt.Tensor._new_contiguous(_C.Storage.allocate(local * WIDTH, nt.float32, nt.Device.Cuda), (local, WIDTH))
+          for _ in range(2)]
+    nbytes = local * WIDTH * 4
+
+    def step(X, Y):
+        loss = nt.mean((model(X) - Y) ** 2)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return loss
+
+    # ---------------- resident: batch already in HBM
+    Xd[0].storage.upload(host[0][0][1].ctypes.data, nbytes)
+    Yd[0].storage.upload(host[0][1][1].ctypes.data, nbytes)
+    for _ in range(args.warmup):
+        step(Xd[0], Yd[0])
+    barrier()
+    launches0 = _C.launch_count()
+    _C.matmul_profile_enable(True)
+    with ClockSampler(local_rank) as clocks:
+        e0 = _C.Event().record()
+        for _ in range(args.steps):
+            loss = step(Xd[0], Yd[0])
+        e1 = _C.Event().record()
+        ms_resident = e0.elapsed_ms(e1)
+        barrier()
+    _C.matmul_profile_enable(False)
+    gemm_ms, gemm_launches = _C.matmul_profile_read()
+    launches = _C.launch_count() - launches0
+    last_loss = float(loss.numpy())
+    ms_resident = max_over_ranks(ms_resident)
+
+    # ---------------- end to end: every step's batch comes from pinned host memory
+    def feed(i):
+        hx, hy = host[i % 2]
+        _C.upload_async(Xd[i % 2].storage, hx[1].ctypes.data, nbytes)
+        _C.upload_async(Yd[i % 2].storage, hy[1].ctypes.data, nbytes)
+
+    def e2e_loop(n, first):
+        result = None
+        for i in range(first, first + n):
+            _C.upload_fence()      # compute waits for batch i
+            feed(i + 1)            # batch i+1 streams in while step i computes
+            result = float(step(Xd[i % 2], Yd[i % 2]).numpy())  # device->host read of the loss, every step
+        return result
+
+    feed(0)
+    e2e_loop(args.warmup, 0)
+    barrier()
+    e0 = _C.Event().record()
+    t_wall = time.perf_counter()
+    e2e_loop(args.steps, args.warmup)
+    e1 = _C.Event().record()
+    ms_e2e = max(e0.elapsed_ms(e1), 1e3 * (time.perf_counter() - t_wall))
+    barrier()
+    ms_e2e = max_over_ranks(ms_e2e)
+
+    samples = GLOBAL_BATCH * args.steps
+    value = samples / (ms_resident / 1e3)
+    e2e_value = samples / (ms_e2e / 1e3)
+
+    if rank == 0:
+        m, k, n = local, WIDTH, WIDTH
+        tensor_flops_per_launch = 3 * 2.0 * m * n * k   # three TF32 products per fp32 product
+        avg_ms = gemm_ms / max(gemm_launches, 1)
+        tf32_peak = peaks["bf16_tflops_sustained"] / 2
+        achieved = tensor_flops_per_launch / avg_ms / 1e9 if gemm_launches else None
+        line = {
+            "metric": "mlp_train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_resident / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_rank_batch": local, "width": WIDTH,
+                       "layers": LAYERS, "matmul_mode": "3xTF32 (tcgen05)" if _C.get_matmul_mode() == 1 else "fp32",
+                       "parallelism": f"dp{world}", "l2": "inputs larger than L2 (weights 537 MB, activations 268 MB each)",
+                       "final_loss": last_loss},
+            "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": 2 * nbytes * world,
+                    "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks.summary(),
+            "roofline": {
+                "kernel": "gemm_3xtf32 (tcgen05.mma kind::tf32, 3 products per fp32 product)",
+                "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
+                "frac": (achieved / tf32_peak) if achieved else None, "traffic": None,
+                "peak_source": f"{peaks['source']}: sustained bf16 cuBLAS rate / 2 (TF32 issues at half the bf16 rate; "
+                               f"no TF32 figure is recorded)",
+                "launches": gemm_launches, "avg_launch_ms": avg_ms,
+                "algorithmic_fp32_tflops": (2.0 * m * n * k / avg_ms / 1e9) if gemm_launches else None,
+            },
+        }
+        if world == 1 and not args.no_ops:
+            line["ops"] = time_ops(nt, peaks)
+            line["cpu_baseline"] = cpu_baseline_sample()
+        print(json.dumps(line))
+    barrier()
+    comm.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-ops", action="store_true", help="skip the per-op sweep and the CPU baseline sample")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    product_arm(args, rank, local_rank, world)
+
+
+if __name__ == "__main__":
+    main()

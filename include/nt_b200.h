@@ -76,6 +76,17 @@ int nt_launch_count(uint64_t *out);   /* kernels launched by this library since 
 int nt_allocator_stats(uint64_t *bytes_reserved, uint64_t *bytes_in_use, uint64_t *n_cuda_malloc);
 int nt_allocator_trim(void);          /* return cached blocks to the driver */
 
+/* Timing on the library stream (no counterpart in the reference, which times with perf_counter
+ * around a device sync, scripts/profile_ops.py:61-89). */
+int nt_event_create(void **event);
+int nt_event_record(void *event);                               /* on the compute stream */
+int nt_event_elapsed_ms(void *start, void *stop, float *ms);    /* waits for `stop` */
+int nt_event_destroy(void *event);
+/* Per-launch timing of the matmul kernels: when enabled every matmul launch is bracketed by two
+ * events; nt_matmul_profile_read waits for them and returns (and clears) their sum and count. */
+int nt_matmul_profile_enable(int on);
+int nt_matmul_profile_read(double *total_ms, int64_t *launches);
+
 /* ------------------------------------------------------------------ storage (src/cpp/storage.cpp:4-70) */
 int nt_storage_allocate(int64_t n, int dtype, int device, nt_storage **out); /* Storage::allocate */
 int nt_storage_retain(nt_storage *s);
@@ -91,6 +102,15 @@ int nt_storage_to(nt_storage *s, int device, nt_storage **out);         /* Stora
 int nt_storage_cast(nt_storage *s, int dtype, nt_storage **out);        /* Storage::cast; on device, no host round trip */
 int nt_storage_upload(nt_storage *dst, const void *host_src, int64_t nbytes);   /* H2D (or memcpy for CPU storages) */
 int nt_storage_download(const nt_storage *src, void *host_dst, int64_t nbytes); /* D2H, synchronises */
+/* Overlapped input feed (no counterpart: the reference's Storage::to is a blocking cudaMemcpy).
+ * The copy runs on a dedicated stream, ordered after everything enqueued on the compute stream so
+ * far (so a buffer that an earlier step still reads is not overwritten early); `host_src` must be
+ * pinned and stay valid until the fence.  nt_upload_fence makes the compute stream wait for every
+ * copy issued so far. */
+int nt_storage_upload_async(nt_storage *dst, const void *host_src, int64_t nbytes);
+int nt_upload_fence(void);
+int nt_host_register(void *ptr, int64_t nbytes);   /* pin caller-owned host memory (cudaHostRegister) */
+int nt_host_unregister(void *ptr);
 
 /* ------------------------------------------------------------------ factories (src/cpp/factory.cu:35-83) */
 int nt_zeros(int64_t n, int dtype, int device, nt_storage **out);

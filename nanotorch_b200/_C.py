@@ -557,6 +557,59 @@ def comm_destroy() -> None:
     _check(_lib.nt_comm_destroy())
 
 
+class Event:
+    """CUDA event on the library's compute stream."""
+
+    def __init__(self):
+        h = C.c_void_p()
+        _check(_lib.nt_event_create(C.byref(h)))
+        self._h = h.value
+
+    def record(self) -> "Event":
+        _check(_lib.nt_event_record(C.c_void_p(self._h)))
+        return self
+
+    def elapsed_ms(self, stop: "Event") -> float:
+        ms = C.c_float(0)
+        _check(_lib.nt_event_elapsed_ms(C.c_void_p(self._h), C.c_void_p(stop._h), C.byref(ms)))
+        return ms.value
+
+    def __del__(self):
+        h = getattr(self, "_h", None)
+        if h:
+            try:
+                _lib.nt_event_destroy(C.c_void_p(h))
+            except Exception:
+                pass
+            self._h = None
+
+
+def matmul_profile_enable(on: bool) -> None:
+    _check(_lib.nt_matmul_profile_enable(1 if on else 0))
+
+
+def matmul_profile_read() -> tuple[float, int]:
+    total, n = C.c_double(0), C.c_int64(0)
+    _check(_lib.nt_matmul_profile_read(C.byref(total), C.byref(n)))
+    return total.value, n.value
+
+
+def upload_async(s: Storage, host_ptr: int, nbytes: int) -> None:
+    _check(_lib.nt_storage_upload_async(C.c_void_p(s._h), C.c_void_p(host_ptr), C.c_int64(nbytes)))
+
+
+def upload_fence() -> None:
+    _check(_lib.nt_upload_fence())
+
+
+def host_register(ptr: int, nbytes: int) -> None:
+    _check(_lib.nt_host_register(C.c_void_p(ptr), C.c_int64(nbytes)))
+
+
+def host_unregister(ptr: int) -> None:
+    _check(_lib.nt_host_unregister(C.c_void_p(ptr)))
+
+
 def exported_symbols() -> list[str]:
     """Every symbol declared in include/nt_b200.h that this library must export."""
     import re

@@ -604,6 +604,11 @@ ALL_OPS_ = [AddOp, ExpOp, ExpandOp, LogOp, MatmulOp, MeanOp, MulOp, NegOp, PowOp
 
 # =============================================================================================
 # backward pass
+# id(leaf tensor) -> callable(leaf): called right after the leaf's gradient has been written (used by
+# the data-parallel trainer to start that parameter's all-reduce while backward continues).
+leaf_grad_hooks: dict[int, Any] = {}
+
+
 def run_backward(root: Tensor) -> None:
     """Reverse-topological sweep from `root`, whose ``_grad`` holds the seed.
 
@@ -626,14 +631,19 @@ def run_backward(root: Tensor) -> None:
         for inp in node.grad_fn.inputs:
             if isinstance(inp, Tensor) and inp.requires_grad and inp.grad_fn is not None and id(inp) not in seen:
                 stack.append((inp, False))
-    for node in reversed(order):
-        fn = node.grad_fn
-        if node._grad is None:
-            raise RuntimeError("f_x.grad is None.")
-        tensor_inputs = [a for a in fn.inputs if isinstance(a, Tensor)]
-        grads = fn.backward(node._grad)
-        for x, gx in zip(tensor_inputs, grads):
-            if gx is None or not x.requires_grad:
-                continue
-            x._grad = gx if x._grad is None else x._grad + gx
-        node._grad = None
+    with no_grad():  # gradients are values, not graph nodes
+        for node in reversed(order):
+            fn = node.grad_fn
+            if node._grad is None:
+                raise RuntimeError("f_x.grad is None.")
+            tensor_inputs = [a for a in fn.inputs if isinstance(a, Tensor)]
+            grads = fn.backward(node._grad)
+            for x, gx in zip(tensor_inputs, grads):
+                if gx is None or not x.requires_grad:
+                    continue
+                x._grad = gx if x._grad is None else x._grad + gx
+                if x.grad_fn is None and leaf_grad_hooks:
+                    hook = leaf_grad_hooks.get(id(x))
+                    if hook is not None:
+                        hook(x)
+            node._grad = None

@@ -99,6 +99,9 @@ template <class F> auto dispatch_float(int dt, F &&f) {
 cudaStream_t stream();       // the one compute stream (non-blocking)
 cudaStream_t comm_stream();  // collectives
 void count_launch(uint64_t n = 1);
+// matmul kernels call these around their launches (no-ops unless profiling is enabled)
+void matmul_profile_begin();
+void matmul_profile_end();
 bool cuda_ok();              // a device is present and usable
 int sm_count();
 

@@ -21,6 +21,11 @@ struct Runtime {
   int sms = 148;
   cudaStream_t compute = nullptr;
   cudaStream_t comm = nullptr;
+  cudaStream_t copy = nullptr;
+  cudaEvent_t copy_gate = nullptr, copy_done = nullptr;
+  bool mm_profile = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> mm_events;
+  std::vector<cudaEvent_t> event_pool;
   std::map<size_t, std::vector<void *>> dev_cache;
   std::map<size_t, std::vector<void *>> pin_cache;
   uint64_t bytes_reserved = 0, bytes_in_use = 0, n_malloc = 0;
@@ -53,6 +58,9 @@ static void ensure_streams_locked(Runtime &r) {
   NT_CUDA_CHECK(cudaSetDevice(r.device));
   NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.compute, cudaStreamNonBlocking));
   NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.comm, cudaStreamNonBlocking));
+  NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.copy, cudaStreamNonBlocking));
+  NT_CUDA_CHECK(cudaEventCreateWithFlags(&r.copy_gate, cudaEventDisableTiming));
+  NT_CUDA_CHECK(cudaEventCreateWithFlags(&r.copy_done, cudaEventDisableTiming));
   cudaDeviceProp prop;
   NT_CUDA_CHECK(cudaGetDeviceProperties(&prop, r.device));
   r.sms = prop.multiProcessorCount;
@@ -83,6 +91,29 @@ int sm_count() {
   return r.sms;
 }
 void count_launch(uint64_t n) { rt().launches.fetch_add(n, std::memory_order_relaxed); }
+
+static cudaEvent_t pooled_event(Runtime &r) {
+  if (!r.event_pool.empty()) {
+    cudaEvent_t e = r.event_pool.back();
+    r.event_pool.pop_back();
+    return e;
+  }
+  cudaEvent_t e;
+  NT_CUDA_CHECK(cudaEventCreate(&e));
+  return e;
+}
+void matmul_profile_begin() {
+  Runtime &r = rt();
+  if (!r.mm_profile) return;
+  cudaEvent_t a = pooled_event(r), b = pooled_event(r);
+  NT_CUDA_CHECK(cudaEventRecord(a, r.compute));
+  r.mm_events.emplace_back(a, b);
+}
+void matmul_profile_end() {
+  Runtime &r = rt();
+  if (!r.mm_profile || r.mm_events.empty()) return;
+  NT_CUDA_CHECK(cudaEventRecord(r.mm_events.back().second, r.compute));
+}
 
 static size_t round_block(size_t nbytes) {
   if (nbytes == 0) nbytes = 1;
@@ -349,6 +380,7 @@ int nt_cuda_sync(void) {
   if (cuda_ok()) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream()));
     NT_CUDA_CHECK(cudaStreamSynchronize(comm_stream()));
+    NT_CUDA_CHECK(cudaStreamSynchronize(rt().copy));
   }
   NT_API_END
 }
@@ -409,6 +441,89 @@ int nt_allocator_trim(void) {
   std::lock_guard<std::mutex> lk(r.mu);
   if (r.compute) NT_CUDA_CHECK(cudaStreamSynchronize(r.compute));
   trim_locked(r);
+  NT_API_END
+}
+
+// ---------------------------------------------------------------- events, profiling
+int nt_event_create(void **event) {
+  NT_API_BEGIN
+  stream();
+  cudaEvent_t e;
+  NT_CUDA_CHECK(cudaEventCreate(&e));
+  *event = e;
+  NT_API_END
+}
+int nt_event_record(void *event) {
+  NT_API_BEGIN
+  NT_CUDA_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(event), stream()));
+  NT_API_END
+}
+int nt_event_elapsed_ms(void *start, void *stop, float *ms) {
+  NT_API_BEGIN
+  NT_CUDA_CHECK(cudaEventSynchronize(static_cast<cudaEvent_t>(stop)));
+  NT_CUDA_CHECK(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(stop)));
+  NT_API_END
+}
+int nt_event_destroy(void *event) {
+  NT_API_BEGIN
+  if (event) NT_CUDA_CHECK(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  NT_API_END
+}
+int nt_matmul_profile_enable(int on) {
+  NT_API_BEGIN
+  stream();
+  rt().mm_profile = on != 0;
+  NT_API_END
+}
+int nt_matmul_profile_read(double *total_ms, int64_t *launches) {
+  NT_API_BEGIN
+  Runtime &r = rt();
+  double total = 0.0;
+  int64_t n = 0;
+  for (auto &pr : r.mm_events) {
+    float ms = 0.f;
+    NT_CUDA_CHECK(cudaEventSynchronize(pr.second));
+    NT_CUDA_CHECK(cudaEventElapsedTime(&ms, pr.first, pr.second));
+    total += ms;
+    ++n;
+    r.event_pool.push_back(pr.first);
+    r.event_pool.push_back(pr.second);
+  }
+  r.mm_events.clear();
+  *total_ms = total;
+  *launches = n;
+  NT_API_END
+}
+
+int nt_storage_upload_async(nt_storage *dst, const void *host_src, int64_t nbytes) {
+  NT_API_BEGIN
+  if (dst->device != NT_CUDA) fail_runtime("nt_storage_upload_async: destination must be a Cuda storage.");
+  if (nbytes < 0 || size_t(nbytes) > size_t(dst->n) * dtype_itemsize(dst->dtype))
+    fail_runtime("nt_storage_upload_async: byte count exceeds the storage.");
+  cudaStream_t st = stream();
+  Runtime &r = rt();
+  NT_CUDA_CHECK(cudaEventRecord(r.copy_gate, st));
+  NT_CUDA_CHECK(cudaStreamWaitEvent(r.copy, r.copy_gate, 0));
+  if (nbytes) NT_CUDA_CHECK(cudaMemcpyAsync(dst->data, host_src, size_t(nbytes), cudaMemcpyHostToDevice, r.copy));
+  NT_API_END
+}
+int nt_upload_fence(void) {
+  NT_API_BEGIN
+  cudaStream_t st = stream();
+  Runtime &r = rt();
+  NT_CUDA_CHECK(cudaEventRecord(r.copy_done, r.copy));
+  NT_CUDA_CHECK(cudaStreamWaitEvent(st, r.copy_done, 0));
+  NT_API_END
+}
+int nt_host_register(void *ptr, int64_t nbytes) {
+  NT_API_BEGIN
+  stream();
+  NT_CUDA_CHECK(cudaHostRegister(ptr, size_t(nbytes), cudaHostRegisterDefault));
+  NT_API_END
+}
+int nt_host_unregister(void *ptr) {
+  NT_API_BEGIN
+  NT_CUDA_CHECK(cudaHostUnregister(ptr));
   NT_API_END
 }
 

@@ -1,0 +1,250 @@
+"""Generates tests/golden/*.npz by running the REFERENCE itself (its Python package on its own
+native module, CPU path) on seeded inputs.  Run where the reference checkout and oracle/_ref exist:
+
+    make -C oracle ref                      # builds oracle/_ref/_C*.so from the reference sources
+    python tests/golden/make_golden.py --ref /root/reference
+
+The reference package is imported from a scratch directory that only holds symlinks to the
+reference's .py files plus the built native module; nothing is copied into this repository except
+the numeric inputs/outputs written to the .npz files.  The fixtures pin oracle/nt_oracle.c and
+oracle/oracle.py (tests/test_oracle.py) and are the known answers of the GPU parity tests.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import tempfile
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+REPO = HERE.parent.parent
+
+
+def import_reference(ref: Path):
+    so = next((REPO / "oracle" / "_ref").glob("_C*.so"))
+    scratch = Path(tempfile.mkdtemp(prefix="ntref_"))
+    pkg = scratch / "nanotorch"
+    src = ref / "src" / "nanotorch"
+    for path in src.rglob("*.py"):
+        dst = pkg / path.relative_to(src)
+        dst.parent.mkdir(parents=True, exist_ok=True)
+        os.symlink(path, dst)
+    os.symlink(so, pkg / so.name)
+    sys.path.insert(0, str(scratch))
+    import nanotorch as nt  # noqa: E402
+
+    return nt
+
+
+def T(nt, a: np.ndarray, requires_grad: bool = False):
+    t = nt.Tensor(a.tolist(), dtype=nt.float32)
+    if a.ndim == 0:
+        t = nt.Tensor(float(a), dtype=nt.float32)
+    if requires_grad:
+        t.enable_grad()
+    return t
+
+
+def A(t) -> np.ndarray:
+    """reference tensor -> numpy float32/bool/int64 array"""
+    data = t.tolist()
+    kind = {"Bool": np.bool_, "Int32": np.int32, "Int64": np.int64, "Float32": np.float32, "Float64": np.float64}
+    return np.array(data, dtype=kind[t.dtype.name]).reshape(t.shape)
+
+
+def elementwise_cases(nt, out: dict):
+    rng = np.random.default_rng(100)
+    R, C = 33, 18
+    a = rng.uniform(-1, 1, (R, C)).astype(np.float32)
+    b = rng.uniform(-1, 1, (R, C)).astype(np.float32)
+    d = rng.uniform(0.5, 2, (R, C)).astype(np.float32)
+    v = rng.uniform(-1, 1, (C,)).astype(np.float32)
+    dv = rng.uniform(0.5, 2, (C,)).astype(np.float32)
+    bt = rng.uniform(-1, 1, (C, R)).astype(np.float32)
+    dt = rng.uniform(0.5, 2, (C, R)).astype(np.float32)
+    n = rng.standard_normal((R, C)).astype(np.float32)
+    p = rng.uniform(0.1, 10, (R, C)).astype(np.float32)
+    G = rng.standard_normal((R, C)).astype(np.float32)
+    for k, val in dict(a=a, b=b, d=d, v=v, dv=dv, bt=bt, dt=dt, n=n, p=p, G=G).items():
+        out[f"ew/in/{k}"] = val
+
+    ops = {"add": lambda x, y: x + y, "sub": lambda x, y: x - y, "mul": lambda x, y: x * y,
+           "div": lambda x, y: x / y}
+    for name, fn in ops.items():
+        for layout in ("contig", "bcast", "transposed"):
+            x = T(nt, a, True)
+            if layout == "contig":
+                y = T(nt, d if name == "div" else b, True)
+                yy = y
+            elif layout == "bcast":
+                y = T(nt, dv if name == "div" else v, True)
+                yy = y
+            else:
+                y = T(nt, dt if name == "div" else bt, True)
+                yy = y.T
+            res = fn(x, yy)
+            (res * T(nt, G)).sum().backward()
+            out[f"ew/{name}/{layout}/out"] = A(res)
+            out[f"ew/{name}/{layout}/gx"] = A(x.grad)
+            out[f"ew/{name}/{layout}/gy"] = A(y.grad)
+
+    unary = {"exp": (n, lambda x: x.exp()), "neg": (n, lambda x: -x), "relu": (n, lambda x: nt.relu(x)),
+             "tanh": (n, lambda x: nt.tanh(x)), "sigmoid": (n, lambda x: nt.sigmoid(x)),
+             "log": (p, lambda x: x.log()), "sqrt": (p, lambda x: nt.sqrt(x)),
+             "pow2": (a, lambda x: x ** 2.0), "pow3.7": (p, lambda x: x ** 3.7), "powm1": (p, lambda x: x ** -1.0)}
+    for name, (src, fn) in unary.items():
+        x = T(nt, src, True)
+        res = fn(x)
+        (res * T(nt, G)).sum().backward()
+        out[f"ew/{name}/out"] = A(res)
+        out[f"ew/{name}/gx"] = A(x.grad)
+    # special values
+    sp = np.array([0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, np.nan, 1e-40, -1e-40, 88.7, -104.0, 20.0, -20.0, 0.3,
+                   1e-30, 3.0e38], dtype=np.float32)
+    out["ew/special/in"] = sp
+    x = T(nt, sp)
+    with np.errstate(all="ignore"):
+        for name, fn in {"exp": lambda t: t.exp(), "relu": nt.relu, "tanh": nt.tanh, "sigmoid": nt.sigmoid,
+                         "neg": lambda t: -t, "pow2": lambda t: t ** 2.0}.items():
+            out[f"ew/special/{name}"] = A(fn(x))
+
+
+def reduction_cases(nt, out: dict):
+    rng = np.random.default_rng(200)
+    x = rng.standard_normal((5, 6, 7)).astype(np.float32)
+    out["red/in/x"] = x
+    for axes in [(0,), (1,), (2,), (0, 2), (1, 2), (0, 1, 2), None]:
+        for keepdim in (False, True):
+            for name in ("sum", "mean", "max", "min"):
+                t = T(nt, x, True)
+                res = getattr(t, name)(axes, keepdim)
+                key = f"red/{name}/{'all' if axes is None else ''.join(map(str, axes))}/{int(keepdim)}"
+                out[key + "/out"] = A(res)
+                res.sum().backward()
+                out[key + "/gx"] = A(t.grad)
+    # transposed view reduced along what was the contiguous dim
+    t = T(nt, x, True)
+    res = t.transpose(0, 2).sum((0,))
+    out["red/sum_transposed/out"] = A(res)
+    # ties: the integer-division quirk zeroes the whole gradient of a tied slice
+    tie = np.array([[1.0, 3.0, 3.0, 2.0], [4.0, 0.0, -1.0, 2.0]], dtype=np.float32)
+    out["red/tie/in"] = tie
+    t = T(nt, tie, True)
+    t.max((1,)).sum().backward()
+    out["red/tie/max_gx"] = A(t.grad)
+    t = T(nt, tie, True)
+    t.min((0,)).sum().backward()
+    out["red/tie/min_gx"] = A(t.grad)
+    y = rng.standard_normal((4, 1, 40)).astype(np.float32)
+    out["red/in/y"] = y
+    for name in ("sum", "mean", "max", "min"):
+        t = T(nt, y, True)
+        res = getattr(t, name)(-1)
+        out[f"red/y/{name}/out"] = A(res)
+        res.sum().backward()
+        out[f"red/y/{name}/gx"] = A(t.grad)
+
+
+def matmul_cases(nt, out: dict):
+    rng = np.random.default_rng(300)
+    shapes = {"2d": ((5, 7), (7, 3)), "batched": ((2, 3, 5, 4), (2, 3, 4, 6)), "bcast_batch": ((3, 5, 4), (4, 6)),
+              "vec_mat": ((7,), (7, 3)), "mat_vec": ((5, 7), (7,)), "vec_vec": ((7,), (7,)),
+              "odd": ((37, 19), (19, 10))}
+    for name, (sa, sb) in shapes.items():
+        a = rng.uniform(-1, 1, sa).astype(np.float32)
+        b = rng.uniform(-1, 1, sb).astype(np.float32)
+        ta, tb = T(nt, a, True), T(nt, b, True)
+        res = ta @ tb
+        g = rng.uniform(-1, 1, res.shape).astype(np.float32)
+        (res * T(nt, g)).sum().backward()
+        out[f"mm/{name}/a"], out[f"mm/{name}/b"], out[f"mm/{name}/g"] = a, b, g
+        out[f"mm/{name}/out"], out[f"mm/{name}/ga"], out[f"mm/{name}/gb"] = A(res), A(ta.grad), A(tb.grad)
+    # transposed operand views
+    a = rng.uniform(-1, 1, (7, 5)).astype(np.float32)
+    b = rng.uniform(-1, 1, (3, 7)).astype(np.float32)
+    out["mm/tt/a"], out["mm/tt/b"] = a, b
+    out["mm/tt/out"] = A(T(nt, a).T @ T(nt, b).T)
+
+
+def mlp_cases(nt, out: dict):
+    import nanotorch.nn as nn
+    from nanotorch.nn.optimizers import GradientDescent
+
+    # configuration 1: 784 -> 256 -> 10, ReLU, batch 256, seed 0, lr 0.01, 100 steps on one batch
+    nt.manual_seed(0)
+    model = nn.Sequential(nn.Linear(784, 256), nn.ReLU(), nn.Linear(256, 10))
+    X = np.random.default_rng(1).standard_normal((256, 784)).astype(np.float32)
+    Y = np.random.default_rng(2).standard_normal((256, 10)).astype(np.float32)
+    tX, tY = T(nt, X), T(nt, Y)
+    opt = GradientDescent(model.parameters(), lr=0.01)
+    out["mlp1/W1_head"] = A(model.parameters()[0])[0, :8]
+    losses = []
+    for _ in range(100):
+        loss = nt.mean((model(tX) - tY) ** 2)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        losses.append(loss.item())
+    out["mlp1/losses"] = np.array(losses, dtype=np.float32)
+    out["mlp1/W2_final"] = A(model.parameters()[2])
+    out["mlp1/b1_final"] = A(model.parameters()[1])
+
+    # a small tanh network in the shape of configuration 5 (Linear/Tanh x3, Linear)
+    nt.manual_seed(0)
+    dims = [24, 32, 32, 32, 16]
+    layers = []
+    for i in range(4):
+        layers.append(nn.Linear(dims[i], dims[i + 1]))
+        if i < 3:
+            layers.append(nn.Tanh())
+    model = nn.Sequential(*layers)
+    X = np.random.default_rng(40).standard_normal((64, 24)).astype(np.float32)
+    Y = np.random.default_rng(41).standard_normal((64, 16)).astype(np.float32)
+    out["mlp5s/X"], out["mlp5s/Y"] = X, Y
+    tX, tY = T(nt, X), T(nt, Y)
+    opt = GradientDescent(model.parameters(), lr=1e-3)
+    losses = []
+    for step in range(5):
+        loss = nt.mean((model(tX) - tY) ** 2)
+        opt.zero_grad()
+        loss.backward()
+        if step == 0:
+            for i, p in enumerate(model.parameters()):
+                out[f"mlp5s/grad0/{i}"] = A(p.grad)
+        opt.step()
+        losses.append(loss.item())
+    out["mlp5s/losses"] = np.array(losses, dtype=np.float32)
+    for i, p in enumerate(model.parameters()):
+        out[f"mlp5s/final/{i}"] = A(p)
+
+
+def rng_cases(nt, out: dict):
+    nt.manual_seed(42)
+    out["rng/seed42"] = A(nt.rand(16))
+    nt.manual_seed(0)
+    out["rng/seed0"] = A(nt.rand(16))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--ref", default="/root/reference")
+    args = ap.parse_args()
+    nt = import_reference(Path(args.ref))
+    out: dict[str, np.ndarray] = {}
+    with np.errstate(all="ignore"):
+        rng_cases(nt, out)
+        elementwise_cases(nt, out)
+        reduction_cases(nt, out)
+        matmul_cases(nt, out)
+        mlp_cases(nt, out)
+    np.savez_compressed(HERE / "reference_cpu.npz", **out)
+    size = (HERE / "reference_cpu.npz").stat().st_size
+    print(f"wrote {len(out)} arrays, {size / 1024:.0f} KiB")
+
+
+if __name__ == "__main__":
+    main()

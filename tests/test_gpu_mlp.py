@@ -1,0 +1,83 @@
+"""GPU parity of whole training steps against the reference's own runs (golden fixtures)."""
+
+import numpy as np
+import pytest
+
+from tests.util import assert_bit_exact, assert_scaled
+
+pytestmark = pytest.mark.gpu
+
+
+def build(nt, dims, act):
+    import nanotorch_b200.nn as nn
+
+    nt.manual_seed(0)
+    layers = []
+    for i in range(len(dims) - 1):
+        layers.append(nn.Linear(dims[i], dims[i + 1]))
+        if i < len(dims) - 2:
+            layers.append(act())
+    return nn.Sequential(*layers)
+
+
+@pytest.mark.parametrize("mode", [2, 0, 1])
+def test_configuration_1(nt, golden, mode):
+    """784 -> 256 -> 10, ReLU, MSE, batch 256, seed-0 Kaiming init, SGD lr 0.01, 100 steps."""
+    import nanotorch_b200.nn as nn
+
+    nt._C.set_matmul_mode(mode)
+    try:
+        model = build(nt, [784, 256, 10], nn.ReLU)
+        assert_bit_exact(model.parameters()[0].numpy()[0, :8], golden["mlp1/W1_head"], "seed-0 init")
+        X = nt.Tensor.from_numpy(np.random.default_rng(1).standard_normal((256, 784)).astype(np.float32), "cuda")
+        Y = nt.Tensor.from_numpy(np.random.default_rng(2).standard_normal((256, 10)).astype(np.float32), "cuda")
+        opt = nn.GradientDescent(model.parameters(), lr=0.01)
+        losses = []
+        for _ in range(100):
+            loss = nt.mean((model(X) - Y) ** 2)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            losses.append(loss)
+        got = np.array([l.numpy() for l in losses], np.float32).reshape(-1)
+    finally:
+        nt._C.set_matmul_mode(1)
+    want = golden["mlp1/losses"]
+    rel = np.abs(got - want) / want
+    print(f"mode {mode}: loss[0] {got[0]:.7f} (ref {want[0]:.7f}), loss[99] {got[99]:.7f} (ref {want[99]:.7f}), "
+          f"max rel diff {rel.max():.2e}")
+    assert rel.max() < 1e-4
+    assert_scaled(model.parameters()[2].numpy(), golden["mlp1/W2_final"], np.abs(golden["mlp1/W2_final"]).max(), 1e-4, "W2")
+    assert_scaled(model.parameters()[1].numpy(), golden["mlp1/b1_final"], np.abs(golden["mlp1/b1_final"]).max() + 1e-3, 1e-3, "b1")
+
+
+@pytest.mark.parametrize("mode", [2, 1])
+def test_tanh_network_gradients(nt, golden, mode):
+    """Linear/Tanh x3 + Linear (the shape of the data-parallel configuration, small): first-step
+    gradients of every parameter and the 5-step loss curve."""
+    import nanotorch_b200.nn as nn
+
+    nt._C.set_matmul_mode(mode)
+    try:
+        model = build(nt, [24, 32, 32, 32, 16], nn.Tanh)
+        X = nt.Tensor.from_numpy(golden["mlp5s/X"], "cuda")
+        Y = nt.Tensor.from_numpy(golden["mlp5s/Y"], "cuda")
+        opt = nn.GradientDescent(model.parameters(), lr=1e-3)
+        losses = []
+        for step in range(5):
+            loss = nt.mean((model(X) - Y) ** 2)
+            opt.zero_grad()
+            loss.backward()
+            if step == 0:
+                for i, p in enumerate(model.parameters()):
+                    want = golden[f"mlp5s/grad0/{i}"]
+                    assert_scaled(p.grad.numpy(), want, np.abs(want).max(), 1e-4, f"grad of parameter {i}")
+            opt.step()
+            losses.append(float(loss.numpy()))
+    finally:
+        nt._C.set_matmul_mode(1)
+    want = golden["mlp5s/losses"]
+    assert np.abs(np.array(losses) - want).max() / want.max() < 1e-5
+    for i, p in enumerate(model.parameters()):
+        w = golden[f"mlp5s/final/{i}"]
+        assert_scaled(p.numpy(), w, np.abs(w).max() + 1e-6, 1e-4, f"parameter {i} after 5 steps")
