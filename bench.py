@@ -207,103 +207,192 @@ def pinned(nt, array: np.ndarray):
 
 
 def time_ops(nt, peaks: dict) -> dict:
-    """Per-op sweep of the elementwise / reduction / matmul configurations at N = 1."""
+    """Per-op sweep of the elementwise / reduction / matmul configurations at N = 1.
+
+    HBM-bound ops are timed as `iters` back-to-back launches through the `_C` boundary (prebuilt
+    views, so the host issues faster than the device drains) between one pair of events.  Launch i
+    works on buffer set i mod n, with n chosen so that the sets together exceed 4x the L2 (inputs and
+    the last n outputs are all distinct allocations): nothing a launch touches is still cached from
+    the previous pass over the same set.  Matmuls (milliseconds each) are timed one launch at a time
+    with the L2 flushed by a 512 MB fill in between.
+    """
     _C = nt._C
-    dev = lambda a: nt.Tensor.from_numpy(a, "cuda")  # noqa: E731
+    F32, CUDA = nt.float32, nt.Device.Cuda
     r = np.random.default_rng
     hbm = peaks["hbm_gbs"]
     out: dict = {}
+    L2_BYTES = 126 * 1024 * 1024
 
-    def flush():
-        _C.zeros(128 * 1024 * 1024, nt.float32, nt.Device.Cuda)  # 512 MB written: larger than L2
+    def dev(a):
+        return nt.Tensor.from_numpy(a, "cuda")
 
-    def timed(fn, iters=10, warm=3):
-        for _ in range(warm):
-            fn()
-        ms = []
-        for _ in range(iters):
-            flush()
-            e0 = _C.Event().record()
-            fn()
-            e1 = _C.Event().record()
-            ms.append(e0.elapsed_ms(e1))
-        return statistics.median(ms)
+    def copies(t, n):
+        return [t] + [t.clone() for _ in range(n - 1)]
 
-    N = 4096
-    a, b = dev(r(10).uniform(-1, 1, (N, N)).astype(np.float32)), dev(r(11).uniform(-1, 1, (N, N)).astype(np.float32))
-    d = dev(r(12).uniform(0.5, 2, (N, N)).astype(np.float32))
-    v, dv = dev(r(13).uniform(-1, 1, (N,)).astype(np.float32)), dev(r(17).uniform(0.5, 2, (N,)).astype(np.float32))
-    n_, p_ = dev(r(14).standard_normal((N, N)).astype(np.float32)), dev(r(15).uniform(0.1, 10, (N, N)).astype(np.float32))
-    G = dev(r(16).standard_normal((N, N)).astype(np.float32))
-    numel = N * N
+    def stream_time(calls, iters=40):
+        n = len(calls)
+        ring = [c() for c in calls]
+        ring = [c() for c in calls]
+        _C.cuda_sync()
+        e0 = _C.Event().record()
+        for i in range(iters):
+            ring[i % n] = calls[i % n]()
+        e1 = _C.Event().record()
+        ms = e0.elapsed_ms(e1) / iters
+        del ring
+        return ms
 
     def record(name, ms, nbytes):
         gbs = nbytes / ms / 1e6
         out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "frac_of_measured_hbm": round(gbs / hbm, 3)}
 
-    with nt.no_grad():
-        for name, fn in {"add": lambda x, y: x + y, "sub": lambda x, y: x - y, "mul": lambda x, y: x * y,
-                         "truediv": lambda x, y: x / y}.items():
-            y, yv = (d, dv) if name == "truediv" else (b, v)
-            record(f"{name}.contiguous", timed(lambda: fn(a, y)), 3 * numel * 4)
-            record(f"{name}.broadcast_row", timed(lambda: fn(a, yv)), (2 * numel + N) * 4)
-            yt = y.T
-            record(f"{name}.transposed", timed(lambda: fn(a, yt)), 3 * numel * 4)
-        for name, fn, src in [("pow2", lambda x: x ** 2.0, a), ("exp", lambda x: x.exp(), n_), ("neg", lambda x: -x, n_),
-                              ("relu", nt.relu, n_), ("tanh", nt.tanh, n_), ("sigmoid", nt.sigmoid, n_),
-                              ("log", lambda x: x.log(), p_), ("sqrt", nt.sqrt, p_)]:
-            record(f"{name}.forward", timed(lambda: fn(src)), 2 * numel * 4)
-        t_out = nt.tanh(n_)
-        for name, kern, saved in [("relu", _C.relu_backward, nt.relu(n_)), ("tanh", _C.tanh_backward, t_out),
-                                  ("sigmoid", _C.sigmoid_backward, nt.sigmoid(n_)), ("exp", _C.exp_backward, n_.exp()),
-                                  ("log", _C.log_backward, p_), ("sqrt", _C.sqrt_backward, nt.sqrt(p_))]:
-            gv, sv = G._C_view, saved._C_view
-            record(f"{name}.backward", timed(lambda: kern(gv, sv)), 3 * numel * 4)
-        record("pow2.backward", timed(lambda: _C.pow_backward(G._C_view, a._C_view, 2.0)), 3 * numel * 4)
-        del a, b, d, n_, p_, G, t_out
+    def nsets(nbytes):
+        return max(3, -(-4 * L2_BYTES // nbytes))
 
+    N = 4096
+    numel = N * N
+    host = {"a": r(10).uniform(-1, 1, (N, N)), "b": r(11).uniform(-1, 1, (N, N)), "d": r(12).uniform(0.5, 2, (N, N)),
+            "n": r(14).standard_normal((N, N)), "p": r(15).uniform(0.1, 10, (N, N)), "G": r(16).standard_normal((N, N))}
+    v_ = dev(r(13).uniform(-1, 1, (N,)).astype(np.float32))
+    dv_ = dev(r(17).uniform(0.5, 2, (N,)).astype(np.float32))
+
+    with nt.no_grad():
+        # ---- binary forward: contiguous, row broadcast, transposed operand
+        k = nsets(3 * numel * 4)
+        A = copies(dev(host["a"].astype(np.float32)), k)
+        B = copies(dev(host["b"].astype(np.float32)), k)
+        D = copies(dev(host["d"].astype(np.float32)), k)
+        for name, kern in (("add", _C.add), ("sub", _C.subtract), ("mul", _C.multiply), ("truediv", _C.divide)):
+            Y, yv = (D, dv_) if name == "truediv" else (B, v_)
+            va = [t._C_view for t in A]
+            record(f"{name}.contiguous", stream_time([lambda i=i: kern(va[i], Y[i]._C_view) for i in range(k)]),
+                   3 * numel * 4)
+            vrow = yv.expand(N, N)._C_view
+            record(f"{name}.broadcast_row", stream_time([lambda i=i: kern(va[i], vrow) for i in range(k)]),
+                   (2 * numel + N) * 4)
+            vt = [t.T._C_view for t in Y]
+            record(f"{name}.transposed", stream_time([lambda i=i: kern(va[i], vt[i]) for i in range(k)]), 3 * numel * 4)
+        del B, D
+        # ---- unary forward
+        k = nsets(2 * numel * 4)
+        Nn = copies(dev(host["n"].astype(np.float32)), k)
+        Pp = copies(dev(host["p"].astype(np.float32)), k)
+        A = A[:k] + [A[0].clone() for _ in range(max(0, k - len(A)))]
+        for name, kern, src in (("pow2", lambda v: _C.pow(v, 2.0), A), ("exp", _C.exp, Nn), ("neg", _C.neg, Nn),
+                                ("relu", _C.relu, Nn), ("tanh", _C.tanh, Nn), ("sigmoid", _C.sigmoid, Nn),
+                                ("log", _C.log, Pp), ("sqrt", _C.sqrt, Pp)):
+            views = [t._C_view for t in src]
+            record(f"{name}.forward", stream_time([lambda i=i: kern(views[i]) for i in range(k)]), 2 * numel * 4)
+        # ---- fused backward kernels: upstream gradient + saved tensor -> input gradient
+        k = nsets(3 * numel * 4)
+        G = copies(dev(host["G"].astype(np.float32)), k)
+        gv = [t._C_view for t in G]
+        saved = {"relu": [nt.relu(t) for t in Nn[:k]], "tanh": [nt.tanh(t) for t in Nn[:k]],
+                 "sigmoid": [nt.sigmoid(t) for t in Nn[:k]], "exp": [t.exp() for t in Nn[:k]], "log": Pp[:k],
+                 "sqrt": [nt.sqrt(t) for t in Pp[:k]]}
+        kernels = {"relu": _C.relu_backward, "tanh": _C.tanh_backward, "sigmoid": _C.sigmoid_backward,
+                   "exp": _C.exp_backward, "log": _C.log_backward, "sqrt": _C.sqrt_backward}
+        for name, kern in kernels.items():
+            sv = [t._C_view for t in saved[name]]
+            record(f"{name}.backward", stream_time([lambda i=i: kern(gv[i], sv[i]) for i in range(k)]), 3 * numel * 4)
+            saved[name] = None
+        av = [t._C_view for t in A[:k]]
+        record("pow2.backward", stream_time([lambda i=i: _C.pow_backward(gv[i], av[i], 2.0) for i in range(k)]),
+               3 * numel * 4)
+        del A, Nn, Pp, G, saved, gv, av
+
+        # ---- reductions
         M = 8192
-        x = dev(r(20).standard_normal((M, M)).astype(np.float32))
+        k = 3
+        X = copies(dev(r(20).standard_normal((M, M)).astype(np.float32)), k)
+        xv = [t._C_view for t in X]
         y3 = dev(r(21).standard_normal((64, 1, 16384)).astype(np.float32))
-        for op in ("sum", "mean", "max", "min"):
-            for label, axes in (("dim0", (0,)), ("dim1", (1,)), ("full", None)):
-                record(f"{op}.{label}", timed(lambda: getattr(x, op)(axes)), M * M * 4)
-            record(f"{op}.[64,1,16384].last", timed(lambda: getattr(y3, op)(-1), iters=20), y3.numel * 4)
+        count = {(0,): M, (1,): M, (0, 1): M * M}
+        for label, axes in (("dim0", (0,)), ("dim1", (1,)), ("full", (0, 1))):
+            ax = list(axes)
+            record(f"sum.{label}", stream_time([lambda i=i: _C.sum(xv[i], ax, F32) for i in range(k)]), M * M * 4)
+            record(f"max.{label}", stream_time([lambda i=i: _C.max(xv[i], ax) for i in range(k)]), M * M * 4)
+            record(f"min.{label}", stream_time([lambda i=i: _C.min(xv[i], ax) for i in range(k)]), M * M * 4)
+            n_out = M * M // count[axes]
+            denom = _C.TensorView(_C.full(1, float(count[axes]), F32, CUDA), (n_out,), (0,), 0)
+
+            def mean_call(i):  # MeanOp.forward: sum, then a true division by the count
+                s_ = _C.sum(xv[i], ax, F32)
+                return _C.divide(_C.TensorView(s_, (n_out,), (1,), 0), denom)
+
+            record(f"mean.{label}", stream_time([lambda i=i: mean_call(i) for i in range(k)]), M * M * 4)
+        y3v = y3._C_view
+        for op, kern in (("sum", lambda v: _C.sum(v, [2], F32)), ("max", lambda v: _C.max(v, [2])),
+                         ("min", lambda v: _C.min(v, [2]))):
+            record(f"{op}.[64,1,16384].last", stream_time([lambda: kern(y3v)] * 3, iters=100), y3.numel * 4)
+        # backward: the reference's sum backward is a stride-0 view (0 bytes); the materialised broadcast
+        # and the mean / max backward kernels are what moves data
         ones_row = dev(np.ones((M,), np.float32))
-        record("sum.backward_materialised", timed(lambda: ones_row.expand(M, M).clone()), M * M * 4)
-        m1 = x.max((1,))
-        g_full = ones_row.reshape(M, 1).expand(M, M)
-        m_full = m1.reshape(M, 1).expand(M, M)
-        record("max.backward", timed(lambda: _C.extremum_backward(g_full._C_view, x._C_view, m_full._C_view, [1])),
-               2 * M * M * 4)
-        del x, y3, m1, g_full, m_full
+        row_view = ones_row.expand(M, M)._C_view
+        record("sum.backward_materialised", stream_time([lambda: _C.clone_contiguous_view_from(row_view)] * 3), M * M * 4)
+        denom_full = _C.TensorView(_C.full(1, float(M), F32, CUDA), (M, M), (0, 0), 0)
+        record("mean.backward", stream_time([lambda: _C.divide(row_view, denom_full)] * 3), M * M * 4)
+        m1 = [t.max((1,)) for t in X]
+        g_full = ones_row.reshape(M, 1).expand(M, M)._C_view
+        m_full = [m.reshape(M, 1).expand(M, M)._C_view for m in m1]
+        record("max.backward", stream_time([lambda i=i: _C.extremum_backward(g_full, xv[i], m_full[i], [1])
+                                            for i in range(k)], iters=20), 2 * M * M * 4)
+        del X, xv, m1, m_full
+
+        # ---- matmul
+        def flush():
+            _C.zeros(128 * 1024 * 1024, F32, CUDA)  # 512 MB written: larger than L2
+
+        def timed(fn, iters, warm=2):
+            for _ in range(warm):
+                fn()
+            ms = []
+            for _ in range(iters):
+                flush()
+                e0 = _C.Event().record()
+                fn()
+                e1 = _C.Event().record()
+                ms.append(e0.elapsed_ms(e1))
+            return statistics.median(ms)
 
         tf32_peak = peaks["bf16_tflops"] / 2
-        for label, (m, k, n, bt) in {"4096x4096x4096": (4096, 4096, 4096, 1), "8192x1024x4096": (8192, 1024, 4096, 1),
-                                     "32x512x512x512": (512, 512, 512, 32)}.items():
-            shape_a = (bt, m, k) if bt > 1 else (m, k)
-            shape_b = (bt, k, n) if bt > 1 else (k, n)
+        for label, (m, kk, n, bt) in {"4096x4096x4096": (4096, 4096, 4096, 1), "8192x1024x4096": (8192, 1024, 4096, 1),
+                                      "32x512x512x512": (512, 512, 512, 32)}.items():
+            shape_a = (bt, m, kk) if bt > 1 else (m, kk)
+            shape_b = (bt, kk, n) if bt > 1 else (kk, n)
             shape_c = (bt, m, n) if bt > 1 else (m, n)
-            A = dev(r(30).uniform(-1, 1, shape_a).astype(np.float32))
-            B = dev(r(31).uniform(-1, 1, shape_b).astype(np.float32))
+            Am = dev(r(30).uniform(-1, 1, shape_a).astype(np.float32))
+            Bm = dev(r(31).uniform(-1, 1, shape_b).astype(np.float32))
             Gc = dev(r(32).uniform(-1, 1, shape_c).astype(np.float32))
-            flops = 2.0 * bt * m * n * k
+            flops = 2.0 * bt * m * n * kk
+            va, vb, vg = Am._C_view, Bm._C_view, Gc._C_view
+            vat, vbt = Am.transpose(-2, -1)._C_view, Bm.transpose(-2, -1)._C_view
             for mode, mname in ((1, "3xtf32"), (0, "fp32_simt")):
                 _C.set_matmul_mode(mode)
                 try:
                     res = {}
-                    for which, fn in (("forward", lambda: A @ B), ("grad_a", lambda: Gc @ B.transpose(-2, -1)),
-                                      ("grad_b", lambda: A.transpose(-2, -1) @ Gc)):
-                        ms = timed(fn, iters=5 if mode == 0 else 10, warm=2)
+                    for which, fn in (("forward", lambda: _C.matmul(va, vb)), ("grad_a", lambda: _C.matmul(vg, vbt)),
+                                      ("grad_b", lambda: _C.matmul(vat, vg))):
+                        _C.matmul_profile_enable(True)
+                        ms = timed(fn, iters=5 if mode == 0 else 10)
+                        total, launches = _C.matmul_profile_read()
+                        _C.matmul_profile_enable(False)
                         res[which] = {"ms": round(ms, 4), "TFLOP/s": round(flops / ms / 1e9, 2)}
                         if mode == 1:
-                            res[which]["tensor_pipe_frac_of_tf32_peak"] = round(3 * flops / ms / 1e9 / tf32_peak, 3)
+                            kms = total / max(launches, 1)
+                            res[which]["gemm_kernel_ms"] = round(kms, 4)
+                            res[which]["tensor_TFLOP/s_3_products"] = round(3 * flops / ms / 1e9, 1)
+                            res[which]["tensor_frac_of_tf32_peak"] = round(3 * flops / ms / 1e9 / tf32_peak, 3)
+                            res[which]["gemm_kernel_tensor_frac_of_tf32_peak"] = round(3 * flops / kms / 1e9 / tf32_peak, 3)
                     out[f"matmul.{label}.{mname}"] = res
                 finally:
                     _C.set_matmul_mode(1)
-            del A, B, Gc
-    out["_notes"] = ("L2 flushed between timed iterations by a 512 MB fill; median of 10 device-timed launches; "
-                     "bytes are the reference's mem_bytes() accounting; tf32 peak taken as measured bf16 / 2")
+            del Am, Bm, Gc
+    out["_notes"] = ("HBM-bound ops: back-to-back launches through the _C boundary over rotating buffer sets larger "
+                     "than 4x L2, one event pair around 40 launches; bytes are the reference's mem_bytes() accounting "
+                     "(sum/max/min count the input only); matmul: L2 flushed by a 512 MB fill between single timed "
+                     "launches, `ms` includes the operand split kernels, gemm_kernel_ms is the tcgen05 kernel alone; "
+                     "tf32 peak taken as measured burst bf16 / 2")
     return out
 
 

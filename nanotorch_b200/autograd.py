@@ -286,13 +286,16 @@ class MatmulOp(Function):
         b = x2
         if b.ndim == 1 and self._shape2[-2:] == (b.shape[0], 1):
             b = b.reshape(b.shape[0], 1)
+        b_orig = b
         b = b.expand(*self._shape2)
         g = g.reshape(*broadcast_shapes(self._shape1[:-2], self._shape2[:-2]), self._shape1[-2], self._shape2[-1])
         g1 = g2 = None
         if _need(self, 0):
             g1 = unbroadcast(g @ b.transpose(-2, -1), x1.shape).reshape(*x1.shape)
         if _need(self, 1):
-            g2 = unbroadcast(a.transpose(-2, -1) @ g, x2.shape).reshape(*x2.shape)
+            # unbroadcast against the 2-D form of a 1-D right operand, then hand the gradient back in
+            # the operand's own shape (the reference returns it as (k, 1); the values are the same)
+            g2 = unbroadcast(a.transpose(-2, -1) @ g, b_orig.shape).reshape(*x2.shape)
         return g1, g2
 
     @classmethod

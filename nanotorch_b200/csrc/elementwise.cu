@@ -2,6 +2,7 @@
 // the fused backward kernels and the SGD update.  All arithmetic is compiled with FMA contraction
 // off, so every functor rounds exactly where the reference's separate kernels round.
 #include "elementwise.cuh"
+#include "tanh_exact.h"
 
 namespace ntb {
 
@@ -109,102 +110,12 @@ template <class T> struct SigmoidF {
   }
 };
 
-// ---- tanh, fp32: the fdlibm algorithm (expm1-based), which is what the host libm the reference's
-// CPU path resolves to computes; only IEEE +,-,*,/ in fp32, so the device result is identical bit
-// for bit to that libm's.  Verified on the host against glibc 2.39 over 1.1e8 arguments.
-__device__ __forceinline__ float expm1_f32(float x) {
-  const float one = 1.0f, huge = 1.0e+30f, tiny = 1.0e-30f, o_threshold = 8.8721679688e+01f,
-              ln2_hi = 6.9313812256e-01f, ln2_lo = 9.0580006145e-06f, invln2 = 1.4426950216e+00f,
-              Q1 = -3.3333335072e-02f, Q2 = 1.5873016091e-03f, Q3 = -7.9365076090e-05f,
-              Q4 = 4.0082177293e-06f, Q5 = -2.0109921195e-07f;
-  float y, hi, lo, c = 0.0f, t, e, hxs, hfx, r1;
-  int k;
-  unsigned hx = __float_as_uint(x);
-  const unsigned xsb = hx & 0x80000000u;
-  hx &= 0x7fffffffu;
-  if (hx >= 0x4195b844u) { // |x| >= 27 ln2
-    if (hx >= 0x42b17218u) {
-      if (hx > 0x7f800000u) return x + x;
-      if (hx == 0x7f800000u) return xsb == 0 ? x : -1.0f;
-      if (x > o_threshold) return huge * huge;
-    }
-    if (xsb != 0) {
-      if (x + tiny < 0.0f) return tiny - one;
-    }
-  }
-  if (hx > 0x3eb17218u) { // |x| > 0.5 ln2
-    if (hx < 0x3F851592u) { // |x| < 1.5 ln2
-      if (xsb == 0) { hi = x - ln2_hi; lo = ln2_lo; k = 1; }
-      else { hi = x + ln2_hi; lo = -ln2_lo; k = -1; }
-    } else {
-      k = __float2int_rz(invln2 * x + ((xsb == 0) ? 0.5f : -0.5f));
-      t = (float)k;
-      hi = x - t * ln2_hi;
-      lo = t * ln2_lo;
-    }
-    x = hi - lo;
-    c = (hi - x) - lo;
-  } else if (hx < 0x33000000u) { // |x| < 2^-25
-    t = huge + x;
-    return x - (t - (huge + x));
-  } else {
-    k = 0;
-  }
-  hfx = 0.5f * x;
-  hxs = x * hfx;
-  r1 = one + hxs * (Q1 + hxs * (Q2 + hxs * (Q3 + hxs * (Q4 + hxs * Q5))));
-  t = 3.0f - r1 * hfx;
-  e = hxs * ((r1 - t) / (6.0f - x * t));
-  if (k == 0) return x - (x * e - hxs);
-  e = (x * (e - c) - c);
-  e -= hxs;
-  if (k == -1) return 0.5f * (x - e) - 0.5f;
-  if (k == 1) {
-    if (x < -0.25f) return -2.0f * (e - (x + 0.5f));
-    return one + 2.0f * (x - e);
-  }
-  if (k <= -2 || k > 56) {
-    y = one - (e - x);
-    y = __uint_as_float(__float_as_uint(y) + ((unsigned)k << 23));
-    return y - one;
-  }
-  if (k < 23) {
-    t = __uint_as_float(0x3f800000u - (0x1000000u >> k));
-    y = t - (e - x);
-    y = __uint_as_float(__float_as_uint(y) + ((unsigned)k << 23));
-  } else {
-    t = __uint_as_float((unsigned)(0x7f - k) << 23);
-    y = x - (e + t);
-    y += one;
-    y = __uint_as_float(__float_as_uint(y) + ((unsigned)k << 23));
-  }
-  return y;
-}
-__device__ __forceinline__ float tanh_f32(float x) {
-  const float one = 1.0f, two = 2.0f, tiny = 1.0e-30f;
-  float t, z;
-  const unsigned jx = __float_as_uint(x), ix = jx & 0x7fffffffu;
-  if (ix >= 0x7f800000u) return ((int)jx >= 0) ? one / x + one : one / x - one;
-  if (ix < 0x41b00000u) { // |x| < 22
-    if (ix == 0) return x;
-    if (ix < 0x24000000u) return x * (one + x);
-    if (ix >= 0x3f800000u) {
-      t = expm1_f32(two * fabsf(x));
-      z = one - two / (t + two);
-    } else {
-      t = expm1_f32(-two * fabsf(x));
-      z = -t / (t + two);
-    }
-  } else {
-    z = one - tiny;
-  }
-  return ((int)jx >= 0) ? z : -z;
-}
+// ---- tanh, fp32: bit-for-bit the host libm's algorithm, see tanh_exact.h
 template <class T> struct TanhF {
   using in_t = T;
   using out_t = T;
   __device__ __forceinline__ T operator()(T a) const {
-    if constexpr (std::is_same_v<T, float>) return tanh_f32(a);
+    if constexpr (std::is_same_v<T, float>) return nt_tanh_f32(a);
     else return tanh(a);
   }
 };

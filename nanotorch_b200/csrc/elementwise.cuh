@@ -90,70 +90,94 @@ __global__ void __launch_bounds__(256) ew_contig(F f, typename F::out_t *out, co
 }
 
 // ---------------------------------------------------------------------------------------------
-// Strided kernel.  IDX is uint32_t when every extent and offset fits, else int64_t/uint64_t.
-template <class F, int NIN, int VEC, class IDX>
-__global__ void __launch_bounds__(256) ew_strided(F f, EwParams p) {
-  using TI = typename F::in_t;
-  using TO = typename F::out_t;
-  const int64_t nthreads_needed = p.numel / VEC;
-  int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (t >= nthreads_needed) return;
-  IDX lin = IDX(t) * VEC;
-  int64_t off[NIN + 1];
+// Strided kernel.  IDX is uint32_t when every extent and offset fits, else uint64_t.
+// VEC == 4: a thread owns UNROLL groups of 4 consecutive elements of the innermost dim (groups of
+// one block are interleaved so that a warp touches consecutive vectors); all loads are issued before
+// the first use.  VEC == 1: one element per thread, any dtype.
+template <class IDX, int NOPS>
+__device__ __forceinline__ void ew_offsets(const EwParams &p, IDX lin, int64_t (&off)[NOPS]) {
 #pragma unroll
-  for (int o = 0; o <= NIN; ++o) off[o] = 0;
+  for (int o = 0; o < NOPS; ++o) off[o] = 0;
   for (int d = p.ndim - 1; d >= 0; --d) {
     IDX ext = IDX(p.shape[d]);
     IDX q = lin / ext;
     IDX r = lin - q * ext;
     lin = q;
 #pragma unroll
-    for (int o = 0; o <= NIN; ++o) off[o] += int64_t(r) * p.strides[o][d];
+    for (int o = 0; o < NOPS; ++o) off[o] += int64_t(r) * p.strides[o][d];
   }
-  const TI *in[NIN];
-#pragma unroll
-  for (int o = 0; o < NIN; ++o) in[o] = static_cast<const TI *>(p.in[o]) + off[o + 1];
-  TO *out = static_cast<TO *>(p.out) + off[0];
+}
 
+template <class F, int NIN, int VEC, class IDX>
+__global__ void __launch_bounds__(256) ew_strided(F f, EwParams p) {
+  using TI = typename F::in_t;
+  using TO = typename F::out_t;
   if constexpr (VEC == 1) {
+    int64_t t = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= p.numel) return;
+    int64_t off[NIN + 1];
+    ew_offsets<IDX, NIN + 1>(p, IDX(t), off);
+    const TI *in[NIN];
+#pragma unroll
+    for (int o = 0; o < NIN; ++o) in[o] = static_cast<const TI *>(p.in[o]) + off[o + 1];
+    TO *out = static_cast<TO *>(p.out) + off[0];
     if constexpr (NIN == 1) *out = f(*in[0]);
     if constexpr (NIN == 2) *out = f(*in[0], *in[1]);
     if constexpr (NIN == 3) *out = f(*in[0], *in[1], *in[2]);
   } else {
     static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "vector path is for 4-byte types");
+    constexpr int UNROLL = 4;
+    const int64_t nvec = p.numel / VEC;
     const int last = p.ndim - 1;
-    TI v[NIN][4];
+    const int64_t base = (int64_t(blockIdx.x) * UNROLL) * blockDim.x + threadIdx.x;
+    TI v[UNROLL][NIN][4];
+    int64_t out_off[UNROLL];
 #pragma unroll
-    for (int o = 0; o < NIN; ++o) {
-      const int mode = p.vec_mode[o + 1];
-      if (mode == 1) {
-        float4 x = *reinterpret_cast<const float4 *>(in[o]);
-        const TI *px = reinterpret_cast<const TI *>(&x);
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t t = base + int64_t(u) * blockDim.x;
+      if (t >= nvec) continue;
+      int64_t off[NIN + 1];
+      ew_offsets<IDX, NIN + 1>(p, IDX(t) * VEC, off);
+      out_off[u] = off[0];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[o][e] = px[e];
-      } else if (mode == 2) {
-        TI x = *in[o];
+      for (int o = 0; o < NIN; ++o) {
+        const TI *src = static_cast<const TI *>(p.in[o]) + off[o + 1];
+        const int mode = p.vec_mode[o + 1];
+        if (mode == 1) {
+          float4 x = *reinterpret_cast<const float4 *>(src);
+          const TI *px = reinterpret_cast<const TI *>(&x);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[o][e] = x;
-      } else {
-        const int64_t s = p.strides[o + 1][last];
+          for (int e = 0; e < 4; ++e) v[u][o][e] = px[e];
+        } else if (mode == 2) {
+          TI x = *src;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[o][e] = in[o][e * s];
+          for (int e = 0; e < 4; ++e) v[u][o][e] = x;
+        } else {
+          const int64_t s = p.strides[o + 1][last];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v[u][o][e] = src[e * s];
+        }
       }
     }
-    TO r[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      if constexpr (NIN == 1) r[e] = f(v[0][e]);
-      if constexpr (NIN == 2) r[e] = f(v[0][e], v[1][e]);
-      if constexpr (NIN == 3) r[e] = f(v[0][e], v[1][e], v[2][e]);
-    }
-    if (p.vec_mode[0] == 1) {
-      *reinterpret_cast<float4 *>(out) = *reinterpret_cast<const float4 *>(r);
-    } else {
-      const int64_t s = p.strides[0][last];
+    for (int u = 0; u < UNROLL; ++u) {
+      const int64_t t = base + int64_t(u) * blockDim.x;
+      if (t >= nvec) continue;
+      TO r[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) out[e * s] = r[e];
+      for (int e = 0; e < 4; ++e) {
+        if constexpr (NIN == 1) r[e] = f(v[u][0][e]);
+        if constexpr (NIN == 2) r[e] = f(v[u][0][e], v[u][1][e]);
+        if constexpr (NIN == 3) r[e] = f(v[u][0][e], v[u][1][e], v[u][2][e]);
+      }
+      TO *out = static_cast<TO *>(p.out) + out_off[u];
+      if (p.vec_mode[0] == 1) {
+        __stcs(reinterpret_cast<float4 *>(out), *reinterpret_cast<const float4 *>(r));
+      } else {
+        const int64_t s = p.strides[0][last];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) out[e * s] = r[e];
+      }
     }
   }
 }
@@ -384,7 +408,7 @@ template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NI
   }
   if constexpr (VECTOR_TYPES) {
     if (vec4) {
-      int64_t blocks = ceil_div(it.numel / 4, 256);
+      int64_t blocks = ceil_div(it.numel / 4, 256 * 4);
       if (idx32)
         ew_strided<F, NIN, 4, uint32_t><<<unsigned(blocks), 256, 0, st>>>(f, p);
       else

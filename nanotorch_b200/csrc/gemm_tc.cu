@@ -1,7 +1,486 @@
+// fp32 GEMM on the Blackwell tensor cores with 3xTF32 split precision.
+//
+//   C[b][m][n] = sum_k A[b][m][k] * B[b][k][n],  every operand fp32, result within fp32 rounding of
+//   the exact product.
+//
+// Two kernels:
+//
+//  split_pack      reads one operand through its strided view (any strides; coalesced along
+//                  whichever matrix dim has unit stride, through a shared-memory transpose when that
+//                  is not k) and writes two K-major planes  hi = tf32(x),  lo = tf32(x - hi)
+//                  [plane][batch][rows][Kp], Kp = K rounded up to the k-block, zero padded.
+//                  x = hi + lo to 2^-22 relative, and both planes are exactly representable in TF32.
+//
+//  gemm_3xtf32_kernel   one CTA per 128 x 256 output tile.  Warp 0 streams 16-wide k-blocks of the
+//                  four planes into a 4-stage shared-memory ring with TMA (cp.async.bulk.tensor,
+//                  64-byte swizzle, mbarrier completion; no multicast).  Warp 1 issues, per 8-wide
+//                  k-step, three tcgen05.mma kind::tf32 instructions  hi*hi + hi*lo + lo*hi  that
+//                  accumulate in fp32 in tensor memory (two 256-column accumulators, summed by the
+//                  epilogue), and releases each stage with
+//                  tcgen05.commit.  Warps 2-5 drain the accumulator with tcgen05.ld and store C.
+//                  The dropped lo*lo term is below 2^-22 relative.
+//
+// Every wait on an mbarrier is bounded: past the limit the kernel records a code in a device flag,
+// stops issuing work, lets in-flight copies land, frees its tensor memory and returns; the host
+// reports the flag at the next synchronisation.
+//
+// Replaces _matmul_contig_fp32 / _matmul_fallback (src/cpp/ops/matmul.cu:60-205), plain SIMT FFMA
+// kernels, for fp32 operands.
+#include <cuda.h>
+
 #include "nt_core.cuh"
+
 namespace ntb {
-bool gemm_3xtf32(const float *, const float *, float *, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t, int64_t,
-                 int64_t, int64_t, int64_t) {
-  return false;
+
+constexpr int TC_BM = 128;   // UMMA M
+constexpr int TC_BN = 256;   // UMMA N
+constexpr int TC_BK = 16;    // k-block per stage: 16 fp32 = 64 bytes = one 64B-swizzle row
+constexpr int TC_STAGES = 4;
+constexpr int TC_UMMA_K = 8; // tf32: 32 bytes of k per instruction
+constexpr int TC_TMEM_COLS = 512; // two fp32 accumulators of 256 columns: hi*hi, and hi*lo + lo*hi
+constexpr uint32_t TC_A_PLANE_BYTES = TC_BM * TC_BK * 4;  // 8 KB
+constexpr uint32_t TC_B_PLANE_BYTES = TC_BN * TC_BK * 4;  // 16 KB
+constexpr uint32_t TC_STAGE_BYTES = 2 * TC_A_PLANE_BYTES + 2 * TC_B_PLANE_BYTES; // 48 KB
+constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+
+// ---------------------------------------------------------------------------------------------
+// split_pack
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
 }
+
+struct SplitArgs {
+  const float *src;
+  float *hi, *lo;       // [batch][R][Kp]
+  int64_t R, K, Kp;
+  int64_t s_r, s_k, s_b; // element strides of the source view
+  int mode;              // 0 generic, 1 unit stride along k (128-bit), 2 unit stride along r (128-bit + transpose)
+};
+
+__device__ __forceinline__ void split_store4(const SplitArgs &a, int64_t idx, float x0, float x1, float x2, float x3) {
+  const float h0 = tf32_round(x0), h1 = tf32_round(x1), h2 = tf32_round(x2), h3 = tf32_round(x3);
+  __stcs(reinterpret_cast<float4 *>(a.hi + idx), make_float4(h0, h1, h2, h3));
+  __stcs(reinterpret_cast<float4 *>(a.lo + idx),
+         make_float4(tf32_round(x0 - h0), tf32_round(x1 - h1), tf32_round(x2 - h2), tf32_round(x3 - h3)));
+}
+
+// One CTA converts a 64 (r) x 64 (k) tile.  Kp is a multiple of 32, so every 4-group of k inside Kp is
+// either fully stored or fully outside.
+__global__ void __launch_bounds__(256) split_pack(SplitArgs a) {
+  __shared__ float tile[64][65];
+  const int64_t r0 = int64_t(blockIdx.y) * 64, k0 = int64_t(blockIdx.x) * 64;
+  const int64_t b = blockIdx.z;
+  const float *src = a.src + b * a.s_b;
+  const int64_t plane_off = b * a.R * a.Kp;
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4; // 16 x 16
+  if (a.mode == 1) {
+    // thread: rows ty + 16 i, k group 4 tx
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t r = r0 + ty + 16 * i, k = k0 + 4 * tx;
+      if (r < a.R && k < a.Kp) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k + 3 < a.K) {
+          x = __ldcs(reinterpret_cast<const float4 *>(src + r * a.s_r + k));
+        } else {
+          if (k + 0 < a.K) x.x = src[r * a.s_r + k + 0];
+          if (k + 1 < a.K) x.y = src[r * a.s_r + k + 1];
+          if (k + 2 < a.K) x.z = src[r * a.s_r + k + 2];
+        }
+        split_store4(a, plane_off + r * a.Kp + k, x.x, x.y, x.z, x.w);
+      }
+    }
+    return;
+  }
+  if (a.mode == 2) {
+    // read along r (unit stride): rows of the tile in smem are k
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int64_t k = k0 + ty + 16 * i, r = r0 + 4 * tx;
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (k < a.K && r < a.R) {
+        if (r + 3 < a.R) {
+          x = __ldcs(reinterpret_cast<const float4 *>(src + k * a.s_k + r));
+        } else {
+          if (r + 0 < a.R) x.x = src[k * a.s_k + r + 0];
+          if (r + 1 < a.R) x.y = src[k * a.s_k + r + 1];
+          if (r + 2 < a.R) x.z = src[k * a.s_k + r + 2];
+        }
+      }
+      tile[ty + 16 * i][4 * tx + 0] = x.x;
+      tile[ty + 16 * i][4 * tx + 1] = x.y;
+      tile[ty + 16 * i][4 * tx + 2] = x.z;
+      tile[ty + 16 * i][4 * tx + 3] = x.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const int kk = (threadIdx.x & 63), rr = (threadIdx.x >> 6) + 4 * i;
+      const int64_t k = k0 + kk, r = r0 + rr;
+      tile[kk][rr] = (k < a.K && r < a.R) ? src[r * a.s_r + k * a.s_k] : 0.0f;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t r = r0 + ty + 16 * i, k = k0 + 4 * tx;
+    if (r < a.R && k < a.Kp)
+      split_store4(a, plane_off + r * a.Kp + k, tile[4 * tx + 0][ty + 16 * i], tile[4 * tx + 1][ty + 16 * i],
+                   tile[4 * tx + 2][ty + 16 * i], tile[4 * tx + 3][ty + 16 * i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+               "selp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false when the barrier did not flip within ~2^31 clocks.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > (1LL << 31)) return false;
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile in the 64-byte swizzle layout that TMA wrote: rows of 64 bytes, groups of 8
+// rows (512 bytes) back to back.  Fields: start address >> 4 in bits [0,14); leading byte offset >> 4
+// in [16,30) (unused for this layout, set to 1); stride byte offset >> 4 in [32,46) = 512 bytes between
+// 8-row groups; descriptor version 1 in [46,48); layout type SWIZZLE_64B = 4 in [61,64).
+__device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
+  d |= uint64_t(1) << 16;
+  d |= uint64_t(512 >> 4) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(4) << 61;
+  return d;
+}
+// Instruction descriptor, kind::tf32: D format F32 (1) in bits [4,6); A and B format TF32 (2) in [7,10) and
+// [10,13); A and B K-major (0) in bits 15, 16; N >> 3 in [17,23); M >> 4 in [24,29).
+constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(TC_BN >> 3) << 17) | (uint32_t(TC_BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\t"
+               "setp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+struct TcArgs {
+  float *C;
+  int64_t M, N;
+  int32_t num_kb;   // k-blocks of TC_BK
+  int32_t batch;    // number of batches (plane index of `lo` = batch + b)
+  int32_t c_vec;    // rows of C may be written 128 bits at a time
+  int *error_flag;
+};
+
+__global__ void __launch_bounds__(192, 1)
+gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE_BYTES;
+  // barriers: full[s] at bar_base + 8 s, empty[s] at + 32 + 8 s, accumulator-ready at + 64; tmem slot at + 72
+  const uint32_t full0 = bar_base, empty0 = bar_base + 32, acc_bar = bar_base + 64;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + (bar_base - smem_u32(smem_raw)) + 72);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN, b = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    mbar_init(acc_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) { // one warp allocates the accumulator columns
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t phase = 0;
+      int s = 0;
+      for (int kb = 0; kb < g.num_kb; ++kb) {
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) {
+          atomicExch(g.error_flag, 1);
+          break;
+        }
+        const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+        mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+        const int k = kb * TC_BK;
+        tma_load_3d(st, &map_a, full0 + 8 * s, k, m0, b);                                           // A hi
+        tma_load_3d(st + TC_A_PLANE_BYTES, &map_a, full0 + 8 * s, k, m0, g.batch + b);              // A lo
+        tma_load_3d(st + 2 * TC_A_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, b);                    // B hi
+        tma_load_3d(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, g.batch + b); // B lo
+        if (++s == TC_STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t phase = 0;
+      int s = 0;
+      bool ok = true;
+      for (int kb = 0; kb < g.num_kb; ++kb) {
+        if (!mbar_wait(full0 + 8 * s, phase)) {
+          atomicExch(g.error_flag, 2);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < TC_BK / TC_UMMA_K; ++ks) {
+          const uint32_t koff = ks * TC_UMMA_K * 4; // 32 bytes along the swizzled row
+          const uint64_t a_hi = umma_desc_sw64(st + koff);
+          const uint64_t a_lo = umma_desc_sw64(st + TC_A_PLANE_BYTES + koff);
+          const uint64_t b_hi = umma_desc_sw64(st + 2 * TC_A_PLANE_BYTES + koff);
+          const uint64_t b_lo = umma_desc_sw64(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES + koff);
+          // The tensor core's fp32 accumulation rounds toward zero, a bias that grows with the number
+          // of accumulations into one accumulator.  The large term gets an accumulator of its own
+          // (K/8 accumulations); the two cross terms, 2^-11 smaller, share the other one.
+          umma_tf32(tmem_acc, a_hi, b_hi, (kb | ks) != 0);
+          umma_tf32(tmem_acc + TC_BN, a_hi, b_lo, (kb | ks) != 0);
+          umma_tf32(tmem_acc + TC_BN, a_lo, b_hi, 1);
+        }
+        umma_commit(empty0 + 8 * s); // the stage may be refilled once these MMAs have read it
+        if (++s == TC_STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit(acc_bar);
+      else asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_bar) : "memory"); // release the epilogue
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue, warps 2..5
+    const int quad = warp & 3; // the 32-lane group of tensor memory this warp may read
+    bool ok = mbar_wait(acc_bar, 0);
+    if (!ok) atomicExch(g.error_flag, 3);
+    ok = ok && (*reinterpret_cast<volatile int *>(g.error_flag) == 0);
+    tcgen05_fence_after();
+    const int64_t m = int64_t(m0) + quad * 32 + lane;
+    float *crow = g.C + (int64_t(b) * g.M + m) * g.N;
+#pragma unroll 1
+    for (int c = 0; c < TC_BN; c += 32) {
+      uint32_t v[32], w[32];
+      const uint32_t taddr = tmem_acc + (uint32_t(quad * 32) << 16) + uint32_t(c);
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]),
+            "=r"(w[8]), "=r"(w[9]), "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]), "=r"(w[14]), "=r"(w[15]),
+            "=r"(w[16]), "=r"(w[17]), "=r"(w[18]), "=r"(w[19]), "=r"(w[20]), "=r"(w[21]), "=r"(w[22]), "=r"(w[23]),
+            "=r"(w[24]), "=r"(w[25]), "=r"(w[26]), "=r"(w[27]), "=r"(w[28]), "=r"(w[29]), "=r"(w[30]), "=r"(w[31])
+          : "r"(taddr + uint32_t(TC_BN))
+          : "memory");
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+            "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+            "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+            "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+          : "r"(taddr)
+          : "memory");
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) + __uint_as_float(w[e]));
+      if (ok && m < g.M) {
+        const int64_t n = int64_t(n0) + c;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int64_t nn = n + 4 * q;
+          if (g.c_vec && nn + 3 < g.N) {
+            *reinterpret_cast<float4 *>(crow + nn) =
+                make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]),
+                            __uint_as_float(v[4 * q + 3]));
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              if (nn + e < g.N) crow[nn + e] = __uint_as_float(v[4 * q + e]);
+          }
+        }
+      }
+    }
+  }
+
+  // If anything timed out, give copies that are still in flight time to land before the shared
+  // memory of this CTA is handed to another one.
+  if (*reinterpret_cast<volatile int *>(g.error_flag) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TC_TMEM_COLS) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    NT_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    if (!p || q != cudaDriverEntryPointSuccess) fail_runtime("cuTensorMapEncodeTiled is not available in this driver.");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// planes: [2 * batch][rows][Kp] fp32, K-major; box = 16 k x box_rows rows.
+static CUtensorMap make_map(float *planes, int64_t rows, int64_t Kp, int64_t batch2, uint32_t box_rows) {
+  CUtensorMap m;
+  cuuint64_t dims[3] = {cuuint64_t(Kp), cuuint64_t(rows), cuuint64_t(batch2)};
+  cuuint64_t strides[2] = {cuuint64_t(Kp) * 4, cuuint64_t(rows) * cuuint64_t(Kp) * 4};
+  cuuint32_t box[3] = {TC_BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, planes, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) fail_runtime("cuTensorMapEncodeTiled failed with code " + std::to_string(int(rc)));
+  return m;
+}
+
+static int *g_error_flag = nullptr;
+static int *error_flag_ptr() {
+  int *&flag = g_error_flag;
+  if (!flag) {
+    size_t rounded;
+    flag = static_cast<int *>(device_alloc(sizeof(int), &rounded));
+    NT_CUDA_CHECK(cudaMemsetAsync(flag, 0, sizeof(int), stream()));
+  }
+  return flag;
+}
+
+// Reads (and clears) the device-side error flag of the tensor-core kernel; called after a stream
+// synchronisation.  0 = no error.
+int gemm_tc_take_error() {
+  int *flag = g_error_flag;
+  if (!flag) return 0; // the kernel never ran
+  int host = 0;
+  if (cudaMemcpy(&host, flag, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+  if (host != 0) cudaMemset(flag, 0, sizeof(int));
+  return host;
+}
+
+static void launch_split(const float *src, float *planes, int64_t batch, int64_t R, int64_t K, int64_t Kp, int64_t s_b,
+                         int64_t s_r, int64_t s_k) {
+  SplitArgs a{};
+  a.src = src;
+  a.hi = planes;
+  a.lo = planes + batch * R * Kp;
+  a.R = R;
+  a.K = K;
+  a.Kp = Kp;
+  a.s_r = s_r;
+  a.s_k = s_k;
+  a.s_b = s_b;
+  const bool base_al = (reinterpret_cast<uintptr_t>(src) & 15) == 0 && (s_b % 4 == 0);
+  a.mode = 0;
+  if (s_k == 1 && base_al && s_r % 4 == 0) a.mode = 1;
+  else if (s_r == 1 && s_k != 1 && base_al && s_k % 4 == 0) a.mode = 2;
+  dim3 grid{unsigned(ceil_div(Kp, 64)), unsigned(ceil_div(R, 64)), unsigned(batch)};
+  split_pack<<<grid, 256, 0, stream()>>>(a);
+  check_launch("split_pack");
+}
+
+bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_t M, int64_t N, int64_t K,
+                 int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn) {
+  // limits of one launch / one tensor map
+  if (batch < 1 || batch > 32767 || M < 1 || N < 1 || K < 1) return false;
+  if (ceil_div(M, TC_BM) > 65535 || ceil_div(N, TC_BN) > 0x7fffffff) return false;
+  if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) return false;
+  static bool configured = false;
+  if (!configured) {
+    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(TC_SMEM_BYTES)));
+    configured = true;
+  }
+  const int64_t Kp = ceil_div(K, 32) * 32;
+  size_t ra = 0, rb = 0;
+  float *pa = static_cast<float *>(device_alloc(size_t(2 * batch * M * Kp) * 4, &ra));
+  float *pb = static_cast<float *>(device_alloc(size_t(2 * batch * N * Kp) * 4, &rb));
+  try {
+    launch_split(A, pa, batch, M, K, Kp, a_sb, a_sm, a_sk);
+    launch_split(B, pb, batch, N, K, Kp, b_sb, b_sn, b_sk);
+    CUtensorMap map_a = make_map(pa, M, Kp, 2 * batch, TC_BM);
+    CUtensorMap map_b = make_map(pb, N, Kp, 2 * batch, TC_BN);
+    TcArgs g{};
+    g.C = C;
+    g.M = M;
+    g.N = N;
+    g.num_kb = int32_t(Kp / TC_BK);
+    g.batch = int32_t(batch);
+    g.c_vec = (N % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
+    g.error_flag = error_flag_ptr();
+    dim3 grid{unsigned(ceil_div(N, TC_BN)), unsigned(ceil_div(M, TC_BM)), unsigned(batch)};
+    matmul_profile_begin();
+    gemm_3xtf32_kernel<<<grid, 192, TC_SMEM_BYTES, stream()>>>(map_a, map_b, g);
+    matmul_profile_end();
+    check_launch("gemm_3xtf32_kernel");
+  } catch (...) {
+    device_free(pa, ra);
+    device_free(pb, rb);
+    throw;
+  }
+  device_free(pa, ra);
+  device_free(pb, rb);
+  return true;
+}
+
 } // namespace ntb

@@ -361,12 +361,10 @@ int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
         a_sb = bi.a_strides[bi.ndim - 1];
         b_sb = bi.b_strides[bi.ndim - 1];
       }
-      matmul_profile_begin();
       if (single) done = gemm_3xtf32(g.A, g.B, g.C, nbatch, M, N, K, a_sb, a_sm, a_sk, b_sb, b_sk, b_sn);
-      if (done) matmul_profile_end();
     }
     if (!done) {
-      if (!(mode == 1 && K > 0)) matmul_profile_begin();
+      matmul_profile_begin();
       sgemm_simt(g, nbatch, /*fused=*/mode != 2);
       matmul_profile_end();
     }

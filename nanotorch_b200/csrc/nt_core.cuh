@@ -103,6 +103,7 @@ void count_launch(uint64_t n = 1);
 void matmul_profile_begin();
 void matmul_profile_end();
 bool cuda_ok();              // a device is present and usable
+int gemm_tc_take_error();    // device-side error flag of the tensor-core GEMM (0 = none); call after a sync
 int sm_count();
 
 // Device arena: 256-byte granules up to 1 MiB, 1 MiB granules above; freed blocks are cached per

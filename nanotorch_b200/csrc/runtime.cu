@@ -381,6 +381,11 @@ int nt_cuda_sync(void) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream()));
     NT_CUDA_CHECK(cudaStreamSynchronize(comm_stream()));
     NT_CUDA_CHECK(cudaStreamSynchronize(rt().copy));
+    const int tc_err = gemm_tc_take_error();
+    if (tc_err != 0)
+      fail_runtime("gemm_3xtf32: a pipeline wait ran out (code " + std::to_string(tc_err) +
+                   ": 1 = producer waiting for a free stage, 2 = MMA waiting for data, 3 = epilogue waiting for "
+                   "the accumulator); the affected products are invalid.");
   }
   NT_API_END
 }
