@@ -546,6 +546,43 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
+PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "exp4096",
+                 "sum8192_dim0", "sum8192_dim1", "sum8192_full")
+
+
+def profile_case(name: str, launches: int = 3) -> None:
+    """One small, fixed case for an `ncu` capture: a warm-up launch, then `launches` launches of one op
+    on inputs larger than L2 (at most ~0.5 GB on the device), then exit."""
+    import nanotorch_b200 as nt
+
+    _C = nt._C
+    r = np.random.default_rng
+    dev = lambda a: nt.Tensor.from_numpy(a.astype(np.float32), "cuda")  # noqa: E731
+    if name == "gemm4096":
+        a, b = dev(r(30).uniform(-1, 1, (4096, 4096))), dev(r(31).uniform(-1, 1, (4096, 4096)))
+        fn = lambda: _C.matmul(a._C_view, b._C_view)  # noqa: E731
+    elif name.startswith("add4096"):
+        a, b = dev(r(10).uniform(-1, 1, (4096, 4096))), dev(r(11).uniform(-1, 1, (4096, 4096)))
+        v = dev(r(13).uniform(-1, 1, (4096,)))
+        other = {"add4096": b, "add4096_transposed": b.T, "add4096_broadcast": v.expand(4096, 4096)}[name]
+        fn = lambda: _C.add(a._C_view, other._C_view)  # noqa: E731
+    elif name in ("tanh4096", "exp4096"):
+        x = dev(r(14).standard_normal((4096, 4096)))
+        kern = _C.tanh if name == "tanh4096" else _C.exp
+        fn = lambda: kern(x._C_view)  # noqa: E731
+    elif name.startswith("sum8192"):
+        x = dev(r(20).standard_normal((8192, 8192)))
+        axes = {"sum8192_dim0": [0], "sum8192_dim1": [1], "sum8192_full": [0, 1]}[name]
+        fn = lambda: _C.sum(x._C_view, axes, nt.float32)  # noqa: E731
+    else:
+        raise SystemExit(f"unknown case {name}; one of {PROFILE_CASES}")
+    keep = [fn()]
+    for _ in range(launches):
+        keep.append(fn())
+    _C.cuda_sync()
+    print(f"{name}: {launches + 1} launches done")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -553,7 +590,11 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op sweep and the CPU baseline sample")
+    ap.add_argument("--case", default=None, help=f"run one small case for a profiler capture and exit: {PROFILE_CASES}")
     args = ap.parse_args()
+    if args.case:
+        profile_case(args.case)
+        return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -308,7 +308,6 @@ int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
   require_same_dtype(x1, x2, "matmul");
   if (x1->ndim != x2->ndim) fail_invalid("matmul: x1 and x2 have different ndim.");
   if (x1->ndim < 2) fail_invalid("matmul: kernel should be called with >=2d tensors.");
-  require_cuda(x1, "matmul");
   const int nd = x1->ndim;
   BatchIndex bi{};
   int64_t nbatch = 1;
@@ -323,6 +322,7 @@ int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
   }
   const int64_t M = x1->shape[nd - 2], K = x1->shape[nd - 1], N = x2->shape[nd - 1];
   if (K != x2->shape[nd - 2]) fail_invalid("Invalid matmul shape.");
+  require_cuda(x1, "matmul");
   const int dt = x1->storage->dtype;
   if (dt == NT_BOOL) fail_invalid("Invalid dtype.");
 

@@ -1,0 +1,109 @@
+"""Host logic of the Tensor/autograd mirror, no kernels: view bookkeeping, shape rules, error behaviour
+(the cases the reference's own tests pin in tests/test_ops/test_tensor_core*.py)."""
+
+import pytest
+
+from nanotorch_b200.autograd import _matmul_shapes, normalize_axes
+from nanotorch_b200.dp import shard_bounds
+from nanotorch_b200.tensor import broadcast_shapes, contiguous_strides
+
+
+def test_construction_and_dtype_inference(nt):
+    t = nt.Tensor([[1, 2, 3], [4, 5, 6]])
+    assert t.shape == (2, 3) and t.dtype == nt.int64 and t.strides == ((3, 1), 0) and t.numel == 6 and len(t) == 2
+    assert nt.Tensor([1, 2.5]).dtype == nt.float32 and nt.Tensor([True, False]).dtype == nt.bool_
+    assert nt.Tensor(3.5).shape == () and nt.Tensor(3.5).item() == 3.5
+    assert nt.Tensor([1.7, -2.2], dtype=nt.int64).tolist() == [1, -2]
+    assert nt.Tensor([]).shape == (0,) and nt.Tensor([]).is_empty
+    with pytest.raises(ValueError):
+        nt.Tensor([[1, 2], [3]])
+    with pytest.raises(ValueError):
+        nt.Tensor([1, [2]])
+    with pytest.raises(TypeError):
+        nt.Tensor(["a"])
+    with pytest.raises(RuntimeError):
+        nt.Tensor([1, 2], requires_grad=True)
+    with pytest.raises(ValueError):
+        nt.Tensor([1.0], device="tpu")
+
+
+def test_views_share_storage_and_never_copy(nt):
+    t = nt.Tensor([[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]])
+    tt = t.T
+    assert tt.storage is t.storage and tt.shape == (3, 2) and tt.strides == ((1, 3), 0)
+    assert tt.tolist() == [[1.0, 4.0], [2.0, 5.0], [3.0, 6.0]]
+    assert t.transpose(0, 1).tolist() == tt.tolist() and t.transpose(1, 1).storage is t.storage
+    e = nt.Tensor([1.0, 2.0, 3.0]).expand(2, 3)
+    assert e.strides == ((0, 1), 0) and e.tolist() == [[1.0, 2.0, 3.0]] * 2
+    assert t.reshape(3, 2).storage is t.storage and t.reshape(2, 3).storage is t.storage
+    assert t.reshape(6).tolist() == [1.0, 2.0, 3.0, 4.0, 5.0, 6.0]
+    s = t[:, ::-1]
+    assert s.strides == ((3, -1), 2) and s.tolist() == [[3.0, 2.0, 1.0], [6.0, 5.0, 4.0]]
+    assert t[1].tolist() == [4.0, 5.0, 6.0] and t[-1, -1].item() == 6.0
+    assert t[None, 1, ..., None].shape == (1, 3, 1) and t[..., 0].tolist() == [1.0, 4.0]
+    assert t[0:1, 1:].shape == (1, 2)
+    with pytest.raises(IndexError):
+        t[2]
+    with pytest.raises(IndexError):
+        t[0, 0, 0]
+    with pytest.raises(ValueError):
+        t.reshape(4, 2)
+    with pytest.raises(ValueError):
+        nt.Tensor([1.0, 2.0]).expand(3)
+    with pytest.raises(IndexError):
+        nt.Tensor._new_view(t.storage, (2, 4), None, None)  # view past the end of its storage
+
+
+def test_shape_rules():
+    assert broadcast_shapes((5, 7), (7,)) == (5, 7) and broadcast_shapes((2, 1, 3), (4, 1)) == (2, 4, 3)
+    assert broadcast_shapes() == () and broadcast_shapes((), (3,)) == (3,)
+    with pytest.raises(RuntimeError):
+        broadcast_shapes((2, 3), (4,))
+    assert contiguous_strides((2, 3, 4)) == (12, 4, 1) and contiguous_strides(()) == ()
+    assert _matmul_shapes((5, 7), (7, 3)) == ((5, 7), (7, 3), (5, 3))
+    assert _matmul_shapes((7,), (7, 3)) == ((1, 7), (7, 3), (3,))
+    assert _matmul_shapes((5, 7), (7,)) == ((5, 7), (7, 1), (5,))
+    assert _matmul_shapes((7,), (7,)) == ((1, 7), (7, 1), ())
+    assert _matmul_shapes((3, 5, 4), (4, 6)) == ((3, 5, 4), (3, 4, 6), (3, 5, 6))
+    assert _matmul_shapes((2, 1, 5, 4), (3, 4, 6)) == ((2, 3, 5, 4), (2, 3, 4, 6), (2, 3, 5, 6))
+    with pytest.raises(RuntimeError):
+        _matmul_shapes((5, 7), (6, 3))
+    with pytest.raises(RuntimeError):
+        _matmul_shapes((), (3,))
+
+
+def test_axis_normalisation(nt):
+    x = nt.Tensor([[[0.0] * 4] * 3] * 2)
+    assert normalize_axes(None, x) == (0, 1, 2) and normalize_axes((), x) == (0, 1, 2)
+    assert normalize_axes(-1, x) == (2,) and normalize_axes((0, -1), x) == (0, 2)
+    with pytest.raises(ValueError):
+        normalize_axes((0, 0), x)
+    with pytest.raises(IndexError):
+        normalize_axes(3, x)
+    with pytest.raises(TypeError):
+        normalize_axes((0.5,), x)
+
+
+def test_autograd_bookkeeping_errors(nt):
+    t = nt.Tensor([1.0, 2.0])
+    with pytest.raises(RuntimeError):
+        t.backward()  # does not require grad
+    t.enable_grad()
+    with pytest.raises(RuntimeError):
+        t.backward()  # not a scalar
+    assert t.requires_grad and t.is_leaf and t.grad is None
+    with pytest.raises(RuntimeError):
+        nt.Tensor([1, 2]).enable_grad()
+    with pytest.raises(TypeError):
+        nt.Tensor([1, 2]).to(nt.Device.Cuda if False else nt.int64).mean()  # mean of an integer tensor
+
+
+def test_shard_bounds_partition_the_batch():
+    for n, world in [(16384, 1), (16384, 8), (10, 4), (7, 8)]:
+        pieces = [shard_bounds(n, r, world) for r in range(world)]
+        assert pieces[0][0] == 0 and pieces[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(pieces, pieces[1:]))
+        sizes = [hi - lo for lo, hi in pieces]
+        assert max(sizes) - min(sizes) <= 1
+    with pytest.raises(ValueError):
+        shard_bounds(8, 2, 2)
