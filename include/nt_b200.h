@@ -148,6 +148,22 @@ int nt_min(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **o
 int nt_argmax(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out); /* Int64 output */
 int nt_argmin(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out); /* Int64 output */
 
+/* Row sums of a dense fp32 matrix, out[r] = sum_c in[r * row_len + c], that allocate nothing.
+ * No counterpart in the reference.  For callers that must not let the library touch the device
+ * allocator: a host runtime that handed all device memory to its own arena at start-up, or a
+ * latency-critical loop in which cudaMalloc's device-wide synchronisation would stall every stream.
+ * `in` and `out` are device pointers owned by the caller (n_rows * row_len and n_rows floats).  The
+ * cross-CTA scratch of the reduction sits in a fixed 9 KB device array inside the library (held by
+ * every GPU that loads it, until exit) instead of coming from the arena.  Rows are split over several
+ * CTAs when there are too few of them to fill the GPU (fewer than 8 per SM) and they are longer than
+ * 8192 elements; such a call may have at most 256 rows and 2048 partial sums, beyond that it is refused
+ * with NT_ERR_INVALID -- use nt_sum for those.  Shapes that need no split have no limit.  The first call on a device looks up the array's device
+ * address; make that first call before any stream capture.  All calls share the one array and each
+ * leaves its partial sums behind: two calls that overlap on the GPU (different streams or
+ * processes' threads) race; calls issued through this library's single stream do not.  Runs on
+ * the library stream, asynchronously. */
+int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float *out);
+
 /* ------------------------------------------------------------------ matmul (src/cpp/ops/matmul.cu:236-273) */
 int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out);
 /* fp32 product mode.  0 = exact FP32 SIMT (FMA, sequential in k: the rounding of the reference's

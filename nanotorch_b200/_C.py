@@ -529,6 +529,17 @@ def sgd_update(param: TensorView, grad: TensorView, lr: float, grad_scale: float
     _check(_lib.nt_sgd_update(_vref(param), _vref(grad), C.c_float(lr), C.c_float(grad_scale)))
 
 
+def sum_rows_noalloc(src: Storage, n_rows: int, row_len: int, out: Storage) -> None:
+    """out[r] = sum of row r of the dense fp32 [n_rows, row_len] matrix at the start of `src`, through
+    the entry point that never allocates: both storages are the caller's, the kernel's scratch is a
+    fixed array inside the library (see nt_sum_rows_noalloc in include/nt_b200.h for the limits)."""
+    for s, need in ((src, n_rows * row_len), (out, n_rows)):
+        if s.device != Device.Cuda or s.dtype != Dtype.Float32 or s.size < need:
+            raise ValueError("sum_rows_noalloc: Float32 Cuda storages of at least n_rows*row_len and n_rows elements")
+    _check(_lib.nt_sum_rows_noalloc(C.c_void_p(src.data_ptr), C.c_int64(n_rows), C.c_int64(row_len),
+                                    C.c_void_p(out.data_ptr)))
+
+
 COMM_ID_BYTES = 128
 
 

@@ -512,11 +512,77 @@ struct UniqueMaskMulF { // g * float(mask && count == 1)
   }
 };
 
+// ---------------------------------------------------------------------------------------------
+// Row sums without any allocation: the cross-CTA scratch of reduce_rows (one partial per CTA, one
+// ticket per row) lives in this fixed device array instead of coming from the arena.
+constexpr int64_t NOALLOC_MAX_PARTIALS = 2048; // floats
+constexpr int64_t NOALLOC_MAX_ROWS = 256;      // tickets: rows that are long enough to be split over CTAs
+struct NoAllocScratch {
+  float partials[NOALLOC_MAX_PARTIALS];
+  unsigned tickets[NOALLOC_MAX_ROWS];
+};
+static __device__ __align__(256) NoAllocScratch g_noalloc_scratch; // 9 KB on every GPU that loads the library
+
+// `g_noalloc_scratch` named in host code is only a host-side handle; the kernel needs the device
+// address, looked up once per device with that device current.
+static NoAllocScratch *noalloc_scratch_device_ptr() {
+  static NoAllocScratch *per_device[64] = {};
+  int dev = 0;
+  NT_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) fail_runtime("nt_sum_rows_noalloc: device ordinal out of range.");
+  if (!per_device[dev]) {
+    void *p = nullptr;
+    NT_CUDA_CHECK(cudaGetSymbolAddress(&p, g_noalloc_scratch));
+    per_device[dev] = static_cast<NoAllocScratch *>(p);
+  }
+  return per_device[dev];
+}
+
 } // namespace ntb
 
 using namespace ntb;
 
 extern "C" {
+
+int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float *out) {
+  NT_API_BEGIN
+  if (!in || !out) fail_invalid("nt_sum_rows_noalloc: null pointer.");
+  if (n_rows < 0 || row_len < 1) fail_invalid("nt_sum_rows_noalloc: n_rows must be >= 0 and row_len >= 1.");
+  if (n_rows == 0) return NT_OK;
+  cudaStream_t st = stream();
+  NoAllocScratch *scratch = noalloc_scratch_device_ptr();
+  // same split rule as the allocating path (try_fast_f32), so both entry points add in the same order
+  const int64_t target_ctas = int64_t(sm_count()) * 8;
+  KeepIndex keep{};
+  keep.ndim = 1;
+  keep.shape[0] = n_rows;
+  keep.strides[0] = row_len;
+  if (row_len < 1024 && n_rows >= 64) {
+    int64_t blocks = ceil_div(n_rows, 8);
+    if (blocks > 0x7fffffffLL) fail_invalid("nt_sum_rows_noalloc: too many rows for one launch.");
+    reduce_rows_warp<RSum><<<unsigned(blocks), 256, 0, st>>>(in, out, keep, n_rows, row_len);
+    check_launch("reduce_rows_warp");
+    return NT_OK;
+  }
+  int64_t S = ceil_div(target_ctas, n_rows);
+  int64_t max_s = ceil_div(row_len, 8192);
+  if (S > max_s) S = max_s;
+  if (S > 1024) S = 1024;
+  if (S < 1) S = 1;
+  int64_t chunk = ceil_div(ceil_div(row_len, S), 1024) * 1024;
+  S = ceil_div(row_len, chunk);
+  if (n_rows * S > 0x7fffffffLL) fail_invalid("nt_sum_rows_noalloc: too many rows for one launch.");
+  if (S > 1 && (n_rows * S > NOALLOC_MAX_PARTIALS || n_rows > NOALLOC_MAX_ROWS))
+    fail_invalid("nt_sum_rows_noalloc: this shape needs " + std::to_string(n_rows * S) + " partial sums over " +
+                 std::to_string(n_rows) + " rows; the fixed scratch holds " + std::to_string(NOALLOC_MAX_PARTIALS) +
+                 " partials and " + std::to_string(NOALLOC_MAX_ROWS) + " row tickets. Use nt_sum for larger inputs.");
+  if (S > 1) // tickets must start at zero whatever the previous call left behind
+    NT_CUDA_CHECK(cudaMemsetAsync(scratch->tickets, 0, size_t(n_rows) * sizeof(unsigned), st));
+  reduce_rows<RSum><<<unsigned(n_rows * S), 256, 0, st>>>(in, out, scratch->partials, scratch->tickets, keep, row_len,
+                                                        int(S), chunk);
+  check_launch("reduce_rows");
+  NT_API_END
+}
 
 int nt_sum(const nt_view *x, const int64_t *axes, int32_t n_axes, int dtype, nt_storage **out) {
   NT_API_BEGIN
