@@ -476,7 +476,30 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
     gemm_ms, gemm_launches = _C.matmul_profile_read()
     launches = _C.launch_count() - launches0
     last_loss = float(loss.numpy())
-    ms_resident = max_over_ranks(ms_resident)
+    ms_eager = max_over_ranks(ms_resident)
+
+    # ---------------- the same step captured once into a CUDA graph and replayed
+    graph = _C.Graph()
+    with graph.capture():
+        graph_loss = step(Xd[0], Yd[0])
+    for _ in range(args.warmup):
+        graph.replay()
+    barrier()
+    launches0 = _C.launch_count()
+    with ClockSampler(local_rank) as clocks_graph:
+        e0 = _C.Event().record()
+        for _ in range(args.steps):
+            graph.replay()
+        e1 = _C.Event().record()
+        ms_graph = e0.elapsed_ms(e1)
+        barrier()
+    graph_launches = _C.launch_count() - launches0
+    last_loss = float(graph_loss.numpy())
+    ms_graph = max_over_ranks(ms_graph)
+    use_graph = ms_graph <= ms_eager
+    ms_resident = ms_graph if use_graph else ms_eager
+    if use_graph:
+        clocks = clocks_graph
 
     # ---------------- end to end: every step's batch comes from pinned host memory
     def feed(i):
@@ -484,12 +507,24 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         _C.upload_async(Xd[i % 2].storage, hx[1].ctypes.data, nbytes)
         _C.upload_async(Yd[i % 2].storage, hy[1].ctypes.data, nbytes)
 
+    graphs = None
+    if use_graph:  # one captured step per input buffer of the double-buffered feed
+        g1 = _C.Graph()
+        with g1.capture():
+            loss1 = step(Xd[1], Yd[1])
+        graphs = [(graph, graph_loss), (g1, loss1)]
+
     def e2e_loop(n, first):
         result = None
         for i in range(first, first + n):
             _C.upload_fence()      # compute waits for batch i
             feed(i + 1)            # batch i+1 streams in while step i computes
-            result = float(step(Xd[i % 2], Yd[i % 2]).numpy())  # device->host read of the loss, every step
+            if graphs is None:
+                out = step(Xd[i % 2], Yd[i % 2])
+            else:
+                graphs[i % 2][0].replay()
+                out = graphs[i % 2][1]
+            result = float(out.numpy())  # device->host read of the loss, every step
         return result
 
     feed(0)
@@ -521,7 +556,10 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
             "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_rank_batch": local, "width": WIDTH,
                        "layers": LAYERS, "matmul_mode": "3xTF32 (tcgen05)" if _C.get_matmul_mode() == 1 else "fp32",
                        "parallelism": f"dp{world}", "l2": "inputs larger than L2 (weights 537 MB, activations 268 MB each)",
-                       "final_loss": last_loss},
+                       "final_loss": last_loss,
+                       "step_issue": "one CUDA-graph replay per step" if use_graph else "eager launches",
+                       "ms_per_step_eager": ms_eager / args.steps, "ms_per_step_graph": ms_graph / args.steps,
+                       "kernels_per_step": launches // args.steps, "graph_replays_timed": graph_launches},
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": 2 * nbytes * world,
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,

@@ -87,6 +87,18 @@ int nt_event_destroy(void *event);
 int nt_matmul_profile_enable(int on);
 int nt_matmul_profile_read(double *total_ms, int64_t *launches);
 
+/* CUDA-graph capture of everything enqueued between begin and end (no counterpart in the reference,
+ * whose ~40 launches per training step are issued one by one from Python).  Device blocks handed out
+ * during the capture belong to the graph and are recycled only inside it, so replays never write
+ * memory that eager work owns; they return to the general cache at nt_graph_destroy.  Do not call a
+ * synchronising entry point (download, to(Cpu), equals, sync) or the matmul profile inside a capture.
+ * Warm the step up once before capturing it: first-use set-up (streams, shared-memory opt-in, the
+ * scratch counters) must not land inside the capture. */
+int nt_graph_begin_capture(int *graph_id);
+int nt_graph_end_capture(int graph_id);
+int nt_graph_launch(int graph_id);      /* replay on the compute stream */
+int nt_graph_destroy(int graph_id);
+
 /* ------------------------------------------------------------------ storage (src/cpp/storage.cpp:4-70) */
 int nt_storage_allocate(int64_t n, int dtype, int device, nt_storage **out); /* Storage::allocate */
 int nt_storage_retain(nt_storage *s);

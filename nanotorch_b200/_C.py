@@ -595,6 +595,50 @@ class Event:
             self._h = None
 
 
+class Graph:
+    """A captured sequence of launches: `with g.capture(): ...` records whatever the block enqueues
+    (kernels, NCCL collectives, stream joins), `g.replay()` re-issues it as one CUDA-graph launch.
+    Tensors created inside the block keep their device addresses, so results are read from the same
+    tensors after every replay."""
+
+    def __init__(self):
+        self._id = 0
+
+    def capture(self):
+        return _GraphCapture(self)
+
+    def replay(self) -> None:
+        _check(_lib.nt_graph_launch(self._id))
+
+    def close(self) -> None:
+        if self._id:
+            _check(_lib.nt_graph_destroy(self._id))
+            self._id = 0
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class _GraphCapture:
+    def __init__(self, graph: Graph):
+        self._g = graph
+
+    def __enter__(self):
+        gid = C.c_int(0)
+        _check(_lib.nt_graph_begin_capture(C.byref(gid)))
+        self._g._id = gid.value
+        return self._g
+
+    def __exit__(self, exc_type, exc, tb):
+        status = _lib.nt_graph_end_capture(self._g._id)
+        if exc_type is None:
+            _check(status)
+        return False
+
+
 def matmul_profile_enable(on: bool) -> None:
     _check(_lib.nt_matmul_profile_enable(1 if on else 0))
 

@@ -4,6 +4,8 @@
 #include <map>
 #include <mutex>
 #include <random>
+#include <set>
+#include <unordered_map>
 
 #include "nt_core.cuh"
 
@@ -28,6 +30,14 @@ struct Runtime {
   std::vector<cudaEvent_t> event_pool;
   std::map<size_t, std::vector<void *>> dev_cache;
   std::map<size_t, std::vector<void *>> pin_cache;
+  // CUDA-graph capture: blocks handed out while a graph is being captured belong to that graph and
+  // are recycled only inside it, so that eager work can never be given memory a replay will write.
+  int capturing = 0;                                   // id of the graph being captured, 0 = none
+  int next_graph_id = 1;
+  std::unordered_map<void *, int> graph_owned;         // block -> graph id
+  std::map<int, std::map<size_t, std::vector<void *>>> graph_cache;
+  std::set<int> live_graphs;
+  std::map<int, cudaGraphExec_t> graph_exec;
   uint64_t bytes_reserved = 0, bytes_in_use = 0, n_malloc = 0;
   size_t pin_cached_bytes = 0;
   std::atomic<uint64_t> launches{0};
@@ -138,16 +148,27 @@ void *device_alloc(size_t nbytes, size_t *rounded) {
   ensure_streams_locked(r);
   size_t sz = round_block(nbytes);
   *rounded = sz;
+  if (r.capturing) {
+    auto &gc = r.graph_cache[r.capturing];
+    auto git = gc.find(sz);
+    if (git != gc.end() && !git->second.empty()) {
+      void *p = git->second.back();
+      git->second.pop_back();
+      r.bytes_in_use += sz;
+      return p;
+    }
+  }
   auto it = r.dev_cache.find(sz);
   if (it != r.dev_cache.end() && !it->second.empty()) {
     void *p = it->second.back();
     it->second.pop_back();
     r.bytes_in_use += sz;
+    if (r.capturing) r.graph_owned[p] = r.capturing;
     return p;
   }
   void *p = nullptr;
   cudaError_t e = cudaMalloc(&p, sz);
-  if (e == cudaErrorMemoryAllocation) {
+  if (e == cudaErrorMemoryAllocation && !r.capturing) {
     cudaGetLastError();
     // Everything cached was freed behind work on the compute stream: drain it, give the cache
     // back to the driver, try once more.
@@ -159,14 +180,23 @@ void *device_alloc(size_t nbytes, size_t *rounded) {
   r.n_malloc += 1;
   r.bytes_reserved += sz;
   r.bytes_in_use += sz;
+  if (r.capturing) r.graph_owned[p] = r.capturing;
   return p;
 }
 void device_free(void *p, size_t rounded) {
   if (!p) return;
   Runtime &r = rt();
   std::lock_guard<std::mutex> lk(r.mu);
-  r.dev_cache[rounded].push_back(p);
   r.bytes_in_use -= rounded;
+  auto own = r.graph_owned.find(p);
+  if (own != r.graph_owned.end()) {
+    if (r.live_graphs.count(own->second)) {
+      r.graph_cache[own->second][rounded].push_back(p); // stays with its graph
+      return;
+    }
+    r.graph_owned.erase(own); // the graph is gone: an ordinary block again
+  }
+  r.dev_cache[rounded].push_back(p);
 }
 
 void *host_alloc(size_t nbytes, bool *pinned) {
@@ -497,6 +527,75 @@ int nt_matmul_profile_read(double *total_ms, int64_t *launches) {
   r.mm_events.clear();
   *total_ms = total;
   *launches = n;
+  NT_API_END
+}
+
+// ---------------------------------------------------------------- CUDA graphs
+int nt_graph_begin_capture(int *graph_id) {
+  NT_API_BEGIN
+  cudaStream_t st = stream();
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  if (r.capturing) fail_runtime("nt_graph_begin_capture: a capture is already in progress.");
+  if (r.mm_profile) fail_runtime("nt_graph_begin_capture: switch the matmul profile off first.");
+  NT_CUDA_CHECK(cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed));
+  r.capturing = r.next_graph_id++;
+  r.live_graphs.insert(r.capturing);
+  *graph_id = r.capturing;
+  NT_API_END
+}
+int nt_graph_end_capture(int graph_id) {
+  NT_API_BEGIN
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  if (r.capturing != graph_id || graph_id == 0) fail_runtime("nt_graph_end_capture: not the graph being captured.");
+  r.capturing = 0;
+  cudaGraph_t graph = nullptr;
+  cudaError_t e = cudaStreamEndCapture(r.compute, &graph);
+  if (e != cudaSuccess || !graph) {
+    r.live_graphs.erase(graph_id);
+    fail_runtime(std::string("cudaStreamEndCapture failed: ") + cudaGetErrorString(e));
+  }
+  cudaGraphExec_t exec = nullptr;
+  e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    r.live_graphs.erase(graph_id);
+    fail_runtime(std::string("cudaGraphInstantiate failed: ") + cudaGetErrorString(e));
+  }
+  r.graph_exec[graph_id] = exec;
+  NT_API_END
+}
+int nt_graph_launch(int graph_id) {
+  NT_API_BEGIN
+  cudaStream_t st = stream();
+  Runtime &r = rt();
+  auto it = r.graph_exec.find(graph_id);
+  if (it == r.graph_exec.end()) fail_invalid("nt_graph_launch: unknown graph.");
+  NT_CUDA_CHECK(cudaGraphLaunch(it->second, st));
+  count_launch();
+  NT_API_END
+}
+int nt_graph_destroy(int graph_id) {
+  NT_API_BEGIN
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  auto it = r.graph_exec.find(graph_id);
+  if (it != r.graph_exec.end()) {
+    if (r.compute) cudaStreamSynchronize(r.compute);
+    cudaGraphExecDestroy(it->second);
+    r.graph_exec.erase(it);
+  }
+  r.live_graphs.erase(graph_id);
+  auto gc = r.graph_cache.find(graph_id);
+  if (gc != r.graph_cache.end()) { // its recycled blocks go back to the general cache
+    for (auto &kv : gc->second)
+      for (void *p : kv.second) {
+        r.graph_owned.erase(p);
+        r.dev_cache[kv.first].push_back(p);
+      }
+    r.graph_cache.erase(gc);
+  }
   NT_API_END
 }
 
