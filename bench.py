@@ -79,7 +79,10 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([time.monotonic()] + [c.strip() for c in line.split(",")])
+
+    def mark(self) -> float:
+        return time.monotonic()
 
     def __exit__(self, *exc):
         if self.proc:
@@ -89,10 +92,15 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
-    def summary(self) -> dict:
+    def summary(self, t0: float | None = None, t1: float | None = None) -> dict:
+        """Samples that arrived in [t0, t1] (one sampling period of slack at the end); if the region was
+        shorter than a period, the first sample after it started."""
+        rows = [r[1:] for r in self.rows if t0 is None or (t0 <= r[0] <= (t1 or 1e30) + 0.25)]
+        if not rows and t0 is not None:
+            rows = [r[1:] for r in self.rows if r[0] >= t0][:1]
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in rows:
             if len(r) < 9:
                 continue
             try:
@@ -432,6 +440,7 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
     comm = Communicator(rank, world, exchange_id)
     peaks = measured_peaks()
+    sampler = ClockSampler(local_rank).__enter__()  # runs for the whole benchmark; regions are cut out by time
     lo, hi = shard_bounds(GLOBAL_BATCH, rank, world)
     local = hi - lo
 
@@ -465,13 +474,14 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
     barrier()
     launches0 = _C.launch_count()
     _C.matmul_profile_enable(True)
-    with ClockSampler(local_rank) as clocks:
-        e0 = _C.Event().record()
-        for _ in range(args.steps):
-            loss = step(Xd[0], Yd[0])
-        e1 = _C.Event().record()
-        ms_resident = e0.elapsed_ms(e1)
-        barrier()
+    t_eager0 = sampler.mark()
+    e0 = _C.Event().record()
+    for _ in range(args.steps):
+        loss = step(Xd[0], Yd[0])
+    e1 = _C.Event().record()
+    ms_resident = e0.elapsed_ms(e1)
+    t_eager1 = sampler.mark()
+    barrier()
     _C.matmul_profile_enable(False)
     gemm_ms, gemm_launches = _C.matmul_profile_read()
     launches = _C.launch_count() - launches0
@@ -486,20 +496,20 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         graph.replay()
     barrier()
     launches0 = _C.launch_count()
-    with ClockSampler(local_rank) as clocks_graph:
-        e0 = _C.Event().record()
-        for _ in range(args.steps):
-            graph.replay()
-        e1 = _C.Event().record()
-        ms_graph = e0.elapsed_ms(e1)
-        barrier()
+    t_graph0 = sampler.mark()
+    e0 = _C.Event().record()
+    for _ in range(args.steps):
+        graph.replay()
+    e1 = _C.Event().record()
+    ms_graph = e0.elapsed_ms(e1)
+    t_graph1 = sampler.mark()
+    barrier()
     graph_launches = _C.launch_count() - launches0
     last_loss = float(graph_loss.numpy())
     ms_graph = max_over_ranks(ms_graph)
     use_graph = ms_graph <= ms_eager
     ms_resident = ms_graph if use_graph else ms_eager
-    if use_graph:
-        clocks = clocks_graph
+    clock_window = (t_graph0, t_graph1) if use_graph else (t_eager0, t_eager1)
 
     # ---------------- end to end: every step's batch comes from pinned host memory
     def feed(i):
@@ -508,6 +518,10 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         _C.upload_async(Yd[i % 2].storage, hy[1].ctypes.data, nbytes)
 
     graphs = None
+    if not use_graph:
+        # eager collectives issued while a graph that captured collectives is alive were measured 3x
+        # slower (NCCL keeps switching between its persistent and eager plans): never mix the two
+        graph.close()
     if use_graph:  # one captured step per input buffer of the double-buffered feed
         g1 = _C.Graph()
         with g1.capture():
@@ -563,7 +577,7 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": 2 * nbytes * world,
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,
-            "clocks": clocks.summary(),
+            "clocks": sampler.summary(*clock_window),
             "roofline": {
                 "kernel": "gemm_3xtf32 (tcgen05.mma kind::tf32, 3 products per fp32 product)",
                 "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
@@ -577,9 +591,15 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         if world == 1 and not args.no_ops:
             line["ops"] = time_ops(nt, peaks)
             line["cpu_baseline"] = cpu_baseline_sample()
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     barrier()
+    # graphs that captured collectives go before the communicator they use
+    if graphs is not None:
+        for g, _ in graphs:
+            g.close()
+    opt.detach()
     comm.close()
+    sampler.__exit__(None, None, None)
     if dist is not None:
         dist.destroy_process_group()
 

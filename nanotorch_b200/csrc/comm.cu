@@ -129,6 +129,10 @@ int nt_comm_destroy(void) {
   NT_API_BEGIN
   Nccl &n = nccl();
   if (n.comm) {
+    // a captured graph that contains a collective keeps the communicator busy: NCCL's destroy waits
+    // for such graphs to be released, so release them first
+    destroy_all_graphs();
+    cudaStreamSynchronize(stream());
     cudaStreamSynchronize(comm_stream());
     n.CommDestroy(n.comm);
     n.comm = nullptr;

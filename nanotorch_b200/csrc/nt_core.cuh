@@ -105,6 +105,7 @@ void matmul_profile_end();
 bool cuda_ok();              // a device is present and usable
 int gemm_tc_take_error();    // device-side error flag of the tensor-core GEMM (0 = none); call after a sync
 int sm_count();
+void destroy_all_graphs();   // captured graphs hold NCCL work: they must go before the communicator does
 
 // Device arena: 256-byte granules up to 1 MiB, 1 MiB granules above; freed blocks are cached per
 // rounded size and reused.  Reuse is safe without events because every consumer is on stream().

@@ -100,6 +100,32 @@ int sm_count() {
   ensure_streams_locked(r);
   return r.sms;
 }
+static void graph_destroy_locked(Runtime &r, int graph_id) {
+  auto it = r.graph_exec.find(graph_id);
+  if (it != r.graph_exec.end()) {
+    if (r.compute) cudaStreamSynchronize(r.compute);
+    cudaGraphExecDestroy(it->second);
+    r.graph_exec.erase(it);
+  }
+  r.live_graphs.erase(graph_id);
+  auto gc = r.graph_cache.find(graph_id);
+  if (gc != r.graph_cache.end()) { // its recycled blocks go back to the general cache
+    for (auto &kv : gc->second)
+      for (void *p : kv.second) {
+        r.graph_owned.erase(p);
+        r.dev_cache[kv.first].push_back(p);
+      }
+    r.graph_cache.erase(gc);
+  }
+}
+
+void destroy_all_graphs() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  std::vector<int> ids;
+  for (auto &kv : r.graph_exec) ids.push_back(kv.first);
+  for (int id : ids) graph_destroy_locked(r, id);
+}
 void count_launch(uint64_t n) { rt().launches.fetch_add(n, std::memory_order_relaxed); }
 
 static cudaEvent_t pooled_event(Runtime &r) {
@@ -580,22 +606,7 @@ int nt_graph_destroy(int graph_id) {
   NT_API_BEGIN
   Runtime &r = rt();
   std::lock_guard<std::mutex> lk(r.mu);
-  auto it = r.graph_exec.find(graph_id);
-  if (it != r.graph_exec.end()) {
-    if (r.compute) cudaStreamSynchronize(r.compute);
-    cudaGraphExecDestroy(it->second);
-    r.graph_exec.erase(it);
-  }
-  r.live_graphs.erase(graph_id);
-  auto gc = r.graph_cache.find(graph_id);
-  if (gc != r.graph_cache.end()) { // its recycled blocks go back to the general cache
-    for (auto &kv : gc->second)
-      for (void *p : kv.second) {
-        r.graph_owned.erase(p);
-        r.dev_cache[kv.first].push_back(p);
-      }
-    r.graph_cache.erase(gc);
-  }
+  graph_destroy_locked(r, graph_id);
   NT_API_END
 }
 
