@@ -605,7 +605,7 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
 
 PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "exp4096",
-                 "sum8192_dim0", "sum8192_dim1", "sum8192_full")
+                 "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192")
 
 
 def profile_case(name: str, launches: int = 3) -> None:
@@ -624,9 +624,14 @@ def profile_case(name: str, launches: int = 3) -> None:
         v = dev(r(13).uniform(-1, 1, (4096,)))
         other = {"add4096": b, "add4096_transposed": b.T, "add4096_broadcast": v.expand(4096, 4096)}[name]
         fn = lambda: _C.add(a._C_view, other._C_view)  # noqa: E731
-    elif name in ("tanh4096", "exp4096"):
+    elif name == "max_backward8192":
+        x = dev(r(20).standard_normal((8192, 8192)))
+        m = x.max((1,)).reshape(8192, 1).expand(8192, 8192)
+        g = dev(np.ones((8192,))).reshape(8192, 1).expand(8192, 8192)
+        fn = lambda: _C.extremum_backward(g._C_view, x._C_view, m._C_view, [1])  # noqa: E731
+    elif name in ("tanh4096", "exp4096", "sigmoid4096"):
         x = dev(r(14).standard_normal((4096, 4096)))
-        kern = _C.tanh if name == "tanh4096" else _C.exp
+        kern = {"tanh4096": _C.tanh, "exp4096": _C.exp, "sigmoid4096": _C.sigmoid}[name]
         fn = lambda: kern(x._C_view)  # noqa: E731
     elif name.startswith("sum8192"):
         x = dev(r(20).standard_normal((8192, 8192)))

@@ -56,7 +56,7 @@ template <class T> struct SqrtF {
   }
 };
 
-// ---- exp: |result - exact| <= 0.51 ulp so that it sits within one ulp of a correctly rounded libm.
+// ---- exp with |result - exact| <= 0.51 ulp, used where exp feeds further rounded steps (sigmoid):
 // e^x = 2^k * e^r with k = round(x/ln2), r = x - k*ln2 evaluated in double (|r| <= 0.347), e^r by
 // its Taylor polynomial to degree 9 (truncation < 2^-33), then one rounding to float.
 __device__ __forceinline__ float exp_f32_accurate(float xf) {
@@ -88,7 +88,10 @@ template <class T> struct ExpF {
   using in_t = T;
   using out_t = T;
   __device__ __forceinline__ T operator()(T a) const {
-    if constexpr (std::is_same_v<T, float>) return exp_f32_accurate(a);
+    // fp32: the CUDA library's expf (documented error <= 2 ulp; measured against the host libm on 2^24
+    // N(0,1) and 2^24 U(-87,88) arguments: never more than 2 ulp apart), ~4x fewer issue slots than
+    // the double-precision evaluation above
+    if constexpr (std::is_same_v<T, float>) return expf(a);
     else return exp(a);
   }
 };

@@ -512,6 +512,223 @@ struct UniqueMaskMulF { // g * float(mask && count == 1)
   }
 };
 
+
+// ---------------------------------------------------------------------------------------------
+// Max/Min backward without materialising the mask: two launches over x.
+//   extremum_count_*  counts, per reduced slice, the positions equal to the slice's extremum
+//                     (integer atomics: exact, order-free);
+//   extremum_apply    out = g_slice * float(x == m_slice && count_slice == 1).
+// x is seen as [n_keep slices] x [n_drop] with the dropped dims either the trailing run (ROWS:
+// x[row_base + j]) or the leading dim of a dense matrix (COLS: x[i * sR + c]).  g and m are read once
+// per slice through their own kept-dim strides (they are stride-0 along the dropped dims).
+// Algorithmic bytes: x twice + out once = 12 per element (the composed chain moves 20).
+struct SliceScalars {
+  KeepIndex x_keep, g_keep, m_keep; // same shapes, each operand's strides over the kept dims
+};
+
+__global__ void __launch_bounds__(256) extremum_count_rows(const float *__restrict__ x, const float *__restrict__ m,
+                                                           int *__restrict__ count, SliceScalars sc, int64_t L,
+                                                           int chunks_per_row, int64_t chunk) {
+  __shared__ int warp_cnt[8];
+  const int64_t row = blockIdx.x / chunks_per_row;
+  const int c = int(blockIdx.x - row * chunks_per_row);
+  const float *p = x + keep_offset(sc.x_keep, row);
+  const float mv = m[keep_offset(sc.m_keep, row)];
+  const int64_t lo = int64_t(c) * chunk;
+  int64_t hi = lo + chunk;
+  if (hi > L) hi = L;
+  int n = 0;
+  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+    const int64_t nvec = (hi - lo) >> 2;
+    const float4 *pv = reinterpret_cast<const float4 *>(p + lo);
+    for (int64_t i = threadIdx.x; i < nvec; i += 256) {
+      float4 v = __ldcs(pv + i);
+      n += (v.x == mv) + (v.y == mv) + (v.z == mv) + (v.w == mv);
+    }
+    for (int64_t j = lo + (nvec << 2) + threadIdx.x; j < hi; j += 256) n += (p[j] == mv);
+  } else {
+    for (int64_t j = lo + threadIdx.x; j < hi; j += 256) n += (p[j] == mv);
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) n += __shfl_xor_sync(0xffffffffu, n, s);
+  if ((threadIdx.x & 31) == 0) warp_cnt[threadIdx.x >> 5] = n;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += warp_cnt[w];
+    if (t) atomicAdd(count + row, t);
+  }
+}
+
+// COLS: block = 128 columns (32 lanes x 4) x rows_per_block rows, 8 warps interleaved over the rows.
+__global__ void __launch_bounds__(256) extremum_count_cols(const float *__restrict__ x, const float *__restrict__ m,
+                                                           int *__restrict__ count, SliceScalars sc, int64_t R, int64_t C,
+                                                           int64_t sR, int64_t rows_per_block, int vec) {
+  __shared__ int part[8][128];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t c0 = int64_t(blockIdx.x) * 128 + lane * 4;
+  int64_t r_lo = int64_t(blockIdx.y) * rows_per_block, r_hi = r_lo + rows_per_block;
+  if (r_hi > R) r_hi = R;
+  int n[4] = {0, 0, 0, 0};
+  float mv[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) mv[e] = (c0 + e < C) ? m[keep_offset(sc.m_keep, c0 + e)] : 0.0f;
+  if (c0 < C) {
+    for (int64_t r = r_lo + warp; r < r_hi; r += 8) {
+      const float *q = x + r * sR + c0;
+      if (vec) {
+        float4 v = __ldcs(reinterpret_cast<const float4 *>(q));
+        n[0] += (v.x == mv[0]); n[1] += (v.y == mv[1]); n[2] += (v.z == mv[2]); n[3] += (v.w == mv[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c0 + e < C) n[e] += (q[e] == mv[e]);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) part[warp][lane * 4 + e] = n[e];
+  __syncthreads();
+  if (threadIdx.x < 128) {
+    int t = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += part[w][threadIdx.x];
+    const int64_t c = int64_t(blockIdx.x) * 128 + threadIdx.x;
+    if (t && c < C) atomicAdd(count + c, t);
+  }
+}
+
+// One thread per 4 consecutive output elements.  ROWS: slice = idx / L (L % 4 == 0 when vec);
+// COLS: slice = idx % C.
+template <bool ROWS>
+__global__ void __launch_bounds__(256) extremum_apply(const float *__restrict__ x, const float *__restrict__ g,
+                                                      const float *__restrict__ m, const int *__restrict__ count,
+                                                      float *__restrict__ out, SliceScalars sc, int64_t n_keep, int64_t L,
+                                                      int64_t sR, int vec) {
+  // L = elements per slice (ROWS) or number of columns C (COLS)
+  const int64_t total = ROWS ? n_keep * L : n_keep /*rows*/ * L;
+  const int64_t t = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  if (t >= total) return;
+  const int64_t outer = t / L, inner = t - outer * L; // ROWS: (slice, j); COLS: (row i, column c)
+  float xv[4], res[4];
+  const float *px = ROWS ? x + keep_offset(sc.x_keep, outer) + inner : x + outer * sR + inner;
+  if (vec) {
+    float4 v = __ldcs(reinterpret_cast<const float4 *>(px));
+    xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) xv[e] = (t + e < total) ? (ROWS ? x[keep_offset(sc.x_keep, (t + e) / L) + (t + e) % L]
+                                                               : x[((t + e) / L) * sR + (t + e) % L])
+                                                        : 0.0f;
+  }
+  if (ROWS && vec) {
+    const float gv = g[keep_offset(sc.g_keep, outer)], mv = m[keep_offset(sc.m_keep, outer)];
+    const bool unique = count[outer] == 1;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) res[e] = gv * ((xv[e] == mv && unique) ? 1.0f : 0.0f);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t idx = t + e;
+      const int64_t slice = ROWS ? idx / L : idx % L;
+      if (idx < total) {
+        const float gv = g[keep_offset(sc.g_keep, slice)], mv = m[keep_offset(sc.m_keep, slice)];
+        res[e] = gv * ((xv[e] == mv && count[slice] == 1) ? 1.0f : 0.0f);
+      }
+    }
+  }
+  if (vec) {
+    __stcs(reinterpret_cast<float4 *>(out + t), make_float4(res[0], res[1], res[2], res[3]));
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (t + e < total) out[t + e] = res[e];
+  }
+}
+
+// Returns false when the views do not have one of the two shapes above (the caller then composes).
+static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt_view *m, const int64_t *axes,
+                                    int32_t n_axes, float *out) {
+  const int nd = x->ndim;
+  if (n_axes < 1 || n_axes > nd) return false;
+  bool dropped[NT_MAX_DIMS] = {};
+  for (int i = 0; i < n_axes; ++i) {
+    if (axes[i] < 0 || axes[i] >= nd || dropped[axes[i]]) return false;
+    dropped[axes[i]] = true;
+  }
+  bool trailing = true, leading = true;
+  for (int d = 0; d < nd; ++d) {
+    if (dropped[d] != (d >= nd - n_axes)) trailing = false;
+    if (dropped[d] != (d < n_axes)) leading = false;
+  }
+  if (!trailing && !leading) return false;
+  // g and m must not vary along the dropped dims
+  for (int d = 0; d < nd; ++d)
+    if (dropped[d] && x->shape[d] > 1 && (g->strides[d] != 0 || m->strides[d] != 0)) return false;
+  Plan pl = make_plan(x, axes, n_axes);
+  if (pl.n_keep == 0 || pl.n_drop == 0) return false;
+  SliceScalars sc{};
+  for (int d = 0; d < nd; ++d) {
+    if (dropped[d] || x->shape[d] == 1) continue;
+    const int k = sc.x_keep.ndim;
+    sc.x_keep.shape[k] = sc.g_keep.shape[k] = sc.m_keep.shape[k] = x->shape[d];
+    sc.x_keep.strides[k] = x->strides[d];
+    sc.g_keep.strides[k] = g->strides[d];
+    sc.m_keep.strides[k] = m->strides[d];
+    sc.x_keep.ndim = sc.g_keep.ndim = sc.m_keep.ndim = k + 1;
+  }
+  const float *xp = static_cast<const float *>(x->storage->data) + x->offset;
+  const float *gp = static_cast<const float *>(g->storage->data) + g->offset;
+  const float *mp = static_cast<const float *>(m->storage->data) + m->offset;
+  cudaStream_t st = stream();
+  const bool rows = trailing && pl.drop.ndim == 1 && pl.drop.strides[0] == 1;
+  const bool cols = !rows && leading && pl.drop.ndim == 1 && pl.keep.ndim == 1 && pl.keep.strides[0] == 1;
+  if (!rows && !cols) return false;
+  if (pl.n_keep * pl.n_drop >= (int64_t(1) << 40)) return false;
+  size_t rounded = 0;
+  int *count = static_cast<int *>(device_alloc(size_t(pl.n_keep) * sizeof(int), &rounded));
+  NT_CUDA_CHECK(cudaMemsetAsync(count, 0, size_t(pl.n_keep) * sizeof(int), st));
+  const int64_t total = pl.n_keep * pl.n_drop;
+  const int64_t apply_blocks = ceil_div(ceil_div(total, 4), 256);
+  if (rows) {
+    const int64_t L = pl.n_drop;
+    const int64_t chunk = 16384; // elements per counting CTA (a multiple of 4)
+    const int64_t chunks = ceil_div(L, chunk);
+    if (pl.n_keep * chunks > 0x7fffffffLL || apply_blocks > 0x7fffffffLL) {
+      device_free(count, rounded);
+      return false;
+    }
+    extremum_count_rows<<<unsigned(pl.n_keep * chunks), 256, 0, st>>>(xp, mp, count, sc, L, int(chunks), chunk);
+    check_launch("extremum_count_rows");
+    bool vec = (L % 4 == 0) && aligned16(xp) && aligned16(out);
+    for (int k = 0; k < sc.x_keep.ndim; ++k) vec = vec && (sc.x_keep.strides[k] % 4 == 0);
+    extremum_apply<true><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, pl.n_keep, L, 0, vec ? 1 : 0);
+    check_launch("extremum_apply");
+  } else {
+    const int64_t R = pl.n_drop, C = pl.n_keep, sR = pl.drop.strides[0];
+    const bool vec = (C % 4 == 0) && (sR % 4 == 0) && aligned16(xp) && aligned16(out);
+    const int64_t tiles = ceil_div(C, 128);
+    int64_t row_blocks = ceil_div(int64_t(sm_count()) * 8, tiles);
+    if (row_blocks > ceil_div(R, 32)) row_blocks = ceil_div(R, 32);
+    if (row_blocks < 1) row_blocks = 1;
+    if (row_blocks > 65535) row_blocks = 65535;
+    const int64_t rows_per_block = ceil_div(R, row_blocks);
+    row_blocks = ceil_div(R, rows_per_block);
+    if (tiles > 0x7fffffffLL || apply_blocks > 0x7fffffffLL) {
+      device_free(count, rounded);
+      return false;
+    }
+    dim3 grid{unsigned(tiles), unsigned(row_blocks), 1};
+    extremum_count_cols<<<grid, 256, 0, st>>>(xp, mp, count, sc, R, C, sR, rows_per_block, vec ? 1 : 0);
+    check_launch("extremum_count_cols");
+    extremum_apply<false><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, R, C, sR, vec ? 1 : 0);
+    check_launch("extremum_apply");
+  }
+  device_free(count, rounded);
+  return true;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Row sums without any allocation: the cross-CTA scratch of reduce_rows (one partial per CTA, one
 // ticket per row) lives in this fixed device array instead of coming from the arena.
@@ -626,6 +843,14 @@ int nt_extremum_backward(const nt_view *g_expanded, const nt_view *x, const nt_v
     require_same_shape(chk[0], chk[i], fname);
   }
   const int64_t n = view_numel(*x);
+  if (n > 0) {
+    StorageRef fused(storage_new(n, NT_FLOAT32, NT_CUDA));
+    if (extremum_backward_fused(g_expanded, x, m_expanded, axes, n_axes, static_cast<float *>(fused->data))) {
+      *out = fused.release();
+      return NT_OK;
+    }
+  }
+  // general views: compose mask, count and product
   // mask = float(x == m)
   StorageRef mask(storage_new(n, NT_FLOAT32, NT_CUDA));
   nt_view mv = fresh_view(mask.s, *x);
