@@ -27,6 +27,10 @@ struct EwParams {
   int ndim;                               // collapsed dims, 0..8 (0 => single element)
   int64_t numel;
   int64_t shape[NT_MAX_DIMS];
+  // 32-bit index path: n / shape[d] == __umulhi(n, div_mul[d]) >> div_shift[d] for every n < 2^31
+  // (div_mul == 0 marks an extent of 1)
+  uint32_t div_mul[NT_MAX_DIMS];
+  uint32_t div_shift[NT_MAX_DIMS];
   int64_t strides[EW_MAX_IN + 1][NT_MAX_DIMS]; // [0] = output
   void *out;                              // already advanced by the view offset
   const void *in[EW_MAX_IN];              // already advanced by the view offsets
@@ -100,12 +104,33 @@ __device__ __forceinline__ void ew_offsets(const EwParams &p, IDX lin, int64_t (
   for (int o = 0; o < NOPS; ++o) off[o] = 0;
   for (int d = p.ndim - 1; d >= 0; --d) {
     IDX ext = IDX(p.shape[d]);
-    IDX q = lin / ext;
+    IDX q;
+    if constexpr (sizeof(IDX) == 4) // multiply-high by a precomputed reciprocal instead of a division
+      q = p.div_mul[d] ? (__umulhi(lin, p.div_mul[d]) >> p.div_shift[d]) : lin;
+    else
+      q = lin / ext;
     IDX r = lin - q * ext;
     lin = q;
 #pragma unroll
     for (int o = 0; o < NOPS; ++o) off[o] += int64_t(r) * p.strides[o][d];
   }
+}
+
+// Reciprocal of a divisor d >= 1 for the 32-bit path above: with p = 31 + ceil(log2 d) and
+// m = ceil(2^p / d) < 2^32, floor(n / d) == (n * m) >> p for all 0 <= n < 2^31.
+inline void ew_fast_divisor(int64_t d, uint32_t *mul, uint32_t *shift) {
+  if (d <= 1) {
+    *mul = 0;
+    *shift = 0;
+    return;
+  }
+  int cl = 0;
+  while ((int64_t(1) << cl) < d) ++cl;
+  const int p = 31 + cl;
+  const unsigned __int128 one = 1;
+  const unsigned __int128 m = ((one << p) + (unsigned __int128)d - 1) / (unsigned __int128)d;
+  *mul = uint32_t(m);
+  *shift = uint32_t(p - 32);
 }
 
 template <class F, int NIN, int VEC, class IDX>
@@ -335,6 +360,7 @@ template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NI
   p.numel = it.numel;
   for (int d = 0; d < it.ndim; ++d) {
     p.shape[d] = it.shape[d];
+    ew_fast_divisor(it.shape[d], &p.div_mul[d], &p.div_shift[d]);
     for (int o = 0; o <= NIN; ++o) p.strides[o][d] = it.strides[o][d];
   }
   p.out = out;

@@ -525,6 +525,12 @@ struct UniqueMaskMulF { // g * float(mask && count == 1)
 struct SliceScalars {
   KeepIndex x_keep, g_keep, m_keep; // same shapes, each operand's strides over the kept dims
 };
+// offset of slice `lin`: a single kept dim needs no division at all
+__device__ __forceinline__ int64_t slice_offset(const KeepIndex &k, int64_t lin) {
+  if (k.ndim == 0) return 0;
+  if (k.ndim == 1) return lin * k.strides[0];
+  return keep_offset(k, lin);
+}
 
 __global__ void __launch_bounds__(256) extremum_count_rows(const float *__restrict__ x, const float *__restrict__ m,
                                                            int *__restrict__ count, SliceScalars sc, int64_t L,
@@ -532,8 +538,8 @@ __global__ void __launch_bounds__(256) extremum_count_rows(const float *__restri
   __shared__ int warp_cnt[8];
   const int64_t row = blockIdx.x / chunks_per_row;
   const int c = int(blockIdx.x - row * chunks_per_row);
-  const float *p = x + keep_offset(sc.x_keep, row);
-  const float mv = m[keep_offset(sc.m_keep, row)];
+  const float *p = x + slice_offset(sc.x_keep, row);
+  const float mv = m[slice_offset(sc.m_keep, row)];
   const int64_t lo = int64_t(c) * chunk;
   int64_t hi = lo + chunk;
   if (hi > L) hi = L;
@@ -573,7 +579,7 @@ __global__ void __launch_bounds__(256) extremum_count_cols(const float *__restri
   int n[4] = {0, 0, 0, 0};
   float mv[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) mv[e] = (c0 + e < C) ? m[keep_offset(sc.m_keep, c0 + e)] : 0.0f;
+  for (int e = 0; e < 4; ++e) mv[e] = (c0 + e < C) ? m[slice_offset(sc.m_keep, c0 + e)] : 0.0f;
   if (c0 < C) {
     for (int64_t r = r_lo + warp; r < r_hi; r += 8) {
       const float *q = x + r * sR + c0;
@@ -604,46 +610,52 @@ __global__ void __launch_bounds__(256) extremum_count_cols(const float *__restri
 template <bool ROWS>
 __global__ void __launch_bounds__(256) extremum_apply(const float *__restrict__ x, const float *__restrict__ g,
                                                       const float *__restrict__ m, const int *__restrict__ count,
-                                                      float *__restrict__ out, SliceScalars sc, int64_t n_keep, int64_t L,
+                                                      float *__restrict__ out, SliceScalars sc, int64_t n_outer, int64_t L,
                                                       int64_t sR, int vec) {
-  // L = elements per slice (ROWS) or number of columns C (COLS)
-  const int64_t total = ROWS ? n_keep * L : n_keep /*rows*/ * L;
+  // ROWS: n_outer slices of L elements; COLS: n_outer rows of L columns (slice = column).
+  // total < 2^40 is guaranteed by the host; the common case fits 32-bit division.
+  const int64_t total = n_outer * L;
   const int64_t t = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
   if (t >= total) return;
-  const int64_t outer = t / L, inner = t - outer * L; // ROWS: (slice, j); COLS: (row i, column c)
-  float xv[4], res[4];
-  const float *px = ROWS ? x + keep_offset(sc.x_keep, outer) + inner : x + outer * sR + inner;
-  if (vec) {
-    float4 v = __ldcs(reinterpret_cast<const float4 *>(px));
-    xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
+  int64_t outer, inner;
+  if (total < (int64_t(1) << 32)) {
+    const uint32_t o32 = uint32_t(t) / uint32_t(L);
+    outer = o32;
+    inner = uint32_t(t) - o32 * uint32_t(L);
   } else {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) xv[e] = (t + e < total) ? (ROWS ? x[keep_offset(sc.x_keep, (t + e) / L) + (t + e) % L]
-                                                               : x[((t + e) / L) * sR + (t + e) % L])
-                                                        : 0.0f;
+    outer = t / L;
+    inner = t - outer * L;
   }
-  if (ROWS && vec) {
-    const float gv = g[keep_offset(sc.g_keep, outer)], mv = m[keep_offset(sc.m_keep, outer)];
-    const bool unique = count[outer] == 1;
+  float res[4];
+  if (vec) { // the four elements share `outer` (L % 4 == 0) and are contiguous in x
+    const float *px = ROWS ? x + slice_offset(sc.x_keep, outer) + inner : x + outer * sR + inner;
+    const float4 v = __ldcs(reinterpret_cast<const float4 *>(px));
+    const float xv[4] = {v.x, v.y, v.z, v.w};
+    if (ROWS) {
+      const float gv = g[slice_offset(sc.g_keep, outer)], mv = m[slice_offset(sc.m_keep, outer)];
+      const bool unique = count[outer] == 1;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) res[e] = gv * ((xv[e] == mv && unique) ? 1.0f : 0.0f);
-  } else {
+      for (int e = 0; e < 4; ++e) res[e] = gv * ((xv[e] == mv && unique) ? 1.0f : 0.0f);
+    } else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t idx = t + e;
-      const int64_t slice = ROWS ? idx / L : idx % L;
-      if (idx < total) {
-        const float gv = g[keep_offset(sc.g_keep, slice)], mv = m[keep_offset(sc.m_keep, slice)];
-        res[e] = gv * ((xv[e] == mv && count[slice] == 1) ? 1.0f : 0.0f);
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = inner + e;
+        const float gv = g[slice_offset(sc.g_keep, c)], mv = m[slice_offset(sc.m_keep, c)];
+        res[e] = gv * ((xv[e] == mv && count[c] == 1) ? 1.0f : 0.0f);
       }
     }
-  }
-  if (vec) {
     __stcs(reinterpret_cast<float4 *>(out + t), make_float4(res[0], res[1], res[2], res[3]));
-  } else {
+    return;
+  }
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      if (t + e < total) out[t + e] = res[e];
+  for (int e = 0; e < 4; ++e) {
+    const int64_t idx = t + e;
+    if (idx >= total) break;
+    const int64_t o = idx / L, i = idx - o * L;
+    const int64_t slice = ROWS ? o : i;
+    const float xv = ROWS ? x[slice_offset(sc.x_keep, o) + i] : x[o * sR + i];
+    const float gv = g[slice_offset(sc.g_keep, slice)], mv = m[slice_offset(sc.m_keep, slice)];
+    out[idx] = gv * ((xv == mv && count[slice] == 1) ? 1.0f : 0.0f);
   }
 }
 

@@ -56,7 +56,7 @@ NT_HD float nt_expm1_for_tanh(float a) {
   const int neg = (ua >> 31) != 0;
   // k: 0 for |a| <= 0.5 ln2, +-1 for |a| < 1.5 ln2, else trunc(a / ln2 +- 0.5)
   int k = (int)(invln2 * a + (neg ? -0.5f : 0.5f));
-  if (hx < 0x3F851592u) k = neg ? -1 : 1;
+  if (hx < 0x3F851592u) k = -1; // only negative arguments are this small (positive ones are >= 2)
   if (hx <= 0x3eb17218u) k = 0;
   const float t = (float)k;
   const float hi = a - t * ln2_hi;
@@ -75,9 +75,7 @@ NT_HD float nt_expm1_for_tanh(float a) {
     res = x - e;
   } else if (k == -1) {
     res = 0.5f * (x - e) - 0.5f;
-  } else if (k == 1) {
-    res = (x < -0.25f) ? -2.0f * (e - (x + 0.5f)) : 1.0f + 2.0f * (x - e);
-  } else if (k <= -2 || k > 56) {
+  } else if (k <= -2 || k > 56) { // (k == 1 cannot occur: a positive argument is >= 2, so k >= 3)
     float y = 1.0f - (e - x);
     y = nt_u2f(nt_f2u(y) + ((uint32_t)k << 23));
     res = y - 1.0f;
