@@ -404,6 +404,79 @@ def time_ops(nt, peaks: dict) -> dict:
     return out
 
 
+def reference_cuda_column() -> dict:
+    """Optional comparison column (--ref-cuda): the reference's OWN generic CUDA kernels, compiled for
+    sm_100 into oracle/_ref by oracle/Makefile, on this GPU through the reference's `_C` API.  Timed the
+    way the reference times itself (scripts/profile_ops.py:61-89): perf_counter around the call plus a
+    device sync, best of 5 after a warm-up.  Not part of the default run."""
+    from oracle import oracle as O
+
+    if not O.ref_available():
+        return {"unavailable": "oracle/_ref is not built"}
+    m = O.load_ref_module()
+    if not m.is_cuda_available():
+        return {"unavailable": "no CUDA device"}
+    F32, CPU, CUDA = m.Dtype.Float32, m.Device.Cpu, m.Device.Cuda
+    r = np.random.default_rng
+
+    def dev(a):
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        s_ = m.Storage.allocate(a.size, F32, CPU)
+        np.asarray(memoryview(s_))[:] = a.reshape(-1)
+        return s_.to(CUDA), a.shape
+
+    def view(st, shape, strides=None, offset=0):
+        if strides is None:
+            strides, acc = [], 1
+            for e in reversed(shape):
+                strides.insert(0, acc)
+                acc *= e
+        return m.TensorView(st, list(shape), list(strides), offset)
+
+    def best(fn, reps=5):
+        fn()
+        m.cuda_sync()
+        ts = []
+        for _ in range(reps):
+            t = time.perf_counter()
+            fn()
+            m.cuda_sync()
+            ts.append(time.perf_counter() - t)
+        return min(ts) * 1e3
+
+    out = {}
+    N = 4096
+    a, _ = dev(r(10).uniform(-1, 1, (N, N)))
+    b, _ = dev(r(11).uniform(-1, 1, (N, N)))
+    v, _ = dev(r(13).uniform(-1, 1, (N,)))
+    n_, _ = dev(r(14).standard_normal((N, N)))
+    va, vb = view(a, (N, N)), view(b, (N, N))
+    for name, fn, nbytes in (
+            ("add.contiguous", lambda: m.add(va, vb), 3 * N * N * 4),
+            ("add.broadcast_row", lambda: m.add(va, view(v, (N, N), (0, 1))), (2 * N * N + N) * 4),
+            ("add.transposed", lambda: m.add(va, view(b, (N, N), (1, N))), 3 * N * N * 4),
+            ("exp.forward", lambda: m.exp(view(n_, (N, N))), 2 * N * N * 4),
+            ("tanh.forward", lambda: m.tanh(view(n_, (N, N))), 2 * N * N * 4)):
+        ms = best(fn)
+        out[name] = {"ms": round(ms, 4), "GB/s": round(nbytes / ms / 1e6, 1)}
+    M = 8192
+    x, _ = dev(r(20).standard_normal((M, M)))
+    vx = view(x, (M, M))
+    for name, fn in (("sum.dim0", lambda: m.sum(vx, [0], F32)), ("sum.dim1", lambda: m.sum(vx, [1], F32)),
+                     ("sum.full", lambda: m.sum(vx, [0, 1], F32)), ("max.dim1", lambda: m.max(vx, [1]))):
+        ms = best(fn)
+        out[name] = {"ms": round(ms, 4), "GB/s": round(M * M * 4 / ms / 1e6, 1)}
+    flops = 2.0 * N * N * N
+    ms = best(lambda: m.matmul(va, vb), reps=3)
+    out["matmul.4096x4096x4096.forward"] = {"ms": round(ms, 3), "TFLOP/s": round(flops / ms / 1e9, 2)}
+    # both gradients multiply by a transposed VIEW and drop to the one-thread-per-output kernel
+    ms = best(lambda: m.matmul(va, view(b, (N, N), (1, N))), reps=1)
+    out["matmul.4096x4096x4096.grad_a"] = {"ms": round(ms, 3), "TFLOP/s": round(flops / ms / 1e9, 2)}
+    out["_notes"] = ("the reference's generic kernels (no sm_100 path exists in the reference) recompiled with "
+                     "-gencode arch=compute_100,code=sm_100; wall-clock perf_counter + device sync per call")
+    return out
+
+
 def product_arm(args, rank: int, local_rank: int, world: int) -> None:
     import nanotorch_b200 as nt
     import nanotorch_b200.nn as nn
@@ -591,6 +664,8 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         if world == 1 and not args.no_ops:
             line["ops"] = time_ops(nt, peaks)
             line["cpu_baseline"] = cpu_baseline_sample()
+        if world == 1 and args.ref_cuda:
+            line["reference_cuda"] = reference_cuda_column()
         print(json.dumps(line), flush=True)
     barrier()
     # graphs that captured collectives go before the communicator they use
@@ -653,6 +728,8 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op sweep and the CPU baseline sample")
+    ap.add_argument("--ref-cuda", action="store_true",
+                    help="also time the reference's own CUDA kernels (oracle/_ref) on this GPU for a comparison column")
     ap.add_argument("--case", default=None, help=f"run one small case for a profiler capture and exit: {PROFILE_CASES}")
     args = ap.parse_args()
     if args.case:

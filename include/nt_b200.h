@@ -148,6 +148,12 @@ int nt_exp(const nt_view *x, nt_storage **out);
 int nt_log(const nt_view *x, nt_storage **out);
 int nt_sqrt(const nt_view *x, nt_storage **out);
 int nt_tanh(const nt_view *x, nt_storage **out);
+/* fp32 tanh mode.  0 (default): the correctly rounded value, by one double-precision evaluation --
+ * within 2 ulp of the host libm's tanhf that the reference's CPU path calls (src/cpp/ops/unary_ops.cu:106).
+ * 1: that libm's algorithm restated operation for operation -- bit-for-bit equal to the reference's CPU
+ * result, at ~2.6x the instruction count. */
+int nt_set_tanh_mode(int mode);
+int nt_get_tanh_mode(void);
 int nt_sigmoid(const nt_view *x, nt_storage **out);
 int nt_neg(const nt_view *x, nt_storage **out);
 int nt_relu(const nt_view *x, nt_storage **out);

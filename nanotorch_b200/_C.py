@@ -491,6 +491,18 @@ def allocator_trim() -> None:
     _check(_lib.nt_allocator_trim())
 
 
+TANH_CORRECTLY_ROUNDED = 0
+TANH_BIT_EXACT_LIBM = 1
+
+
+def set_tanh_mode(mode: int) -> None:
+    _check(_lib.nt_set_tanh_mode(int(mode)))
+
+
+def get_tanh_mode() -> int:
+    return _lib.nt_get_tanh_mode()
+
+
 MATMUL_EXACT_FP32 = 0
 MATMUL_3XTF32 = 1
 MATMUL_FP32_UNFUSED = 2

@@ -3,6 +3,7 @@
 // off, so every functor rounds exactly where the reference's separate kernels round.
 #include "elementwise.cuh"
 #include "tanh_exact.h"
+#include "cr_math.h"
 
 namespace ntb {
 
@@ -56,34 +57,6 @@ template <class T> struct SqrtF {
   }
 };
 
-// ---- exp with |result - exact| <= 0.51 ulp, used where exp feeds further rounded steps (sigmoid):
-// e^x = 2^k * e^r with k = round(x/ln2), r = x - k*ln2 evaluated in double (|r| <= 0.347), e^r by
-// its Taylor polynomial to degree 9 (truncation < 2^-33), then one rounding to float.
-__device__ __forceinline__ float exp_f32_accurate(float xf) {
-  if (!(xf == xf)) return xf + xf;
-  if (xf > 88.72283935546875f) return __int_as_float(0x7f800000);
-  if (xf < -103.97208404541015625f) return 0.0f;
-  const double x = (double)xf;
-  const double kd = rint(x * 1.4426950408889634074);
-  const double r = fma(kd, -1.90821492927058770002e-10, fma(kd, -6.93147180369123816490e-01, x));
-  double p = 1.0 / 362880.0;
-  p = fma(p, r, 1.0 / 40320.0);
-  p = fma(p, r, 1.0 / 5040.0);
-  p = fma(p, r, 1.0 / 720.0);
-  p = fma(p, r, 1.0 / 120.0);
-  p = fma(p, r, 1.0 / 24.0);
-  p = fma(p, r, 1.0 / 6.0);
-  p = fma(p, r, 0.5);
-  p = fma(p, r, 1.0);
-  p = fma(p, r, 1.0);
-  const int k = (int)kd;
-  // scale by 2^k through the exponent field; k in [-150, 128], split so both factors are normal
-  const int k1 = k / 2, k2 = k - k1;
-  const double s1 = __longlong_as_double((long long)(1023 + k1) << 52);
-  const double s2 = __longlong_as_double((long long)(1023 + k2) << 52);
-  return (float)((p * s1) * s2);
-}
-
 template <class T> struct ExpF {
   using in_t = T;
   using out_t = T;
@@ -108,13 +81,24 @@ template <class T> struct SigmoidF {
   using in_t = T;
   using out_t = T;
   __device__ __forceinline__ T operator()(T a) const {
-    if constexpr (std::is_same_v<T, float>) return 1.0f / (1.0f + exp_f32_accurate(-a));
+    if constexpr (std::is_same_v<T, float>) return nt_sigmoid_f32(a); // correctly rounded, see cr_math.h
     else return 1.0 / (1.0 + exp(-a));
   }
 };
 
-// ---- tanh, fp32: bit-for-bit the host libm's algorithm, see tanh_exact.h
+// ---- tanh, fp32, two modes (nt_set_tanh_mode):
+//   0 (default)  correctly rounded through one double-precision evaluation (tanh_fast.h): within 2 ulp of
+//                the host libm, ~50 instructions per element;
+//   1            bit for bit the host libm's algorithm (tanh_exact.h), ~130 instructions per element.
 template <class T> struct TanhF {
+  using in_t = T;
+  using out_t = T;
+  __device__ __forceinline__ T operator()(T a) const {
+    if constexpr (std::is_same_v<T, float>) return nt_tanh_fast_f32(a);
+    else return tanh(a);
+  }
+};
+template <class T> struct TanhExactF {
   using in_t = T;
   using out_t = T;
   __device__ __forceinline__ T operator()(T a) const {
@@ -122,6 +106,7 @@ template <class T> struct TanhF {
     else return tanh(a);
   }
 };
+static std::atomic<int> g_tanh_mode{0};
 
 // ---- pow.  fp32: the small integer exponents that training uses are exact products / reciprocals
 // (<= 1 ulp from a correctly rounded powf); any other exponent goes through double precision.
@@ -412,9 +397,16 @@ int nt_sqrt(const nt_view *x, nt_storage **out) {
 }
 int nt_tanh(const nt_view *x, nt_storage **out) {
   NT_API_BEGIN
-  *out = unary_impl<TanhF, 0>(x, "tanh");
+  *out = (g_tanh_mode.load() == 1) ? unary_impl<TanhExactF, 0>(x, "tanh") : unary_impl<TanhF, 0>(x, "tanh");
   NT_API_END
 }
+int nt_set_tanh_mode(int mode) {
+  NT_API_BEGIN
+  if (mode != 0 && mode != 1) fail_invalid("tanh mode must be 0 (correctly rounded) or 1 (bit-exact host libm).");
+  g_tanh_mode.store(mode);
+  NT_API_END
+}
+int nt_get_tanh_mode(void) { return g_tanh_mode.load(); }
 int nt_sigmoid(const nt_view *x, nt_storage **out) {
   NT_API_BEGIN
   *out = unary_impl<SigmoidF, 0>(x, "sigmoid");

@@ -50,7 +50,7 @@ def test_binary_golden(nt, golden, op, layout):
         assert_bit_exact(got, want, "grad x2")
 
 
-UNARY_FWD_TOL = {"exp": 2, "neg": 0, "relu": 0, "tanh": 0, "sigmoid": 2, "log": 2, "sqrt": 0, "pow2": 2, "pow3.7": 2,
+UNARY_FWD_TOL = {"exp": 2, "neg": 0, "relu": 0, "tanh": 2, "sigmoid": 2, "log": 2, "sqrt": 0, "pow2": 2, "pow3.7": 2,
                  "powm1": 2}
 
 
@@ -86,7 +86,7 @@ def test_unary_golden(nt, golden, name):
 
 def test_special_values(nt, golden):
     x = dev(nt, golden["ew/special/in"])
-    for name, tol in [("exp", 2), ("relu", 0), ("tanh", 0), ("sigmoid", 2), ("neg", 0), ("pow2", 0)]:
+    for name, tol in [("exp", 2), ("relu", 0), ("tanh", 2), ("sigmoid", 2), ("neg", 0), ("pow2", 0)]:
         got = apply_unary(nt, name, x).numpy()
         want = golden[f"ew/special/{name}"]
         if tol == 0:
@@ -195,7 +195,7 @@ def test_binary_full_size(nt, port, big, op):
 
 
 @pytest.mark.parametrize("name,src,prim,e,tol", [("exp", "n", "exp", 0, 2), ("neg", "n", "neg", 0, 0),
-                                                 ("relu", "n", "relu", 0, 0), ("tanh", "n", "tanh", 0, 0),
+                                                 ("relu", "n", "relu", 0, 0), ("tanh", "n", "tanh", 0, 2),
                                                  ("sigmoid", "n", "sigmoid", 0, 2), ("log", "p", "log", 0, 2),
                                                  ("sqrt", "p", "sqrt", 0, 0), ("pow2", "a", "pow", 2.0, 2)])
 def test_unary_full_size(nt, port, big, name, src, prim, e, tol):
@@ -207,6 +207,24 @@ def test_unary_full_size(nt, port, big, name, src, prim, e, tol):
     else:
         worst = assert_ulp(got, want, tol, name)
         print(f"{name}: max ulp distance to the CPU oracle {worst}, mismatching fraction {(got != want).mean():.2e}")
+
+
+def test_tanh_bit_exact_mode(nt, port, big, golden):
+    """Mode 1 restates the host libm's tanhf operation for operation: identical bits to the CPU oracle,
+    on the seeded [4096, 4096] input, on the special values and on a strided view."""
+    h, d = big
+    nt._C.set_tanh_mode(nt._C.TANH_BIT_EXACT_LIBM)
+    try:
+        assert_bit_exact(nt.tanh(d["n"]).numpy(), port.unary("tanh", h["n"]), "4096^2")
+        assert_bit_exact(nt.tanh(d["n"].T[::3, 5:]).numpy(), port.unary("tanh", h["n"].T[::3, 5:]), "strided view")
+        assert_bit_exact(nt.tanh(dev(nt, golden["ew/special/in"])).numpy(), golden["ew/special/tanh"], "special values")
+        wide = np.random.default_rng(3).uniform(-25, 25, (1 << 20,)).astype(np.float32)
+        assert_bit_exact(nt.tanh(dev(nt, wide)).numpy(), port.unary("tanh", wide), "U(-25, 25)")
+    finally:
+        nt._C.set_tanh_mode(nt._C.TANH_CORRECTLY_ROUNDED)
+    # default mode: the correctly rounded value (float64 tanh rounded once)
+    got = nt.tanh(d["n"]).numpy()
+    assert_bit_exact(got, np.tanh(h["n"].astype(np.float64)).astype(np.float32), "correctly rounded")
 
 
 @pytest.mark.parametrize("name", ["relu", "tanh", "sigmoid", "exp", "log", "sqrt", "pow2"])

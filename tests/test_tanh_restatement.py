@@ -50,3 +50,78 @@ def test_restated_tanh_is_bit_exact_with_host_libm(tmp_path):
     sys.stdout.write(out.stdout)
     assert out.returncode == 0, out.stdout
     assert "mismatches=0" in out.stdout
+
+
+FAST_SRC = r"""
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include "cr_math.h"
+static float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static long key(float f) { int32_t i; memcpy(&i, &f, 4); return i < 0 ? -(long)(i & 0x7fffffff) : i; }
+int main(void) {
+  long n = 0, over2 = 0, not_cr = 0, libm_vs_cr_max = 0;
+  for (uint64_t u = 0; u < 0x100000000ull; u += 41) {
+    float x = u2f((uint32_t)u);
+    if (isnan(x)) continue;
+    float libm = tanhf(x), fast = nt_tanh_fast_f32(x), cr = (float)tanh((double)x);
+    if (labs(key(libm) - key(fast)) > 2) over2++;
+    if (key(fast) != key(cr)) not_cr++;
+    long d = labs(key(libm) - key(cr));
+    if (d > libm_vs_cr_max) libm_vs_cr_max = d;
+    n++;
+  }
+  printf("checked=%ld over_2ulp=%ld differs_from_correctly_rounded=%ld libm_vs_cr_max=%ld\n", n, over2, not_cr, libm_vs_cr_max);
+  return (over2 != 0) || (not_cr != 0);
+}
+"""
+
+
+def test_default_tanh_is_correctly_rounded_and_within_2ulp_of_host_libm(tmp_path):
+    """cr_math.h (the default mode): equal to float(tanh(double(x))) for every argument of the sweep,
+    hence within 2 ulp of the host libm, whose own distance to the correctly rounded value is at most 2."""
+    src = tmp_path / "tanh_fast_check.c"
+    src.write_text(FAST_SRC)
+    exe = tmp_path / "tanh_fast_check"
+    subprocess.run(["gcc", "-O2", "-fno-fast-math", "-ffp-contract=off", f"-I{REPO / 'nanotorch_b200' / 'csrc'}",
+                    "-o", str(exe), str(src), "-lm"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    sys.stdout.write(out.stdout)
+    assert out.returncode == 0, out.stdout
+    assert "over_2ulp=0" in out.stdout and "differs_from_correctly_rounded=0" in out.stdout
+
+
+SIGMOID_SRC = r"""
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include "cr_math.h"
+static float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
+static long key(float f) { int32_t i; memcpy(&i, &f, 4); return i < 0 ? -(long)(i & 0x7fffffff) : i; }
+int main(void) {
+  long n = 0, over2 = 0, worst = 0;
+  for (uint64_t u = 0; u < 0x100000000ull; u += 53) {
+    float x = u2f((uint32_t)u);
+    if (isnan(x)) continue;
+    float ref = 1.0f / (1.0f + expf(-x));   /* the reference's functor on the host libm */
+    float got = nt_sigmoid_f32(x);
+    long d = labs(key(ref) - key(got));
+    if (d > worst) worst = d;
+    if (d > 2) { if (over2 < 5) printf("x=%a ref=%a got=%a\n", x, ref, got); over2++; }
+    n++;
+  }
+  printf("checked=%ld over_2ulp=%ld worst=%ld\n", n, over2, worst);
+  return over2 != 0;
+}
+"""
+
+
+def test_sigmoid_within_2ulp_of_the_reference_expression_on_host_libm(tmp_path):
+    src = tmp_path / "sigmoid_check.c"
+    src.write_text(SIGMOID_SRC)
+    exe = tmp_path / "sigmoid_check"
+    subprocess.run(["gcc", "-O2", "-fno-fast-math", "-ffp-contract=off", f"-I{REPO / 'nanotorch_b200' / 'csrc'}",
+                    "-o", str(exe), str(src), "-lm"], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    sys.stdout.write(out.stdout)
+    assert out.returncode == 0, out.stdout
