@@ -679,7 +679,7 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
-PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "exp4096",
+PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
                  "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192")
 
 
@@ -704,9 +704,11 @@ def profile_case(name: str, launches: int = 3) -> None:
         m = x.max((1,)).reshape(8192, 1).expand(8192, 8192)
         g = dev(np.ones((8192,))).reshape(8192, 1).expand(8192, 8192)
         fn = lambda: _C.extremum_backward(g._C_view, x._C_view, m._C_view, [1])  # noqa: E731
-    elif name in ("tanh4096", "exp4096", "sigmoid4096"):
+    elif name in ("tanh4096", "tanh4096_exact", "exp4096", "sigmoid4096"):
         x = dev(r(14).standard_normal((4096, 4096)))
-        kern = {"tanh4096": _C.tanh, "exp4096": _C.exp, "sigmoid4096": _C.sigmoid}[name]
+        if name == "tanh4096_exact":
+            _C.set_tanh_mode(_C.TANH_BIT_EXACT_LIBM)
+        kern = {"tanh4096": _C.tanh, "tanh4096_exact": _C.tanh, "exp4096": _C.exp, "sigmoid4096": _C.sigmoid}[name]
         fn = lambda: kern(x._C_view)  # noqa: E731
     elif name.startswith("sum8192"):
         x = dev(r(20).standard_normal((8192, 8192)))
