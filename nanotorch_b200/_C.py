@@ -506,6 +506,7 @@ def get_tanh_mode() -> int:
 MATMUL_EXACT_FP32 = 0
 MATMUL_3XTF32 = 1
 MATMUL_FP32_UNFUSED = 2
+MATMUL_3XTF32_SINGLE_CHAIN = 3
 
 
 def set_matmul_mode(mode: int) -> None:

@@ -366,6 +366,199 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 }
 
 // ---------------------------------------------------------------------------------------------
+// Variant with promoted accumulation (matmul mode 1, the default; the kernel above is mode 3).
+//
+// The tensor core adds into its fp32 accumulator with round-toward-zero, so a long accumulation chain
+// carries a bias that grows with its length.  Here a chain is only TC_PERIOD_KB k-blocks (128 values of
+// k, 48 MMAs) long: the two 256-column halves of tensor memory alternate as the accumulator of
+// successive periods; while the MMA warp fills one, eight epilogue warps drain the other with
+// tcgen05.ld and add it -- round-to-nearest -- into running sums they keep in registers (128 per
+// thread).  The result has the error of an ordinary fp32 summation (~1e-6 relative at K = 4096).
+constexpr int TC_PERIOD_KB = 8; // k-blocks (of TC_BK = 16) per accumulation chain
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+        "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+        "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+        "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(320, 1)
+gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE_BYTES;
+  // full[s] at +8 s, empty[s] at +32 + 8 s, acc_full[b] at +64 + 8 b, acc_empty[b] at +80 + 8 b, tmem slot at +96
+  const uint32_t full0 = bar_base, empty0 = bar_base + 32, acc_full0 = bar_base + 64, acc_empty0 = bar_base + 80;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + (bar_base - smem_u32(smem_raw)) + 96);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN, b = blockIdx.z;
+  const int num_periods = (g.num_kb + TC_PERIOD_KB - 1) / TC_PERIOD_KB;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(acc_full0 + 8 * i, 1);
+      mbar_init(acc_empty0 + 8 * i, 8); // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t phase = 0;
+      int s = 0;
+      for (int kb = 0; kb < g.num_kb; ++kb) {
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) {
+          atomicExch(g.error_flag, 1);
+          break;
+        }
+        const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+        mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+        const int k = kb * TC_BK;
+        tma_load_3d(st, &map_a, full0 + 8 * s, k, m0, b);
+        tma_load_3d(st + TC_A_PLANE_BYTES, &map_a, full0 + 8 * s, k, m0, g.batch + b);
+        tma_load_3d(st + 2 * TC_A_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, b);
+        tma_load_3d(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, g.batch + b);
+        if (++s == TC_STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t phase = 0;
+      int s = 0, kb = 0;
+      bool ok = true;
+      for (int p = 0; p < num_periods && ok; ++p) {
+        const int buf = p & 1;
+        // the epilogue must have drained this half (two periods ago) before it is overwritten
+        if (!mbar_wait(acc_empty0 + 8 * buf, ((p >> 1) & 1) ^ 1)) {
+          atomicExch(g.error_flag, 4);
+          ok = false;
+          break;
+        }
+        tcgen05_fence_after();
+        const uint32_t d = tmem_acc + uint32_t(buf * TC_BN);
+        const int kb_end = min(kb + TC_PERIOD_KB, g.num_kb);
+        bool first = true;
+        for (; kb < kb_end; ++kb) {
+          if (!mbar_wait(full0 + 8 * s, phase)) {
+            atomicExch(g.error_flag, 2);
+            ok = false;
+            break;
+          }
+          tcgen05_fence_after();
+          const uint32_t st = smem_base + s * TC_STAGE_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < TC_BK / TC_UMMA_K; ++ks) {
+            const uint32_t koff = ks * TC_UMMA_K * 4;
+            const uint64_t a_hi = umma_desc_sw64(st + koff);
+            const uint64_t a_lo = umma_desc_sw64(st + TC_A_PLANE_BYTES + koff);
+            const uint64_t b_hi = umma_desc_sw64(st + 2 * TC_A_PLANE_BYTES + koff);
+            const uint64_t b_lo = umma_desc_sw64(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES + koff);
+            // small terms first, the large one last
+            umma_tf32(d, a_hi, b_lo, first ? 0u : 1u);
+            umma_tf32(d, a_lo, b_hi, 1);
+            umma_tf32(d, a_hi, b_hi, 1);
+            first = false;
+          }
+          umma_commit(empty0 + 8 * s);
+          if (++s == TC_STAGES) {
+            s = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(acc_full0 + 8 * buf);
+      }
+      if (!ok) { // release the epilogue warps from whatever they wait on
+        for (int i = 0; i < 2; ++i)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_full0 + 8 * i) : "memory");
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue, warps 2..9
+    const int quad = warp & 3;          // 32-lane group of tensor memory this warp may read
+    const int half = (warp - 2) >> 2;   // which 128 of the 256 columns
+    float sum[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) sum[i] = 0.0f;
+    bool ok = true;
+    for (int p = 0; p < num_periods; ++p) {
+      const int buf = p & 1;
+      if (ok && !mbar_wait(acc_full0 + 8 * buf, (p >> 1) & 1)) {
+        atomicExch(g.error_flag, 3);
+        ok = false;
+      }
+      if (!ok || *reinterpret_cast<volatile int *>(g.error_flag) != 0) {
+        ok = false;
+        break;
+      }
+      tcgen05_fence_after();
+      const uint32_t taddr = tmem_acc + (uint32_t(quad * 32) << 16) + uint32_t(buf * TC_BN + half * 128);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(taddr + uint32_t(c * 32), v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sum[c * 32 + e] = sum[c * 32 + e] + __uint_as_float(v[e]);
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
+    }
+    const int64_t m = int64_t(m0) + quad * 32 + lane;
+    if (ok && m < g.M) {
+      float *crow = g.C + (int64_t(b) * g.M + m) * g.N;
+      const int64_t n = int64_t(n0) + half * 128;
+#pragma unroll
+      for (int q = 0; q < 32; ++q) {
+        const int64_t nn = n + 4 * q;
+        if (g.c_vec && nn + 3 < g.N) {
+          *reinterpret_cast<float4 *>(crow + nn) = make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            if (nn + e < g.N) crow[nn + e] = sum[4 * q + e];
+        }
+      }
+    }
+  }
+
+  if (*reinterpret_cast<volatile int *>(g.error_flag) != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000) {
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(512) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
 // Host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -440,6 +633,9 @@ static void launch_split(const float *src, float *planes, int64_t batch, int64_t
   check_launch("split_pack");
 }
 
+static std::atomic<int> g_promoted{1};
+void gemm_tc_set_promoted(bool on) { g_promoted.store(on ? 1 : 0); }
+
 bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_t M, int64_t N, int64_t K,
                  int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn) {
   // limits of one launch / one tensor map
@@ -449,6 +645,8 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
   static bool configured = false;
   if (!configured) {
     NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(TC_SMEM_BYTES)));
+    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_promoted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(TC_SMEM_BYTES)));
     configured = true;
   }
   const int64_t Kp = ceil_div(K, 32) * 32;
@@ -470,7 +668,10 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
     g.error_flag = error_flag_ptr();
     dim3 grid{unsigned(ceil_div(N, TC_BN)), unsigned(ceil_div(M, TC_BM)), unsigned(batch)};
     matmul_profile_begin();
-    gemm_3xtf32_kernel<<<grid, 192, TC_SMEM_BYTES, stream()>>>(map_a, map_b, g);
+    if (g_promoted.load())
+      gemm_3xtf32_promoted_kernel<<<grid, 320, TC_SMEM_BYTES, stream()>>>(map_a, map_b, g);
+    else
+      gemm_3xtf32_kernel<<<grid, 192, TC_SMEM_BYTES, stream()>>>(map_a, map_b, g);
     matmul_profile_end();
     check_launch("gemm_3xtf32_kernel");
   } catch (...) {

@@ -1,7 +1,8 @@
 // nt_matmul: batched C[..., M, N] = A[..., M, K] x B[..., K, N] over arbitrary strided views.
 //
 // fp32 has three modes (nt_set_matmul_mode):
-//   1 (default) 3xTF32 on the tcgen05 tensor cores, see gemm_tc.cu;
+//   1 (default) 3xTF32 on the tcgen05 tensor cores with promoted accumulation, see gemm_tc.cu;
+//   3           3xTF32 with one accumulation chain per output (3 % faster, ~10x the rounding bias);
 //   0           exact FP32 on the CUDA cores: 128x128x16 shared-memory tiles, 8x8 register
 //               micro-tiles, register-prefetch double buffering, one FMA per multiply-add,
 //               accumulated in ascending k -- the rounding of the reference's CUDA kernels
@@ -20,6 +21,7 @@ namespace ntb {
 // implemented in gemm_tc.cu; returns false when the shape/layout is outside what it supports
 bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_t M, int64_t N, int64_t K,
                  int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn);
+void gemm_tc_set_promoted(bool on);
 
 static std::atomic<int> g_matmul_mode{1};
 
@@ -294,8 +296,10 @@ extern "C" {
 
 int nt_set_matmul_mode(int mode) {
   NT_API_BEGIN
-  if (mode < 0 || mode > 2) fail_invalid("matmul mode must be 0 (exact fp32), 1 (3xTF32) or 2 (fp32, unfused multiply-add).");
+  if (mode < 0 || mode > 3)
+    fail_invalid("matmul mode must be 0 (exact fp32), 1 (3xTF32), 2 (fp32, unfused multiply-add) or 3 (3xTF32, single accumulation chain).");
   g_matmul_mode.store(mode);
+  gemm_tc_set_promoted(mode == 1);
   NT_API_END
 }
 int nt_get_matmul_mode(void) { return g_matmul_mode.load(); }
@@ -345,7 +349,7 @@ int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
     g.batch = bi;
     const int mode = g_matmul_mode.load();
     bool done = false;
-    if (mode == 1 && K > 0) {
+    if ((mode == 1 || mode == 3) && K > 0) {
       // the tensor-core path takes a single (collapsed) batch stride per operand
       int64_t a_sb = 0, b_sb = 0;
       bool single = true;

@@ -129,6 +129,8 @@ def test_matmul_mode_switch(nt):
     assert _C.get_matmul_mode() == 1
     _C.set_matmul_mode(0)
     assert _C.get_matmul_mode() == 0
+    _C.set_matmul_mode(3)
+    assert _C.get_matmul_mode() == 3
     _C.set_matmul_mode(1)
     with pytest.raises(ValueError):
         _C.set_matmul_mode(7)

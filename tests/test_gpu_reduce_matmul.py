@@ -147,7 +147,7 @@ def test_reductions_full_size(nt, port, big, axes):
 MM_CASES = ["2d", "batched", "bcast_batch", "vec_mat", "mat_vec", "vec_vec", "odd"]
 
 
-@pytest.mark.parametrize("mode", [2, 0, 1])
+@pytest.mark.parametrize("mode", [2, 0, 1, 3])
 @pytest.mark.parametrize("case", MM_CASES)
 def test_matmul_golden(nt, golden, case, mode):
     nt._C.set_matmul_mode(mode)
@@ -183,7 +183,7 @@ def test_matmul_layouts_vs_oracle(nt, port, dims):
     for lname, ha, hb, va, vb in _mm_views(rng, M, K, N):
         want = port.matmul(va(ha), vb(hb))
         bound = np.abs(va(ha)).astype(np.float64) @ np.abs(vb(hb)).astype(np.float64)
-        for mode in (2, 0, 1):
+        for mode in (2, 0, 1, 3):
             nt._C.set_matmul_mode(mode)
             try:
                 got = (va(dev(nt, ha)) @ vb(dev(nt, hb))).numpy()
@@ -230,7 +230,7 @@ def test_matmul_full_size(nt, shape):
     rows = np.random.default_rng(33).choice(M, 48, replace=False)
     cols = np.random.default_rng(34).choice(N, 48, replace=False)
     krows = np.random.default_rng(35).choice(K, 48, replace=False)
-    for mode in (1, 0):
+    for mode in (1, 3, 0):
         nt._C.set_matmul_mode(mode)
         try:
             ta, tb = dev(nt, A, True), dev(nt, B, True)
@@ -245,7 +245,8 @@ def test_matmul_full_size(nt, shape):
         assert_scaled(gB[krows], A64[:, krows].T @ G64, np.abs(A64[:, krows].T) @ np.abs(G64), 1e-4, f"grad B mode {mode}")
         rel = np.abs(C[rows] - A64[rows] @ B64).max() / np.abs(A64[rows] @ B64).max()
         print(f"mode {mode} {shape}: max|C - C64| / max|C64| = {rel:.2e}")
-        assert rel < 1e-4  # the stated tolerance, also in its plain max-relative reading
+        # the stated tolerance in its plain max-relative reading; the default mode holds fp32 accuracy
+        assert rel < (1e-4 if mode == 3 else 3e-6)
     del cols
 
 
