@@ -186,13 +186,13 @@ int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float 
 int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out);
 /* fp32 product mode.
  *   0  exact FP32 on the CUDA cores (FMA, sequential in k: the rounding of the reference's CUDA kernels);
- *   1  (default) 3xTF32 on the tcgen05 tensor cores with promoted accumulation: chains of 128 values of k
+ *   1  (default) 3xTF32 on the tcgen05 tensor cores with promoted accumulation: chains of 256 values of k
  *      accumulate in tensor memory, their sums are added round-to-nearest in registers -- the error of an
- *      ordinary fp32 summation (~1e-6 relative at K = 4096);
+ *      ordinary fp32 summation (2e-6 of max|C| at K = 4096 and at K = 16384);
  *   2  FP32 on the CUDA cores with separate multiply and add, sequential in k: bit-for-bit the reference's
  *      CPU loop (src/cpp/ops/matmul.cu:31-45);
- *   3  3xTF32 with a single accumulation chain per output: ~3 % faster than mode 1; the tensor core's
- *      round-toward-zero accumulate then shows as a bias of ~1e-5 relative at K = 4096. */
+ *   3  3xTF32 with a single accumulation chain per output: ~1 % faster than mode 1; the tensor core's
+ *      round-toward-zero accumulate then shows as a bias of 1e-5 of max|C| at K = 4096, 4e-5 at 16384. */
 int nt_set_matmul_mode(int mode);
 int nt_get_matmul_mode(void);
 

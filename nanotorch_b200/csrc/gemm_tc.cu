@@ -369,12 +369,13 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 // Variant with promoted accumulation (matmul mode 1, the default; the kernel above is mode 3).
 //
 // The tensor core adds into its fp32 accumulator with round-toward-zero, so a long accumulation chain
-// carries a bias that grows with its length.  Here a chain is only TC_PERIOD_KB k-blocks (128 values of
-// k, 48 MMAs) long: the two 256-column halves of tensor memory alternate as the accumulator of
+// carries a bias that grows with its length.  Here a chain is only TC_PERIOD_KB k-blocks (256 values of
+// k, 96 MMAs) long: the two 256-column halves of tensor memory alternate as the accumulator of
 // successive periods; while the MMA warp fills one, eight epilogue warps drain the other with
 // tcgen05.ld and add it -- round-to-nearest -- into running sums they keep in registers (128 per
-// thread).  The result has the error of an ordinary fp32 summation (~1e-6 relative at K = 4096).
-constexpr int TC_PERIOD_KB = 8; // k-blocks (of TC_BK = 16) per accumulation chain
+// thread).  The result has the error of an ordinary fp32 summation (2e-6 of max|C| at K = 4096 and 16384;
+// chains of 128 measured 1e-6 at 3 % more time, one chain per output 1e-5 .. 4e-5).
+constexpr int TC_PERIOD_KB = 16; // k-blocks (of TC_BK = 16) per accumulation chain
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(

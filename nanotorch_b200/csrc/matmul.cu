@@ -2,7 +2,7 @@
 //
 // fp32 has three modes (nt_set_matmul_mode):
 //   1 (default) 3xTF32 on the tcgen05 tensor cores with promoted accumulation, see gemm_tc.cu;
-//   3           3xTF32 with one accumulation chain per output (3 % faster, ~10x the rounding bias);
+//   3           3xTF32 with one accumulation chain per output (1 % faster, 5-20x the rounding bias);
 //   0           exact FP32 on the CUDA cores: 128x128x16 shared-memory tiles, 8x8 register
 //               micro-tiles, register-prefetch double buffering, one FMA per multiply-add,
 //               accumulated in ascending k -- the rounding of the reference's CUDA kernels
