@@ -98,11 +98,15 @@ __global__ void __launch_bounds__(256) ew_contig(F f, typename F::out_t *out, co
 // VEC == 4: a thread owns UNROLL groups of 4 consecutive elements of the innermost dim (groups of
 // one block are interleaved so that a warp touches consecutive vectors); all loads are issued before
 // the first use.  VEC == 1: one element per thread, any dtype.
-template <class IDX, int NOPS>
+// ND > 0: the number of collapsed dims is known at compile time (the loop unrolls and every extent,
+// reciprocal and stride is read straight from the constant bank); ND == 0: any ndim.
+template <class IDX, int NOPS, int ND = 0>
 __device__ __forceinline__ void ew_offsets(const EwParams &p, IDX lin, int64_t (&off)[NOPS]) {
 #pragma unroll
   for (int o = 0; o < NOPS; ++o) off[o] = 0;
-  for (int d = p.ndim - 1; d >= 0; --d) {
+  const int nd = (ND > 0) ? ND : p.ndim;
+#pragma unroll
+  for (int d = nd - 1; d >= 0; --d) {
     IDX ext = IDX(p.shape[d]);
     IDX q;
     if constexpr (sizeof(IDX) == 4) // multiply-high by a precomputed reciprocal instead of a division
@@ -133,7 +137,7 @@ inline void ew_fast_divisor(int64_t d, uint32_t *mul, uint32_t *shift) {
   *shift = uint32_t(p - 32);
 }
 
-template <class F, int NIN, int VEC, class IDX>
+template <class F, int NIN, int VEC, class IDX, int ND = 0>
 __global__ void __launch_bounds__(256) ew_strided(F f, EwParams p) {
   using TI = typename F::in_t;
   using TO = typename F::out_t;
@@ -153,7 +157,7 @@ __global__ void __launch_bounds__(256) ew_strided(F f, EwParams p) {
     static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "vector path is for 4-byte types");
     constexpr int UNROLL = 4;
     const int64_t nvec = p.numel / VEC;
-    const int last = p.ndim - 1;
+    const int last = ((ND > 0) ? ND : p.ndim) - 1;
     const int64_t base = (int64_t(blockIdx.x) * UNROLL) * blockDim.x + threadIdx.x;
     TI v[UNROLL][NIN][4];
     int64_t out_off[UNROLL];
@@ -162,7 +166,7 @@ __global__ void __launch_bounds__(256) ew_strided(F f, EwParams p) {
       const int64_t t = base + int64_t(u) * blockDim.x;
       if (t >= nvec) continue;
       int64_t off[NIN + 1];
-      ew_offsets<IDX, NIN + 1>(p, IDX(t) * VEC, off);
+      ew_offsets<IDX, NIN + 1, ND>(p, IDX(t) * VEC, off);
       out_off[u] = off[0];
 #pragma unroll
       for (int o = 0; o < NIN; ++o) {
@@ -435,7 +439,9 @@ template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NI
   if constexpr (VECTOR_TYPES) {
     if (vec4) {
       int64_t blocks = ceil_div(it.numel / 4, 256 * 4);
-      if (idx32)
+      if (idx32 && p.ndim == 2) // the common case ([R, C] with a broadcast or sliced operand): unrolled index math
+        ew_strided<F, NIN, 4, uint32_t, 2><<<unsigned(blocks), 256, 0, st>>>(f, p);
+      else if (idx32)
         ew_strided<F, NIN, 4, uint32_t><<<unsigned(blocks), 256, 0, st>>>(f, p);
       else
         ew_strided<F, NIN, 4, uint64_t><<<unsigned(blocks), 256, 0, st>>>(f, p);
