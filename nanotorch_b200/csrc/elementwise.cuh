@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(256) ew_tile2d(F f, EwParams p) {
         if (j < nJ) {
           const TI *q = src + j * sJ + i;
           if (p.vec_mode[o + 1] == 1 && i + 3 < nI) {
-            float4 x = *reinterpret_cast<const float4 *>(q);
+            float4 x = __ldcs(reinterpret_cast<const float4 *>(q));
             const TI *px = reinterpret_cast<const TI *>(&x);
 #pragma unroll
             for (int e = 0; e < 4; ++e) tile[slot][ty + 16 * r][4 * tx + e] = px[e];
@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(256) ew_tile2d(F f, EwParams p) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) v[o][e] = x;
         } else if (p.vec_mode[o + 1] == 1 && full) {
-          float4 x = *reinterpret_cast<const float4 *>(src + j);
+          float4 x = __ldcs(reinterpret_cast<const float4 *>(src + j));
           const TI *px = reinterpret_cast<const TI *>(&x);
 #pragma unroll
           for (int e = 0; e < 4; ++e) v[o][e] = px[e];
@@ -316,7 +316,7 @@ __global__ void __launch_bounds__(256) ew_tile2d(F f, EwParams p) {
     }
     TO *q = dst + i * oI + j * oJ;
     if (p.vec_mode[0] == 1 && full) {
-      *reinterpret_cast<float4 *>(q) = *reinterpret_cast<const float4 *>(res);
+      __stcs(reinterpret_cast<float4 *>(q), *reinterpret_cast<const float4 *>(res));
     } else {
 #pragma unroll
       for (int e = 0; e < 4; ++e)

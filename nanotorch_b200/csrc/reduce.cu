@@ -659,6 +659,37 @@ __global__ void __launch_bounds__(256) extremum_apply(const float *__restrict__ 
   }
 }
 
+// Vector form of extremum_apply: a CTA owns 1024 consecutive elements of ONE outer index (a slice for
+// ROWS, a matrix row for COLS), so the outer index and -- for ROWS -- the slice's g, m and count are
+// block-uniform and no thread divides anything.
+template <bool ROWS>
+__global__ void __launch_bounds__(256) extremum_apply_vec(const float *__restrict__ x, const float *__restrict__ g,
+                                                          const float *__restrict__ m, const int *__restrict__ count,
+                                                          float *__restrict__ out, SliceScalars sc, int64_t L, int64_t sR,
+                                                          int chunks) {
+  const int64_t outer = blockIdx.x / chunks;
+  const int64_t inner = int64_t(blockIdx.x - outer * chunks) * 1024 + threadIdx.x * 4;
+  if (inner >= L) return;
+  const float *px = ROWS ? x + slice_offset(sc.x_keep, outer) + inner : x + outer * sR + inner;
+  const float4 v = __ldcs(reinterpret_cast<const float4 *>(px));
+  const float xv[4] = {v.x, v.y, v.z, v.w};
+  float res[4];
+  if (ROWS) {
+    const float gv = g[slice_offset(sc.g_keep, outer)], mv = m[slice_offset(sc.m_keep, outer)];
+    const bool unique = count[outer] == 1;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) res[e] = gv * ((xv[e] == mv && unique) ? 1.0f : 0.0f);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t c = inner + e;
+      const float gv = g[slice_offset(sc.g_keep, c)], mv = m[slice_offset(sc.m_keep, c)];
+      res[e] = gv * ((xv[e] == mv && count[c] == 1) ? 1.0f : 0.0f);
+    }
+  }
+  __stcs(reinterpret_cast<float4 *>(out + outer * L + inner), make_float4(res[0], res[1], res[2], res[3]));
+}
+
 // Returns false when the views do not have one of the two shapes above (the caller then composes).
 static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt_view *m, const int64_t *axes,
                                     int32_t n_axes, float *out) {
@@ -715,7 +746,11 @@ static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt
     check_launch("extremum_count_rows");
     bool vec = (L % 4 == 0) && aligned16(xp) && aligned16(out);
     for (int k = 0; k < sc.x_keep.ndim; ++k) vec = vec && (sc.x_keep.strides[k] % 4 == 0);
-    extremum_apply<true><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, pl.n_keep, L, 0, vec ? 1 : 0);
+    const int64_t vchunks = ceil_div(L, 1024);
+    if (vec && pl.n_keep * vchunks <= 0x7fffffffLL)
+      extremum_apply_vec<true><<<unsigned(pl.n_keep * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, L, 0, int(vchunks));
+    else
+      extremum_apply<true><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, pl.n_keep, L, 0, vec ? 1 : 0);
     check_launch("extremum_apply");
   } else {
     const int64_t R = pl.n_drop, C = pl.n_keep, sR = pl.drop.strides[0];
@@ -734,7 +769,11 @@ static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt
     dim3 grid{unsigned(tiles), unsigned(row_blocks), 1};
     extremum_count_cols<<<grid, 256, 0, st>>>(xp, mp, count, sc, R, C, sR, rows_per_block, vec ? 1 : 0);
     check_launch("extremum_count_cols");
-    extremum_apply<false><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, R, C, sR, vec ? 1 : 0);
+    const int64_t vchunks = ceil_div(C, 1024);
+    if (vec && R * vchunks <= 0x7fffffffLL)
+      extremum_apply_vec<false><<<unsigned(R * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, C, sR, int(vchunks));
+    else
+      extremum_apply<false><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, R, C, sR, vec ? 1 : 0);
     check_launch("extremum_apply");
   }
   device_free(count, rounded);
