@@ -137,14 +137,14 @@ def reference_arm(args, rank: int) -> None:
     rng = np.random.default_rng(40)
     X = rng.standard_normal((batch, WIDTH)).astype(np.float32)
     Y = np.random.default_rng(41).standard_normal((batch, WIDTH)).astype(np.float32)
-    budget_s = 150.0
+    limit_s = 150.0
     times = []
     total = args.warmup + args.steps
     for i in range(total):
         t = time.perf_counter()
         O.mlp_step(oracle, params, X, Y, LR, "tanh")
         dt = time.perf_counter() - t
-        if i == 0 and dt * total > budget_s and batch > 1:
+        if i == 0 and dt * total > limit_s and batch > 1:
             batch = 1
             X, Y = X[:1], Y[:1]
         if i >= args.warmup:
@@ -168,7 +168,7 @@ def reference_arm(args, rank: int) -> None:
     print(json.dumps(line))
 
 
-def cpu_baseline_sample(budget_s: float = 20.0) -> dict:
+def cpu_baseline_sample(limit_s: float = 20.0) -> dict:
     """Rank 0, N = 1: one step of the reference's CPU path on a batch of 2 rows of the workload."""
     from oracle import oracle as O
 
@@ -184,7 +184,7 @@ def cpu_baseline_sample(budget_s: float = 20.0) -> dict:
     Y = np.random.default_rng(41).standard_normal((batch, WIDTH)).astype(np.float32)
     times = []
     t_start = time.perf_counter()
-    while len(times) < 3 and (time.perf_counter() - t_start) < budget_s:
+    while len(times) < 3 and (time.perf_counter() - t_start) < limit_s:
         t = time.perf_counter()
         O.mlp_step(oracle, params, X, Y, LR, "tanh")
         times.append(time.perf_counter() - t)

@@ -2,7 +2,7 @@
 native module, CPU path) on seeded inputs.  Run where the reference checkout and oracle/_ref exist:
 
     make -C oracle ref                      # builds oracle/_ref/_C*.so from the reference sources
-    python tests/golden/make_golden.py --ref /root/reference
+    python tests/golden/make_golden.py --ref <reference checkout>
 
 The reference package is imported from a scratch directory that only holds symlinks to the
 reference's .py files plus the built native module; nothing is copied into this repository except
@@ -231,7 +231,8 @@ def rng_cases(nt, out: dict):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("NT_REFERENCE", "/root/reference"),
+                    help="path of the reference checkout (or set NT_REFERENCE)")
     args = ap.parse_args()
     nt = import_reference(Path(args.ref))
     out: dict[str, np.ndarray] = {}
