@@ -345,7 +345,22 @@ def time_ops(nt, peaks: dict) -> dict:
         m_full = [m.reshape(M, 1).expand(M, M)._C_view for m in m1]
         record("max.backward", stream_time([lambda i=i: _C.extremum_backward(g_full, xv[i], m_full[i], [1])
                                             for i in range(k)], iters=20), 2 * M * M * 4)
-        del X, xv, m1, m_full
+        del m1, m_full
+        # ---- index-array gather / scatter of whole rows by a permutation (read + write = 8 bytes/element)
+        perm_view = [dev(r(22).permutation(M).astype(np.int64))._C_view]
+        plan = dict(fancy_dims_in_src=[0], fancy_dims_data=perm_view, out_axis_is_fancy=[True, False],
+                    out_axis_target=[0, 1], checked=True)
+        record("gather.rows_permuted", stream_time(
+            [lambda i=i: _C.gather_from_axes(x=xv[i], new_shape=[M, M], **plan) for i in range(k)], iters=20), 2 * M * M * 4)
+        T_ = [t.clone() for t in X]
+        tv = [t._C_view for t in T_]
+        record("scatter.rows_permuted", stream_time(
+            [lambda i=i: _C.scatter_to_axes(src=xv[i], out=tv[i], unique=True, **plan) for i in range(k)], iters=20),
+            2 * M * M * 4)
+        record("scatter.rows_permuted.ordered", stream_time(
+            [lambda i=i: _C.scatter_to_axes(src=xv[i], out=tv[i], unique=False, **plan) for i in range(k)], iters=20),
+            2 * M * M * 4)
+        del X, xv, T_, tv
 
         # ---- matmul
         def flush():
@@ -680,7 +695,7 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
 
 PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
-                 "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192")
+                 "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows")
 
 
 def profile_case(name: str, launches: int = 3) -> None:
@@ -710,6 +725,12 @@ def profile_case(name: str, launches: int = 3) -> None:
             _C.set_tanh_mode(_C.TANH_BIT_EXACT_LIBM)
         kern = {"tanh4096": _C.tanh, "tanh4096_exact": _C.tanh, "exp4096": _C.exp, "sigmoid4096": _C.sigmoid}[name]
         fn = lambda: kern(x._C_view)  # noqa: E731
+    elif name == "gather8192_rows":
+        x = dev(r(20).standard_normal((8192, 8192)))
+        perm = nt.Tensor.from_numpy(r(22).permutation(8192).astype(np.int64), "cuda")
+        fn = lambda: _C.gather_from_axes(  # noqa: E731
+            x=x._C_view, new_shape=[8192, 8192], fancy_dims_in_src=[0], fancy_dims_data=[perm._C_view],
+            out_axis_is_fancy=[True, False], out_axis_target=[0, 1], checked=True)
     elif name.startswith("sum8192"):
         x = dev(r(20).standard_normal((8192, 8192)))
         axes = {"sum8192_dim0": [0], "sum8192_dim1": [1], "sum8192_full": [0, 1]}[name]

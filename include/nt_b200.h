@@ -43,7 +43,8 @@ typedef enum {
   NT_OK = 0,
   NT_ERR_RUNTIME = 1, /* RuntimeError */
   NT_ERR_INVALID = 2, /* ValueError   */
-  NT_ERR_TYPE = 3     /* TypeError    */
+  NT_ERR_TYPE = 3,    /* TypeError    */
+  NT_ERR_INDEX = 4    /* IndexError (index-array entry points only) */
 } nt_status;
 
 /* Opaque, reference-counted flat typed buffer (src/cpp/storage.h:34-66). */
@@ -204,8 +205,33 @@ int nt_div_inplace(const nt_view *out, const nt_view *other);
 int nt_copy_inplace(const nt_view *out, const nt_view *other);
 
 /* ------------------------------------------------------------------ copies (src/cpp/ops/copy_ops.cu:172-217) */
-int nt_copy_view(const nt_view *src, const nt_view *out);                    /* copy_view: strided -> strided; bumps version */
+int nt_copy_view(const nt_view *src, const nt_view *out);                    /* copy_view: strided -> strided; version untouched, as in the reference */
 int nt_clone_contiguous_view_from(const nt_view *src, nt_storage **out);     /* also the materialising broadcast */
+
+/* ------------------------------------------------------------------ index-array ("fancy") gather / scatter
+ * src/cpp/ops/copy_ops.cu:85-160 (gather_from_axes) and :7-83 (scatter_to_axes), which the reference
+ * implements for CPU storages only; argument meaning is the reference's:
+ *   fancy_dims_in_src[p]   dim of the indexed tensor that index array p addresses;
+ *   fancy_dims_data[p]     Int64 Cuda views, all of one (already broadcast) shape;
+ *   out_axis_is_fancy[i], out_axis_target[i]   for axis i of the iteration space (the result shape
+ *       for gather, the shape of `src` for scatter): an axis of the index arrays, or a basic dim of
+ *       the indexed tensor.
+ * Negative indices wrap.  Unless NT_INDEX_CHECKED is set, a pass over the index arrays first rejects
+ * values outside [-extent, extent) with NT_ERR_INDEX before anything is written (the check the
+ * reference's Python layer does on the host, src/nanotorch/core.py:712-718); that pass synchronises.
+ * Scatter: where several source positions address one destination, the destination ends with the
+ * value of the last of them in row-major order of `src`, as the reference's sequential loop leaves
+ * it; NT_INDEX_UNIQUE (the caller vouches that destinations are distinct) skips the ordering pass
+ * and its scratch of 16 bytes per destination element.  Storage::version is not bumped, as in the
+ * reference. */
+#define NT_INDEX_CHECKED 1u
+#define NT_INDEX_UNIQUE 2u
+int nt_gather_from_axes(const nt_view *x, const int64_t *new_shape, int32_t new_ndim, const int64_t *fancy_dims_in_src,
+                        int32_t n_fancy, const nt_view *fancy_dims_data, const uint8_t *out_axis_is_fancy,
+                        const int64_t *out_axis_target, uint32_t flags, nt_storage **out);
+int nt_scatter_to_axes(const nt_view *src, const nt_view *out, const int64_t *fancy_dims_in_src, int32_t n_fancy,
+                       const nt_view *fancy_dims_data, const uint8_t *out_axis_is_fancy, const int64_t *out_axis_target,
+                       uint32_t flags);
 
 /* ------------------------------------------------------------------ fused backward kernels
  * No single counterpart in the reference: each replaces the chain of primitive kernels that the

@@ -87,7 +87,7 @@ for _name in (
 ):
     getattr(_lib, _name).argtypes = [C.c_void_p]
 
-_ERRORS = {1: RuntimeError, 2: ValueError, 3: TypeError}
+_ERRORS = {1: RuntimeError, 2: ValueError, 3: TypeError, 4: IndexError}
 
 
 def _check(status: int) -> None:
@@ -405,12 +405,49 @@ def clone_contiguous_view_from(src: TensorView) -> Storage:
     return _ret_storage(_lib.nt_clone_contiguous_view_from, _vref(src))
 
 
-def scatter_to_axes(**_kw):
-    raise RuntimeError("scatter_to_axes: requires Cpu.")  # CPU-only in the reference (src/cpp/ops/copy_ops.cu:12-13)
+# Index-array gather/scatter.  Keyword names are the reference's (src/cpp/ops/copy_ops.cu:219-233);
+# the reference runs them on CPU storages only, here they are device kernels.  `checked` / `unique`
+# are additions: the caller already validated the indices on the host / vouches that no two source
+# positions address one destination (see include/nt_b200.h).
+INDEX_CHECKED = 1
+INDEX_UNIQUE = 2
 
 
-def gather_from_axes(**_kw):
-    raise RuntimeError("gather_from_axes: requires Cpu.")  # CPU-only in the reference (src/cpp/ops/copy_ops.cu:92)
+def _index_plan(fancy_dims_in_src, fancy_dims_data, out_axis_is_fancy, out_axis_target):
+    nf, na = len(fancy_dims_in_src), len(out_axis_is_fancy)
+    if len(fancy_dims_data) != nf or len(out_axis_target) != na:
+        raise ValueError("index plan: list lengths differ.")
+    if nf > NT_MAX_DIMS or na > NT_MAX_DIMS:
+        raise RuntimeError("index plan: more than 8 dimensions are not supported on device.")
+    dims = (C.c_int64 * (nf or 1))(*fancy_dims_in_src)
+    views = (_View * (nf or 1))()
+    for i, v in enumerate(fancy_dims_data):
+        views[i] = v._struct()
+    is_fancy = (C.c_uint8 * (na or 1))(*[1 if f else 0 for f in out_axis_is_fancy])
+    target = (C.c_int64 * (na or 1))(*out_axis_target)
+    return dims, nf, views, is_fancy, target
+
+
+def scatter_to_axes(*, src: TensorView, out: TensorView, fancy_dims_in_src, fancy_dims_data, out_axis_is_fancy,
+                    out_axis_target, checked: bool = False, unique: bool = False) -> None:
+    if len(out_axis_is_fancy) != len(src.shape):
+        raise ValueError("scatter_to_axes: one axis entry per dimension of src.")
+    dims, nf, views, is_fancy, target = _index_plan(fancy_dims_in_src, fancy_dims_data, out_axis_is_fancy,
+                                                    out_axis_target)
+    flags = (INDEX_CHECKED if checked else 0) | (INDEX_UNIQUE if unique else 0)
+    _check(_lib.nt_scatter_to_axes(_vref(src), _vref(out), dims, C.c_int32(nf), views, is_fancy, target,
+                                   C.c_uint32(flags)))
+
+
+def gather_from_axes(*, x: TensorView, new_shape, fancy_dims_in_src, fancy_dims_data, out_axis_is_fancy,
+                     out_axis_target, checked: bool = False) -> Storage:
+    if len(out_axis_is_fancy) != len(new_shape):
+        raise ValueError("gather_from_axes: one axis entry per dimension of new_shape.")
+    dims, nf, views, is_fancy, target = _index_plan(fancy_dims_in_src, fancy_dims_data, out_axis_is_fancy,
+                                                    out_axis_target)
+    shape = (C.c_int64 * (len(new_shape) or 1))(*new_shape)
+    return _ret_storage(_lib.nt_gather_from_axes, _vref(x), shape, C.c_int32(len(new_shape)), dims, C.c_int32(nf),
+                        views, is_fancy, target, C.c_uint32(INDEX_CHECKED if checked else 0))
 
 
 # ---- factories (src/cpp/factory.cu:85-99)

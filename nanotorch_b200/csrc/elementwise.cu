@@ -482,7 +482,8 @@ int nt_copy_view(const nt_view *src, const nt_view *out) {
     const nt_view *views[2] = {out, src};
     ew_launch<IdentityF<T>, 1>(IdentityF<T>{}, views);
   });
-  out->storage->version += 1;
+  // no version bump: the reference's copy_view leaves Storage::version alone (only the *_inplace
+  // family bumps it, src/cpp/ops/inplace_ops.cu:60)
   NT_API_END
 }
 

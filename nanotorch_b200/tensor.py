@@ -5,8 +5,9 @@ Host-side mirror of the reference's ``nanotorch.Tensor`` for the op-kernel hot p
 stride 0 = broadcast, views never copy), same attribute and method names, same error classes.
 Everything numeric happens in ``_C`` (libnt_b200.so); this file only does bookkeeping.
 
-Not mirrored: fancy (index-array / mask) indexing, which is a CPU-only host feature of the
-reference (src/nanotorch/core.py:666-830) and not on the kernel path.
+Index-array and mask indexing (src/nanotorch/core.py:172-254, 666-772) follows the reference's plan
+(the numpy rule for where the index dimensions land) and runs as device gather/scatter kernels; the
+reference copies element by element on the host.
 """
 
 from __future__ import annotations
@@ -322,8 +323,12 @@ class Tensor:
     def _alias(self) -> "Tensor":
         return Tensor._new_view(self._storage, self._shape, self._strides, self._offset)
 
-    # ------------------------------------------------------------------ basic indexing (views)
-    def _basic_index(self, index) -> "Tensor":
+    # ------------------------------------------------------------------ indexing
+    def _basic_index(self, index) -> "tuple[Tensor, tuple | None]":
+        """int / slice / None / Ellipsis selectors as a view of the same storage
+        (src/nanotorch/core.py:775-827).  Index-array and mask selectors keep their dimension in the
+        view and come back in the second result, aligned with the view's dims (None elsewhere);
+        the second result is None when the whole index was basic."""
         if not isinstance(index, tuple):
             index = (index,)
         if self.ndim == 0:
@@ -339,47 +344,71 @@ class Tensor:
                 expanded.extend([slice(None)] * (self.ndim - n_real))
             else:
                 expanded.append(i)
-        shape, strides, offset, dim = [], [], self._offset, 0
+        shape, strides, residual, offset, dim = [], [], [], self._offset, 0
         for sel in expanded:
             if sel is None:
                 shape.append(1)
                 strides.append(0)
+                residual.append(None)
                 continue
             extent, stride = self._shape[dim], self._strides[dim]
-            if isinstance(sel, bool) or not isinstance(sel, (int, slice)):
-                raise NotImplementedError("Only int / slice / None / Ellipsis indexing is supported on device.")
             if isinstance(sel, int):
                 if sel < 0:
                     sel += extent
                 if not 0 <= sel < extent:
                     raise IndexError(f"Cannot index at position {sel} in {extent} elements.")
                 offset += sel * stride
-            else:
+            elif isinstance(sel, slice):
                 start, stop, step = sel.indices(extent)
                 shape.append(len(range(start, stop, step)))
                 strides.append(stride * step)
+                residual.append(None)
                 offset += start * stride
+            else:  # index array or mask: resolved by _fancy_plan
+                shape.append(extent)
+                strides.append(stride)
+                residual.append(sel)
             dim += 1
         shape.extend(self._shape[dim:])
         strides.extend(self._strides[dim:])
-        return Tensor._new_view(self._storage, tuple(shape), tuple(strides), offset)
+        residual.extend([None] * (self.ndim - dim))
+        view = Tensor._new_view(self._storage, tuple(shape), tuple(strides), offset)
+        return view, (tuple(residual) if any(r is not None for r in residual) else None)
 
     def __getitem__(self, index) -> "Tensor":
-        return self._basic_index(index)
+        view, residual = self._basic_index(index)
+        if residual is None:
+            return view
+        plan = _fancy_plan(view._shape, residual, self.device)
+        storage = _C.gather_from_axes(
+            x=view._C_view, new_shape=plan.new_shape, fancy_dims_in_src=plan.fancy_dims_in_src,
+            fancy_dims_data=[t._C_view for t in plan.fancy_dims_data], out_axis_is_fancy=plan.out_axis_is_fancy,
+            out_axis_target=plan.out_axis_target, checked=plan.checked)
+        return Tensor._new_contiguous(storage, plan.new_shape)
 
     def __setitem__(self, index, value) -> None:
-        target = self._basic_index(index)
+        target, residual = self._basic_index(index)
         if not isinstance(value, Tensor):
             value = Tensor(value, dtype=self.dtype, device=self.device)
         elif value.dtype != self.dtype:
             value = value.to(self.dtype)
+        plan = None if residual is None else _fancy_plan(target._shape, residual, self.device)
         try:
-            value = value.expand(*target.shape)
+            value = value.expand(*(target.shape if plan is None else plan.new_shape))
         except ValueError as e:
             raise IndexError(str(e)) from e
         if value._storage is self._storage:
             value = value._to_contiguous(force=True)
-        _C.copy_view(src=value._C_view, out=target._C_view)
+        if plan is None:
+            _C.copy_view(src=value._C_view, out=target._C_view)
+            return
+        # The reference hands the *unsliced* tensor to scatter_to_axes (src/nanotorch/core.py:246-248),
+        # which is only right when every basic selector is a full slice; the sliced view is used here,
+        # which coincides with it in that case.
+        _C.scatter_to_axes(
+            src=value._C_view, out=target._C_view, fancy_dims_in_src=plan.fancy_dims_in_src,
+            fancy_dims_data=[t._C_view for t in plan.fancy_dims_data], out_axis_is_fancy=plan.out_axis_is_fancy,
+            out_axis_target=plan.out_axis_target, checked=plan.checked, unique=plan.unique)
 
     # ------------------------------------------------------------------ autograd
     @property
@@ -426,3 +455,102 @@ class Tensor:
             run_backward(self)
 
     __hash__ = None  # elementwise __eq__
+
+
+# ---------------------------------------------------------------------------------------------
+# Index-array / mask indexing plan (the reference's _FancyAxes, src/nanotorch/core.py:666-772)
+class _FancyPlan:
+    __slots__ = ("new_shape", "fancy_dims_in_src", "fancy_dims_data", "out_axis_is_fancy", "out_axis_target",
+                 "checked", "unique")
+
+
+def _host_index_array(sel, extent: int, dim: int):
+    """A host selector (nested list, or a Cpu tensor) as a wrapped, range-checked int64 numpy array."""
+    import numpy as np
+
+    if isinstance(sel, Tensor):
+        arr = sel.numpy()
+    else:
+        if not isinstance(sel, Sequence) or isinstance(sel, (str, bytes)):
+            raise IndexError(f"Unexpected selector type {type(sel)}")
+        try:
+            probe = Tensor(sel)  # the reference's own inference of shape and dtype for nested lists
+        except Exception as e:
+            raise IndexError(f"Could not interpret index {dim} as a Tensor: {e}")
+        arr = probe.numpy()
+    if arr.dtype == np.bool_:
+        if arr.ndim > 1:
+            raise NotImplementedError("nD boolean masks not here (yet).")
+        if arr.shape[0] != extent:
+            raise IndexError(f"Wrong boolean index shape: {arr.shape[0]} (expected {extent}).")
+        return np.flatnonzero(arr).astype(np.int64)
+    flat = arr.reshape(-1)
+    wrapped = np.where(flat < 0, flat + extent, flat)
+    bad = np.flatnonzero((wrapped < 0) | (wrapped >= extent))
+    if bad.size:
+        raise IndexError(f"Invalid index {wrapped[bad[0]].item()} in axis of len {extent}.")
+    return wrapped.astype(np.int64).reshape(arr.shape)
+
+
+def _fancy_plan(shape: Shape, residual: tuple, device: Device) -> _FancyPlan:
+    """Where the index dimensions land in the result and which result axis walks which source dim.
+
+    ``residual[d]`` is the index-array / mask selector of dim ``d`` of the (already basic-indexed)
+    view of shape ``shape``, or None.  Adjacent indexed dims are replaced in place by the broadcast
+    index shape; indexed dims separated by a basic dim move the index shape to the front (the numpy
+    rule the reference follows, src/nanotorch/core.py:737-763).
+    Host selectors are wrapped and range-checked here (``checked``) and tested for distinct
+    destinations (``unique``); Cuda index tensors are checked by the library.
+    """
+    import numpy as np
+
+    fancy_dims, basic_axes, raw, host_arrays = [], [], [], []
+    for dim in range(len(shape)):
+        sel = residual[dim] if dim < len(residual) else None
+        if sel is None:
+            basic_axes.append(dim)
+            continue
+        fancy_dims.append(dim)
+        if isinstance(sel, Tensor) and sel.device == Device.Cuda and sel.dtype != Dtype.Bool:
+            if sel.dtype > Dtype.Int64:
+                raise IndexError(f"Index tensors must be integer or Bool, got {sel.dtype.name}.")
+            raw.append(sel.to(Dtype.Int64))
+            host_arrays.append(None)
+        else:
+            if isinstance(sel, Tensor) and sel.device == Device.Cuda:
+                sel = sel.cpu()  # a mask's extent is data dependent: read it back
+            arr = _host_index_array(sel, shape[dim], dim)
+            host_arrays.append(arr)
+            raw.append(Tensor.from_numpy(arr, device))
+    try:
+        ind_shape = broadcast_shapes(*(t.shape for t in raw))
+    except RuntimeError as e:
+        raise IndexError(str(e)) from e
+    plan = _FancyPlan()
+    plan.fancy_dims_in_src = fancy_dims
+    plan.fancy_dims_data = [t.expand(*ind_shape) for t in raw]
+    plan.checked = all(a is not None for a in host_arrays)
+    plan.unique = False
+    if plan.checked:
+        cols = [np.broadcast_to(a, ind_shape).reshape(-1) for a in host_arrays]
+        if len(cols) == 1:
+            plan.unique = np.unique(cols[0]).size == cols[0].size
+        else:
+            plan.unique = np.unique(np.stack(cols, axis=1), axis=0).shape[0] == cols[0].size
+    basic_shape = [shape[d] for d in basic_axes]
+    nidx = len(ind_shape)
+    adjacent = all(b - a == 1 for a, b in zip(fancy_dims, fancy_dims[1:]))
+    if adjacent:
+        first = fancy_dims[0]  # == number of basic dims in front of the indexed block
+        plan.new_shape = tuple(basic_shape[:first]) + tuple(ind_shape) + tuple(basic_shape[first:])
+        plan.out_axis_is_fancy = [first <= i < first + nidx for i in range(len(plan.new_shape))]
+        plan.out_axis_target = [
+            (i - first) if first <= i < first + nidx else basic_axes[i if i < first else i - nidx]
+            for i in range(len(plan.new_shape))]
+    else:
+        plan.new_shape = tuple(ind_shape) + tuple(basic_shape)
+        plan.out_axis_is_fancy = [i < nidx for i in range(len(plan.new_shape))]
+        plan.out_axis_target = [i if i < nidx else basic_axes[i - nidx] for i in range(len(plan.new_shape))]
+    if len(plan.new_shape) > 8:
+        raise RuntimeError("Indexing result has more than 8 dimensions.")
+    return plan

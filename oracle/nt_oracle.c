@@ -263,3 +263,73 @@ void nto_uniform_f32(nto_rng *r, float *out, int64_t n) {
   }
 }
 int64_t nto_rng_sizeof(void) { return (int64_t)sizeof(nto_rng); }
+
+/* ---------------------------------------------------------------- index-array gather / scatter
+ * src/cpp/ops/copy_ops.cu:85-160 (gather_from_axes) and :7-83 (scatter_to_axes): an odometer walks
+ * the iteration space (the result shape for gather, the source shape for scatter) in row-major
+ * order; each iteration axis either drives one axis of the (equally shaped) index arrays or one
+ * basic dim of the indexed operand; the coordinate of an indexed dim is read from its index array.
+ * Indices arrive already wrapped and range-checked (the reference's Python layer does that,
+ * src/nanotorch/core.py:712-718).  Elements are copied as `itemsize` raw bytes (DispatchAll there).
+ * Scatter visits the source in row-major order, so of several writers to one destination the last
+ * one wins. */
+typedef struct {
+  const int64_t *data; /* Int64 index array storage */
+  nto_view view;
+} nto_index_array;
+
+static void index_walk(int scatter, int itemsize, const char *lin_data, const nto_view *lin, char *ix_data_w,
+                       const char *ix_data_r, const nto_view *ix, const int64_t *fancy_dims, int n_fancy,
+                       const nto_index_array *ind, const uint8_t *axis_is_fancy, const int64_t *axis_target,
+                       char *lin_data_w) {
+  int64_t pos[NTO_MAX_DIMS] = {0};         /* odometer over the iteration space */
+  int64_t ix_basic[NTO_MAX_DIMS] = {0};    /* coordinates of the indexed operand's basic dims */
+  int64_t ind_coord[NTO_MAX_DIMS] = {0};   /* coordinates into the index arrays */
+  int fancy_slot[NTO_MAX_DIMS];
+  for (int d = 0; d < NTO_MAX_DIMS; ++d) fancy_slot[d] = -1;
+  for (int q = 0; q < n_fancy; ++q) fancy_slot[fancy_dims[q]] = q;
+  const int64_t n = numel(lin);
+  for (int64_t it = 0; it < n; ++it) {
+    for (int a = 0; a < lin->ndim; ++a) {
+      if (axis_is_fancy[a]) ind_coord[axis_target[a]] = pos[a];
+      else ix_basic[axis_target[a]] = pos[a];
+    }
+    int64_t at_lin = lin->offset;
+    for (int a = 0; a < lin->ndim; ++a) at_lin += lin->strides[a] * pos[a];
+    int64_t at_ix = ix->offset;
+    for (int d = 0; d < ix->ndim; ++d) {
+      int64_t coord = ix_basic[d];
+      const int q = fancy_slot[d];
+      if (q >= 0) {
+        int64_t flat = ind[q].view.offset;
+        for (int k = 0; k < ind[q].view.ndim; ++k) flat += ind[q].view.strides[k] * ind_coord[k];
+        coord = ind[q].data[flat];
+      }
+      at_ix += ix->strides[d] * coord;
+    }
+    if (scatter) memcpy(ix_data_w + at_ix * itemsize, lin_data + at_lin * itemsize, (size_t)itemsize);
+    else memcpy(lin_data_w + at_lin * itemsize, ix_data_r + at_ix * itemsize, (size_t)itemsize);
+    for (int a = lin->ndim - 1; a >= 0; --a) {
+      if (++pos[a] < lin->shape[a]) break;
+      pos[a] = 0;
+    }
+  }
+}
+
+/* out: contiguous buffer of prod(out_view->shape) elements; out_view carries the result shape with
+ * contiguous strides and offset 0. */
+int nto_gather_from_axes(int itemsize, const void *x, const nto_view *vx, void *out, const nto_view *out_view,
+                         const int64_t *fancy_dims, int n_fancy, const nto_index_array *ind,
+                         const uint8_t *axis_is_fancy, const int64_t *axis_target) {
+  index_walk(0, itemsize, NULL, out_view, NULL, (const char *)x, vx, fancy_dims, n_fancy, ind, axis_is_fancy,
+             axis_target, (char *)out);
+  return 0;
+}
+
+int nto_scatter_to_axes(int itemsize, const void *src, const nto_view *vsrc, void *out, const nto_view *vout,
+                        const int64_t *fancy_dims, int n_fancy, const nto_index_array *ind,
+                        const uint8_t *axis_is_fancy, const int64_t *axis_target) {
+  index_walk(1, itemsize, (const char *)src, vsrc, (char *)out, NULL, vout, fancy_dims, n_fancy, ind, axis_is_fancy,
+             axis_target, NULL);
+  return 0;
+}

@@ -34,6 +34,10 @@ class _View(C.Structure):
                 ("offset", C.c_int64)]
 
 
+class _IndexArray(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("view", _View)]
+
+
 def build_port(force: bool = False) -> Path:
     """Compile oracle/nt_oracle.c (gcc, seconds)."""
     src = HERE / "nt_oracle.c"
@@ -43,13 +47,13 @@ def build_port(force: bool = False) -> Path:
     return PORT_LIB
 
 
-def _base_and_view(a: np.ndarray):
-    """(flat array owning the memory, element strides, element offset) of any fp32 numpy view."""
-    assert a.dtype == np.float32
+def _base_and_view(a: np.ndarray, dtype=np.float32):
+    """(flat array owning the memory, element strides, element offset) of any numpy view of `dtype`."""
+    assert a.dtype == dtype
     root = a
     while isinstance(root.base, np.ndarray):
         root = root.base
-    if not root.flags["C_CONTIGUOUS"] or root.dtype != np.float32:
+    if not root.flags["C_CONTIGUOUS"] or root.dtype != dtype:
         a = np.ascontiguousarray(a)
         root = a
     flat = root.reshape(-1)
@@ -144,6 +148,56 @@ class PortOracle:
         self.lib.nto_clone_f32(fx.ctypes.data_as(C.c_void_p), C.byref(vx), out.ctypes.data_as(C.c_void_p))
         return out
 
+    # index-array gather/scatter on arrays of any supported dtype; `plan` is a FancyPlan (below)
+    def _index_args(self, plan):
+        arrays = (_IndexArray * max(len(plan.fancy_dims_data), 1))()
+        keep = []
+        for i, ind in enumerate(plan.fancy_dims_data):
+            flat, strides, offset = _base_and_view(ind, np.int64)
+            keep.append(flat)
+            arrays[i].data = flat.ctypes.data
+            arrays[i].view.ndim = ind.ndim
+            for d in range(ind.ndim):
+                arrays[i].view.shape[d] = ind.shape[d]
+                arrays[i].view.strides[d] = strides[d]
+            arrays[i].view.offset = offset
+        dims = (C.c_int64 * 8)(*plan.fancy_dims_in_src)
+        is_fancy = (C.c_uint8 * 8)(*[int(f) for f in plan.out_axis_is_fancy])
+        target = (C.c_int64 * 8)(*plan.out_axis_target)
+        return arrays, keep, dims, is_fancy, target
+
+    @staticmethod
+    def _cv_any(a: np.ndarray):
+        flat, strides, offset = _base_and_view(a, a.dtype)
+        v = _View()
+        v.ndim = a.ndim
+        for i in range(a.ndim):
+            v.shape[i] = a.shape[i]
+            v.strides[i] = strides[i]
+        v.offset = offset
+        return flat, v
+
+    def gather_from_axes(self, x: np.ndarray, plan) -> np.ndarray:
+        fx, vx = self._cv_any(x)
+        out = np.empty(plan.new_shape, x.dtype)
+        _, vo = self._cv_any(out)
+        arrays, keep, dims, is_fancy, target = self._index_args(plan)
+        self.lib.nto_gather_from_axes(C.c_int(x.itemsize), fx.ctypes.data_as(C.c_void_p), C.byref(vx),
+                                      out.ctypes.data_as(C.c_void_p), C.byref(vo), dims,
+                                      C.c_int(len(plan.fancy_dims_in_src)), arrays, is_fancy, target)
+        return out
+
+    def scatter_to_axes(self, src: np.ndarray, out: np.ndarray, plan) -> None:
+        """Writes through `out` (any writable view) in place."""
+        assert src.dtype == out.dtype and src.shape == tuple(plan.new_shape)
+        fs, vs = self._cv_any(src)
+        fo, vo = self._cv_any(out)
+        assert np.shares_memory(fo, out), "scatter target must be a view of a C-contiguous array"
+        arrays, keep, dims, is_fancy, target = self._index_args(plan)
+        self.lib.nto_scatter_to_axes(C.c_int(src.itemsize), fs.ctypes.data_as(C.c_void_p), C.byref(vs),
+                                     fo.ctypes.data_as(C.c_void_p), C.byref(vo), dims,
+                                     C.c_int(len(plan.fancy_dims_in_src)), arrays, is_fancy, target)
+
     def uniform(self, seed: int, n: int) -> np.ndarray:
         self.lib.nto_rng_sizeof.restype = C.c_int64
         state = C.create_string_buffer(self.lib.nto_rng_sizeof())
@@ -226,6 +280,33 @@ class RefOracle:
     def clone(self, x):
         vx, _ = self._tv(x)
         return self._out(self.m.clone_contiguous_view_from(vx), x.shape)
+
+    def _tv_any(self, a: np.ndarray):
+        dt = {np.dtype(np.bool_): self.m.Dtype.Bool, np.dtype(np.int32): self.m.Dtype.Int32,
+              np.dtype(np.int64): self.m.Dtype.Int64, np.dtype(np.float32): self.F32,
+              np.dtype(np.float64): self.m.Dtype.Float64}[a.dtype]
+        flat, strides, offset = _base_and_view(a, a.dtype)
+        s = self.m.Storage.allocate(max(flat.size, 1), dt, self.CPU)
+        if flat.size:
+            np.asarray(memoryview(s))[: flat.size] = flat
+        return self.m.TensorView(s, list(a.shape), list(strides), offset), s, flat
+
+    def gather_from_axes(self, x, plan):
+        vx, _, _ = self._tv_any(x)
+        out = self.m.gather_from_axes(
+            x=vx, new_shape=list(plan.new_shape), fancy_dims_in_src=list(plan.fancy_dims_in_src),
+            fancy_dims_data=[self._tv_any(i)[0] for i in plan.fancy_dims_data],
+            out_axis_is_fancy=list(plan.out_axis_is_fancy), out_axis_target=list(plan.out_axis_target))
+        return self._out(out, plan.new_shape, x.dtype)
+
+    def scatter_to_axes(self, src, out, plan):
+        vs, _, _ = self._tv_any(src)
+        vo, so, flat = self._tv_any(out)
+        self.m.scatter_to_axes(
+            src=vs, out=vo, fancy_dims_in_src=list(plan.fancy_dims_in_src),
+            fancy_dims_data=[self._tv_any(i)[0] for i in plan.fancy_dims_data],
+            out_axis_is_fancy=list(plan.out_axis_is_fancy), out_axis_target=list(plan.out_axis_target))
+        flat[:] = np.asarray(memoryview(so))[: flat.size]
 
     def uniform(self, seed, n):
         self.m.manual_seed(seed)
@@ -339,3 +420,97 @@ def mlp_step(o, params, X, Y, lr, activation: str, compute_input_grad: bool = Fa
         sgd_update(o, W, gW, lr)
         sgd_update(o, b, gb, lr)
     return float(loss.reshape(-1)[0])
+
+
+# =============================================================================================
+# Index-array / mask indexing as the reference's Python layer plans it.
+class FancyPlan:
+    """new_shape, fancy_dims_in_src, fancy_dims_data (broadcast int64 arrays), out_axis_is_fancy,
+    out_axis_target -- the fields of the reference's _FancyAxes (src/nanotorch/core.py:666-675)."""
+
+
+def fancy_plan(shape, index) -> FancyPlan:
+    """src/nanotorch/core.py:677-772.  `index` has one entry per dim of `shape` (shorter = trailing
+    dims basic): None for a basic dim, else a list / bool mask / integer array for that dim."""
+    fancy_dims, basic_axes, basic_shape, raw = [], [], [], []
+    for dim, extent in enumerate(shape):
+        sel = index[dim] if dim < len(index) else None
+        if sel is None:
+            basic_axes.append(dim)
+            basic_shape.append(extent)
+            continue
+        arr = np.asarray(sel)
+        if arr.dtype == np.bool_:                              # :720-728
+            if arr.ndim > 1:
+                raise NotImplementedError("nD boolean masks not here (yet).")
+            if arr.shape[0] != extent:
+                raise IndexError(f"Wrong boolean index shape: {arr.shape[0]} (expected {extent}).")
+            arr = np.flatnonzero(arr)
+        else:                                                  # :712-718: wrap, then range check
+            arr = arr.astype(np.int64)
+            arr = np.where(arr < 0, arr + extent, arr)
+            bad = arr[(arr < 0) | (arr >= extent)]
+            if bad.size:
+                raise IndexError(f"Invalid index {int(bad.reshape(-1)[0])} in axis of len {extent}.")
+        fancy_dims.append(dim)
+        raw.append(arr.astype(np.int64))
+    ind_shape = np.broadcast_shapes(*(a.shape for a in raw))
+    plan = FancyPlan()
+    plan.fancy_dims_in_src = fancy_dims
+    plan.fancy_dims_data = [np.broadcast_to(a, ind_shape) for a in raw]   # expand = stride 0, :734
+    nidx = len(ind_shape)
+    scattered = any(b - a != 1 for a, b in zip(fancy_dims, fancy_dims[1:]))  # :739-745
+    plan.out_axis_is_fancy, plan.out_axis_target = [], []
+    if scattered:
+        plan.new_shape = tuple(ind_shape) + tuple(basic_shape)
+        for i in range(len(plan.new_shape)):
+            plan.out_axis_is_fancy.append(i < nidx)
+            plan.out_axis_target.append(i if i < nidx else basic_axes[i - nidx])
+    else:
+        a0 = fancy_dims[0]
+        plan.new_shape = tuple(basic_shape[:a0]) + tuple(ind_shape) + tuple(basic_shape[a0:])
+        for i in range(len(plan.new_shape)):
+            inside = a0 <= i < a0 + nidx
+            plan.out_axis_is_fancy.append(inside)
+            plan.out_axis_target.append(i - a0 if inside else basic_axes[i if i < a0 else i - nidx])
+    return plan
+
+
+def _split_index(index, ndim):
+    """(numpy basic index with full slices at the index-array positions, residual per view dim)."""
+    if not isinstance(index, tuple):
+        index = (index,)
+    if any(sel is Ellipsis for sel in index):                  # expand_ellipsis, _indexing.py:29-51
+        n_real = sum(1 for sel in index if sel is not None and sel is not Ellipsis)
+        at = next(i for i, sel in enumerate(index) if sel is Ellipsis)
+        index = index[:at] + (slice(None),) * (ndim - n_real) + index[at + 1:]
+    basic, residual = [], []
+    for sel in index:
+        if sel is None:
+            basic.append(None)
+            residual.append(None)
+        elif isinstance(sel, (int, np.integer)) and not isinstance(sel, (bool, np.bool_)):
+            basic.append(int(sel))
+        elif isinstance(sel, slice):
+            basic.append(sel)
+            residual.append(None)
+        else:
+            basic.append(slice(None))
+            residual.append(sel)
+    return tuple(basic), residual
+
+
+def getitem(o, x: np.ndarray, index) -> np.ndarray:
+    """Tensor.__getitem__ with at least one index-array selector (src/nanotorch/core.py:172-203)."""
+    basic, residual = _split_index(index, x.ndim)
+    view = x[basic]
+    return o.gather_from_axes(view, fancy_plan(view.shape, residual))
+
+
+def setitem(o, x: np.ndarray, index, value: np.ndarray) -> None:
+    """Tensor.__setitem__ with index arrays (src/nanotorch/core.py:205-254), writing through the
+    basic-indexed view (what the reference does whenever its basic selectors are full slices)."""
+    basic, residual = _split_index(index, x.ndim)
+    view = x[basic]
+    plan = fancy_plan(view.shape, residual)
+    o.scatter_to_axes(np.broadcast_to(np.asarray(value, dtype=x.dtype), plan.new_shape), view, plan)

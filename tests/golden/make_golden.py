@@ -222,6 +222,29 @@ def mlp_cases(nt, out: dict):
         out[f"mlp5s/final/{i}"] = A(p)
 
 
+def index_cases(nt, out: dict):
+    """Index-array / mask getitem and setitem through the reference's Tensor (CPU path)."""
+    sys.path.insert(0, str(REPO / "tests"))
+    from util import INDEX_GET_CASES, INDEX_SET_CASES, INDEX_SHAPE, index_case, index_value
+
+    rng = np.random.default_rng(500)
+    x = rng.standard_normal(INDEX_SHAPE).astype(np.float32)
+    out["idx/in/x"] = x
+    for k, source in enumerate(INDEX_GET_CASES):
+        out[f"idx/get/{k}"] = A(T(nt, x)[index_case(source)])
+    xi = rng.integers(-50, 50, INDEX_SHAPE).astype(np.int64)
+    out["idx/in/xi"] = xi
+    ti = nt.Tensor(xi.tolist(), dtype=nt.int64)
+    out["idx/get_int64"] = A(ti[index_case(INDEX_GET_CASES[2])])
+    for k, (source, kind) in enumerate(INDEX_SET_CASES):
+        t = T(nt, x)
+        index = index_case(source)
+        value = index_value(kind, t[index].shape, rng)
+        out[f"idx/set/{k}/value"] = np.asarray(value, dtype=np.float32)
+        t[index] = T(nt, np.asarray(value, dtype=np.float32))
+        out[f"idx/set/{k}/out"] = A(t)
+
+
 def rng_cases(nt, out: dict):
     nt.manual_seed(42)
     out["rng/seed42"] = A(nt.rand(16))
@@ -242,6 +265,7 @@ def main():
         reduction_cases(nt, out)
         matmul_cases(nt, out)
         mlp_cases(nt, out)
+        index_cases(nt, out)
     np.savez_compressed(HERE / "reference_cpu.npz", **out)
     size = (HERE / "reference_cpu.npz").stat().st_size
     print(f"wrote {len(out)} arrays, {size / 1024:.0f} KiB")

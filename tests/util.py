@@ -57,3 +57,55 @@ def assert_scaled(got: np.ndarray, want: np.ndarray, scale: np.ndarray, rel: flo
         raise AssertionError(f"{what}: |diff| {err[i]:.3e} > {rel:g} * scale {np.broadcast_to(scale, err.shape)[i]:.3e} "
                              f"at {i} ({int(over.sum())} elements over)")
     return float((err / np.maximum(np.asarray(scale, dtype=np.float64), 1e-300)).max()) if err.size else 0.0
+
+
+# ---------------------------------------------------------------------------------------------
+# Index-array / mask indexing cases shared by tests/golden/make_golden.py (which records what the
+# reference returns for them) and the parity tests.  Each entry is the source of an index tuple for
+# a tensor of shape INDEX_SHAPE; evaluate with index_case().
+INDEX_SHAPE = (5, 6, 7)
+INDEX_GET_CASES = [
+    "([4, 0, -1],)",
+    "(slice(None), [0, 2, 5])",
+    "(slice(None), slice(None), [[0, 1], [6, -2]])",
+    "([0, 1], slice(None), [2, 3])",                 # separated index dims: index shape moves to the front
+    "([0, 1], [2, 3])",
+    "([0, 1], [1, 2], [2, 3])",
+    "(slice(1, 4), [0, 2], slice(None, None, 2))",
+    "([True, False, True, False, True],)",
+    "(slice(None), [False, True, True, False, False, True])",
+    "(slice(None), [1, 1, 1])",
+    "(2, [0, 5])",
+    "(0, slice(None), [1, 2])",                      # the int is consumed first: result (6, 2), unlike numpy
+    "(None, [1, 2])",
+    "([[0], [1]], [[1, 2, 3]])",                     # broadcast index arrays
+    "(Ellipsis, [0, 3])",
+    "([1, 3], Ellipsis)",
+    "(slice(None, None, -1), [5, 0])",               # negative-stride view under the index array
+]
+# setitem: cases whose basic selectors are full slices (where the reference writes to the right place)
+INDEX_SET_CASES = [
+    ("([4, 0, -1],)", "full"),
+    ("(slice(None), [0, 2, 5])", "full"),
+    ("(slice(None), slice(None), [[0, 1], [6, -2]])", "full"),
+    ("([0, 1], slice(None), [2, 3])", "full"),
+    ("([0, 1], [2, 3])", "row"),
+    ("([True, False, True, False, True],)", "scalar"),
+    ("(slice(None), [1, 1, 1])", "full"),            # colliding destinations: the last writer wins
+    ("([[0], [1]], [[1, 2, 3]])", "row"),
+    ("([3, 3, 0, 3],)", "full"),
+]
+
+
+def index_case(source: str):
+    return eval(source, {"__builtins__": {}}, {"slice": slice, "Ellipsis": Ellipsis, "None": None,
+                                               "True": True, "False": False})
+
+
+def index_value(kind: str, shape, rng):
+    """The right-hand side of a setitem case: a full-shape array, a broadcast row, or a scalar."""
+    if kind == "full":
+        return rng.standard_normal(shape).astype(np.float32)
+    if kind == "row":
+        return rng.standard_normal(shape[-1:]).astype(np.float32)
+    return np.float32(rng.standard_normal())
