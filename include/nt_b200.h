@@ -129,10 +129,19 @@ int nt_host_unregister(void *ptr);
 int nt_zeros(int64_t n, int dtype, int device, nt_storage **out);
 int nt_ones(int64_t n, int dtype, int device, nt_storage **out);
 int nt_full(int64_t n, const nt_scalar *value, int dtype, int device, nt_storage **out);
+/* eye / arange are written by a kernel when device is Cuda (host loop + copy in the reference). */
 int nt_eye(int64_t n, int dtype, int device, nt_storage **out);
 int nt_arange(int64_t n, int64_t start, int64_t step, int dtype, int device, nt_storage **out);
-int nt_manual_seed(uint64_t seed);                                       /* src/cpp/random.h:12 */
-int nt_uniform(int64_t n, int dtype, int device, nt_storage **out);      /* host mt19937_64 stream, then H2D */
+int nt_manual_seed(uint64_t seed);                                       /* src/cpp/random.h:12; seeds both generators below */
+/* U[0,1).  Generator mode 0 (default): the reference's host stream -- std::mt19937_64 through
+ * std::uniform_real_distribution, then a host-to-device copy (src/cpp/factory.cu:73-83) -- so that a
+ * seed reproduces the reference's values, parameter initialisation included.  Mode 1 (no counterpart
+ * in the reference): Philox4x32-10 keyed by the seed, generated by a kernel straight into the Cuda
+ * storage; consecutive calls continue one counter stream (4 floats or 2 doubles per 128-bit block,
+ * a call starts on a fresh block); float = (word >> 8) * 2^-24, double = 53 bits of two words. */
+int nt_uniform(int64_t n, int dtype, int device, nt_storage **out);
+int nt_set_rng_mode(int mode);
+int nt_get_rng_mode(void);
 
 /* ------------------------------------------------------------------ pointwise binary (src/cpp/ops/binary_ops.cu:97-113) */
 int nt_add(const nt_view *x1, const nt_view *x2, nt_storage **out);

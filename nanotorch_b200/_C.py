@@ -540,6 +540,18 @@ def get_tanh_mode() -> int:
     return _lib.nt_get_tanh_mode()
 
 
+RNG_HOST_MT19937_64 = 0   # the reference's seeded host stream (default)
+RNG_DEVICE_PHILOX = 1     # Philox4x32-10 generated on the device
+
+
+def set_rng_mode(mode: int) -> None:
+    _check(_lib.nt_set_rng_mode(int(mode)))
+
+
+def get_rng_mode() -> int:
+    return _lib.nt_get_rng_mode()
+
+
 MATMUL_EXACT_FP32 = 0
 MATMUL_3XTF32 = 1
 MATMUL_FP32_UNFUSED = 2

@@ -42,6 +42,11 @@ struct Runtime {
   size_t pin_cached_bytes = 0;
   std::atomic<uint64_t> launches{0};
   std::mt19937_64 rng{std::random_device{}()};
+  // device generator (rng_mode 1): Philox4x32-10 keyed by the seed; `philox_offset` counts the 128-bit
+  // blocks handed out so far, so successive calls continue one stream
+  int rng_mode = 0;
+  uint64_t philox_seed = std::random_device{}();
+  uint64_t philox_offset = 0;
 };
 static Runtime &rt() {
   static Runtime r;
@@ -360,6 +365,67 @@ template <class S, class D> __global__ void cast_kernel(const S *in, D *out, int
       out[i] = in[i] ? true : false;
     else
       out[i] = static_cast<D>(in[i]);
+  }
+}
+
+// eye(n): ones where row == column, i.e. at every (n + 1)-th element (src/cpp/factory.cu:51-59)
+template <class T> __global__ void eye_kernel(T *out, int64_t n) {
+  int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  int64_t step = int64_t(gridDim.x) * blockDim.x;
+  for (; i < n * n; i += step) out[i] = static_cast<T>(i % (n + 1) == 0 ? 1 : 0);
+}
+
+// arange: static_cast<T>(start + i * step) in int64, as the reference's host loop (src/cpp/factory.cu:62-71)
+template <class T> __global__ void arange_kernel(T *out, int64_t n, int64_t start, int64_t inc) {
+  int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  int64_t step = int64_t(gridDim.x) * blockDim.x;
+  for (; i < n; i += step) out[i] = static_cast<T>(start + i * inc);
+}
+
+// Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC'11):
+// a counter-based generator -- block b of the stream is a pure function of (key, b), so every thread
+// computes its own four words with no state shared between threads or launches.
+__host__ __device__ inline void philox4x32_10(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+  for (int round = 0; round < 10; ++round) {
+    const uint64_t p0 = uint64_t(0xD2511F53u) * c[0];
+    const uint64_t p1 = uint64_t(0xCD9E8D57u) * c[2];
+    const uint32_t n0 = uint32_t(p1 >> 32) ^ c[1] ^ k0;
+    const uint32_t n2 = uint32_t(p0 >> 32) ^ c[3] ^ k1;
+    c[1] = uint32_t(p1);
+    c[3] = uint32_t(p0);
+    c[0] = n0;
+    c[2] = n2;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+}
+
+// U[0,1): float = top 24 bits * 2^-24 (4 per block); double = top 53 bits of two words * 2^-53 (2 per block)
+template <class T> __global__ void philox_uniform_kernel(T *out, int64_t n, uint64_t seed, uint64_t offset) {
+  constexpr int PER = std::is_same_v<T, float> ? 4 : 2;
+  const int64_t blocks = (n + PER - 1) / PER;
+  int64_t b = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t step = int64_t(gridDim.x) * blockDim.x;
+  for (; b < blocks; b += step) {
+    const uint64_t ctr = offset + uint64_t(b);
+    uint32_t c[4] = {uint32_t(ctr), uint32_t(ctr >> 32), 0u, 0u};
+    philox4x32_10(c, uint32_t(seed), uint32_t(seed >> 32));
+    T v[PER];
+    if constexpr (std::is_same_v<T, float>) {
+      for (int j = 0; j < 4; ++j) v[j] = float(c[j] >> 8) * 5.9604644775390625e-08f;
+    } else {
+      for (int j = 0; j < 2; ++j)
+        v[j] = double(((uint64_t(c[2 * j + 1]) << 32) | c[2 * j]) >> 11) * 1.1102230246251565e-16;
+    }
+    const int64_t at = b * PER;
+    if (at + PER <= n) {
+      if constexpr (std::is_same_v<T, float>)
+        *reinterpret_cast<float4 *>(out + at) = make_float4(v[0], v[1], v[2], v[3]);
+      else
+        *reinterpret_cast<double2 *>(out + at) = make_double2(v[0], v[1]);
+    } else {
+      for (int j = 0; at + j < n; ++j) out[at + j] = v[j];
+    }
   }
 }
 
@@ -778,37 +844,80 @@ int nt_full(int64_t n, const nt_scalar *value, int dtype, int device, nt_storage
 
 int nt_eye(int64_t n, int dtype, int device, nt_storage **out) {
   NT_API_BEGIN
-  StorageRef host(storage_new(n * n, dtype, NT_CPU));
+  if (n < 0) fail_invalid("eye: negative size.");
+  StorageRef o(storage_new(n * n, dtype, device));
   dispatch_all(dtype, [&]<class T>() {
-    T *p = static_cast<T *>(host->data);
-    for (int64_t i = 0; i < n * n; ++i) p[i] = static_cast<T>(0);
-    for (int64_t i = 0; i < n; ++i) p[i * n + i] = static_cast<T>(1);
+    T *p = static_cast<T *>(o->data);
+    if (device == NT_CUDA) {
+      if (n > 0) {
+        eye_kernel<T><<<grid_for(n * n, 256), 256, 0, stream()>>>(p, n);
+        check_launch("eye");
+      }
+    } else {
+      for (int64_t i = 0; i < n * n; ++i) p[i] = static_cast<T>(0);
+      for (int64_t i = 0; i < n; ++i) p[i * n + i] = static_cast<T>(1);
+    }
   });
-  *out = to_device_impl(host.s, device);
+  *out = o.release();
   NT_API_END
 }
 
 int nt_arange(int64_t n, int64_t start, int64_t step, int dtype, int device, nt_storage **out) {
   NT_API_BEGIN
-  StorageRef host(storage_new(n, dtype, NT_CPU));
+  if (n < 0) fail_invalid("arange: negative size.");
+  StorageRef o(storage_new(n, dtype, device));
   dispatch_all(dtype, [&]<class T>() {
-    T *p = static_cast<T *>(host->data);
-    for (int64_t i = 0; i < n; ++i) p[i] = static_cast<T>(start + i * step);
+    T *p = static_cast<T *>(o->data);
+    if (device == NT_CUDA) {
+      if (n > 0) {
+        arange_kernel<T><<<grid_for(n, 256), 256, 0, stream()>>>(p, n, start, step);
+        check_launch("arange");
+      }
+    } else {
+      for (int64_t i = 0; i < n; ++i) p[i] = static_cast<T>(start + i * step);
+    }
   });
-  *out = to_device_impl(host.s, device);
+  *out = o.release();
   NT_API_END
 }
 
 int nt_manual_seed(uint64_t seed) {
   NT_API_BEGIN
   rt().rng.seed(seed);
+  rt().philox_seed = seed;
+  rt().philox_offset = 0;
   NT_API_END
 }
 
-// Same host generator and distribution as the reference (src/cpp/random.h:6-9, factory.cu:73-83),
-// so a seed reproduces the reference's parameter initialisation value for value.
+int nt_set_rng_mode(int mode) {
+  NT_API_BEGIN
+  if (mode != 0 && mode != 1) fail_invalid("nt_set_rng_mode: mode must be 0 (host mt19937_64) or 1 (device Philox4x32-10).");
+  rt().rng_mode = mode;
+  NT_API_END
+}
+int nt_get_rng_mode(void) { return rt().rng_mode; }
+
+// Mode 0: the same host generator and distribution as the reference (src/cpp/random.h:6-9,
+// factory.cu:73-83), so a seed reproduces the reference's parameter initialisation value for value.
+// Mode 1 (Cuda storages): generated on the device, no host loop and no host-to-device copy.
 int nt_uniform(int64_t n, int dtype, int device, nt_storage **out) {
   NT_API_BEGIN
+  if (n < 0) fail_invalid("uniform: negative size.");
+  if (rt().rng_mode == 1 && device == NT_CUDA) {
+    StorageRef o(storage_new(n, dtype, NT_CUDA));
+    dispatch_float(dtype, [&]<class T>() {
+      constexpr int per = std::is_same_v<T, float> ? 4 : 2;
+      const int64_t blocks = ceil_div(n, per);
+      if (n > 0) {
+        philox_uniform_kernel<T><<<grid_for(blocks, 256), 256, 0, stream()>>>(static_cast<T *>(o->data), n,
+                                                                              rt().philox_seed, rt().philox_offset);
+        check_launch("philox_uniform");
+      }
+      rt().philox_offset += uint64_t(blocks);
+    });
+    *out = o.release();
+    return NT_OK;
+  }
   StorageRef host(storage_new(n, dtype, NT_CPU));
   dispatch_float(dtype, [&]<class T>() {
     T *p = static_cast<T *>(host->data);

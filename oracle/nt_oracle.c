@@ -333,3 +333,44 @@ int nto_scatter_to_axes(int itemsize, const void *src, const nto_view *vsrc, voi
              axis_target, NULL);
   return 0;
 }
+
+/* ---------------------------------------------------------------- Philox4x32-10
+ * No counterpart in the reference (whose only generator is the host mt19937_64 above): the checker
+ * of the library's optional device generator.  Published algorithm: Salmon, Moraes, Dror, Shaw,
+ * "Parallel random numbers: as easy as 1, 2, 3" (SC'11), 10 rounds, multipliers 0xD2511F53 /
+ * 0xCD9E8D57, Weyl key increments 0x9E3779B9 / 0xBB67AE85; pinned by the known-answer vectors
+ * distributed with the authors' Random123 library (tests/test_rng_philox.py). */
+void nto_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]) {
+  uint32_t c0 = ctr[0], c1 = ctr[1], c2 = ctr[2], c3 = ctr[3], k0 = key[0], k1 = key[1];
+  for (int r = 0; r < 10; ++r) {
+    uint64_t a = (uint64_t)0xD2511F53u * c0, b = (uint64_t)0xCD9E8D57u * c2;
+    uint32_t n0 = (uint32_t)(b >> 32) ^ c1 ^ k0, n2 = (uint32_t)(a >> 32) ^ c3 ^ k1;
+    c1 = (uint32_t)b;
+    c3 = (uint32_t)a;
+    c0 = n0;
+    c2 = n2;
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+
+/* The library's stream layout: block b = philox(ctr = {lo(offset+b), hi(offset+b), 0, 0}, key = seed);
+ * four floats per block, (word >> 8) * 2^-24. */
+void nto_philox_uniform_f32(uint64_t seed, uint64_t offset, float *out, int64_t n) {
+  for (int64_t b = 0; b * 4 < n; ++b) {
+    uint64_t at = offset + (uint64_t)b;
+    uint32_t ctr[4] = {(uint32_t)at, (uint32_t)(at >> 32), 0u, 0u}, key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)}, w[4];
+    nto_philox4x32_10(ctr, key, w);
+    for (int j = 0; j < 4 && b * 4 + j < n; ++j) out[b * 4 + j] = (float)(w[j] >> 8) * 5.9604644775390625e-08f;
+  }
+}
+void nto_philox_uniform_f64(uint64_t seed, uint64_t offset, double *out, int64_t n) {
+  for (int64_t b = 0; b * 2 < n; ++b) {
+    uint64_t at = offset + (uint64_t)b;
+    uint32_t ctr[4] = {(uint32_t)at, (uint32_t)(at >> 32), 0u, 0u}, key[2] = {(uint32_t)seed, (uint32_t)(seed >> 32)}, w[4];
+    nto_philox4x32_10(ctr, key, w);
+    for (int j = 0; j < 2 && b * 2 + j < n; ++j)
+      out[b * 2 + j] = (double)((((uint64_t)w[2 * j + 1] << 32) | w[2 * j]) >> 11) * 1.1102230246251565e-16;
+  }
+}

@@ -198,6 +198,17 @@ class PortOracle:
                                      fo.ctypes.data_as(C.c_void_p), C.byref(vo), dims,
                                      C.c_int(len(plan.fancy_dims_in_src)), arrays, is_fancy, target)
 
+    def philox(self, ctr, key) -> list[int]:
+        out = (C.c_uint32 * 4)()
+        self.lib.nto_philox4x32_10((C.c_uint32 * 4)(*ctr), (C.c_uint32 * 2)(*key), out)
+        return list(out)
+
+    def philox_uniform(self, seed: int, offset: int, n: int, dtype=np.float32) -> np.ndarray:
+        out = np.empty(n, dtype)
+        fn = self.lib.nto_philox_uniform_f32 if dtype == np.float32 else self.lib.nto_philox_uniform_f64
+        fn(C.c_uint64(seed), C.c_uint64(offset), out.ctypes.data_as(C.c_void_p), C.c_int64(n))
+        return out
+
     def uniform(self, seed: int, n: int) -> np.ndarray:
         self.lib.nto_rng_sizeof.restype = C.c_int64
         state = C.create_string_buffer(self.lib.nto_rng_sizeof())
