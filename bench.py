@@ -338,8 +338,15 @@ def time_ops(nt, peaks: dict) -> dict:
         ones_row = dev(np.ones((M,), np.float32))
         row_view = ones_row.expand(M, M)._C_view
         record("sum.backward_materialised", stream_time([lambda: _C.clone_contiguous_view_from(row_view)] * 3), M * M * 4)
-        denom_full = _C.TensorView(_C.full(1, float(M), F32, CUDA), (M, M), (0, 0), 0)
-        record("mean.backward", stream_time([lambda: _C.divide(row_view, denom_full)] * 3), M * M * 4)
+        # mean backward: the kept elements are divided once, the quotient is expanded as a stride-0 view;
+        # a consumer that needs it dense pays the materialising broadcast
+        denom_row = _C.TensorView(_C.full(1, float(M), F32, CUDA), (M,), (0,), 0)
+
+        def mean_backward():
+            q = _C.divide(ones_row._C_view, denom_row)
+            return _C.clone_contiguous_view_from(_C.TensorView(q, (M, M), (0, 1), 0))
+
+        record("mean.backward_materialised", stream_time([mean_backward] * 3), M * M * 4)
         m1 = [t.max((1,)) for t in X]
         g_full = ones_row.reshape(M, 1).expand(M, M)._C_view
         m_full = [m.reshape(M, 1).expand(M, M)._C_view for m in m1]

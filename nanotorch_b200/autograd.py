@@ -497,7 +497,10 @@ class MeanOp(_ReductionOp):
     def backward(self, g):
         if not self._orig_shape:
             return (g,)
-        return (_expand_back(g, self._orig_shape, self._axis) / self._denom,)
+        # The reference divides the expanded gradient element by element (autograd/ops_reduction.py:129-137);
+        # dividing the kept elements once and expanding the quotient (a stride-0 view, like Sum's
+        # gradient) yields the same bits without a division and a write per input element.
+        return (_expand_back(g / self._denom, self._orig_shape, self._axis),)
 
 
 class _ExtremumOp(_ReductionOp):
