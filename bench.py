@@ -702,7 +702,7 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
 
 PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
-                 "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows")
+                 "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows", "gemm_step_shapes")
 
 
 def profile_case(name: str, launches: int = 3) -> None:
@@ -716,6 +716,15 @@ def profile_case(name: str, launches: int = 3) -> None:
     if name == "gemm4096":
         a, b = dev(r(30).uniform(-1, 1, (4096, 4096))), dev(r(31).uniform(-1, 1, (4096, 4096)))
         fn = lambda: _C.matmul(a._C_view, b._C_view)  # noqa: E731
+    elif name == "gemm_step_shapes":
+        # the two GEMM shapes of the benchmark's training step: activation @ weight (forward and input
+        # gradient, 16384 x 4096 x 4096) and activation^T @ gradient (weight gradient, 4096 x 4096 x 16384)
+        x, w = dev(r(40).standard_normal((16384, 4096))), dev(r(31).uniform(-0.04, 0.04, (4096, 4096)))
+        g = dev(r(32).standard_normal((16384, 4096)))
+        launches = 1
+
+        def fn():
+            return _C.matmul(x._C_view, w._C_view), _C.matmul(x.T._C_view, g._C_view)
     elif name.startswith("add4096"):
         a, b = dev(r(10).uniform(-1, 1, (4096, 4096))), dev(r(11).uniform(-1, 1, (4096, 4096)))
         v = dev(r(13).uniform(-1, 1, (4096,)))

@@ -216,13 +216,17 @@ __global__ void __launch_bounds__(256) ew_strided(F f, EwParams p) {
 // second-to-last (I), z = product of the leading dims.  256 threads own a 64x64 tile; in output
 // order a thread holds rows ty+16r (r=0..3), columns 4*tx..4*tx+3.
 constexpr int TILE = 64;
+constexpr int TILE_PITCH = TILE + 1;
+// Shared memory is dynamic: one TILE x (TILE+1) slot per staged (column-major) operand, so that a launch
+// with a single transposed operand holds 8 CTAs per SM instead of 6.  The row-major operands' global
+// loads are issued before the staging barrier: their latency overlaps the staging of the tile.
 template <class F, int NIN>
-__global__ void __launch_bounds__(256) ew_tile2d(F f, EwParams p) {
+__global__ void __launch_bounds__(256, 4) ew_tile2d(F f, EwParams p) {
   using TI = typename F::in_t;
   using TO = typename F::out_t;
   static_assert(sizeof(TI) == 4 && sizeof(TO) == 4, "tile path is for 4-byte types");
-  constexpr int NSLOT = (NIN < 2) ? NIN : 2; // at most two staged operands (48 KB static limit)
-  __shared__ TI tile[NSLOT][TILE][TILE + 1];
+  extern __shared__ __align__(16) unsigned char tile_raw[];
+  TI(*tile)[TILE][TILE_PITCH] = reinterpret_cast<TI(*)[TILE][TILE_PITCH]>(tile_raw);
 
   const int dI = p.ndim - 2, dJ = p.ndim - 1;
   const int64_t nI = p.shape[dI], nJ = p.shape[dJ];
@@ -245,35 +249,72 @@ __global__ void __launch_bounds__(256) ew_tile2d(F f, EwParams p) {
 
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
 
-  // stage the column-major operands: read along I (their unit-stride dim), 4 elements per thread
+  // (1) row-major operands: this thread's output-order values (rows ty+16r, columns 4tx..4tx+3), loaded now
+  TI v[4][NIN][4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int64_t i = i0 + ty + 16 * r;
+    const int64_t j = j0 + 4 * tx;
+    const bool live = i < nI && j < nJ;
+    const bool full = (j + 3 < nJ);
+#pragma unroll
+    for (int o = 0; o < NIN; ++o) {
+      if (p.col_major[o + 1] || !live) continue;
+      const TI *src = static_cast<const TI *>(p.in[o]) + base[o + 1] + i * p.strides[o + 1][dI];
+      const int64_t sJ = p.strides[o + 1][dJ];
+      if (sJ == 0) {
+        TI x = *src;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[r][o][e] = x;
+      } else if (p.vec_mode[o + 1] == 1 && full) {
+        float4 x = __ldcs(reinterpret_cast<const float4 *>(src + j));
+        const TI *px = reinterpret_cast<const TI *>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[r][o][e] = px[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[r][o][e] = (j + e < nJ) ? src[(j + e) * sJ] : TI(0);
+      }
+    }
+  }
+
+  // (2) stage the column-major operands: read along I (their unit-stride dim), 4 elements per thread
 #pragma unroll
   for (int o = 0; o < NIN; ++o) {
     if (p.col_major[o + 1]) {
       const int slot = p.col_major[o + 1] - 1;
       const TI *src = static_cast<const TI *>(p.in[o]) + base[o + 1];
       const int64_t sJ = p.strides[o + 1][dJ]; // stride along J; stride along I is 1
+      float4 x[4];
+      bool vec[4];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const int64_t j = j0 + ty + 16 * r;
         const int64_t i = i0 + 4 * tx;
-        if (j < nJ) {
+        vec[r] = j < nJ && p.vec_mode[o + 1] == 1 && i + 3 < nI;
+        if (vec[r]) x[r] = __ldcs(reinterpret_cast<const float4 *>(src + j * sJ + i));
+      }
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int64_t j = j0 + ty + 16 * r;
+        const int64_t i = i0 + 4 * tx;
+        if (j >= nJ) continue;
+        if (vec[r]) {
+          const TI *px = reinterpret_cast<const TI *>(&x[r]);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) tile[slot][ty + 16 * r][4 * tx + e] = px[e];
+        } else {
           const TI *q = src + j * sJ + i;
-          if (p.vec_mode[o + 1] == 1 && i + 3 < nI) {
-            float4 x = __ldcs(reinterpret_cast<const float4 *>(q));
-            const TI *px = reinterpret_cast<const TI *>(&x);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) tile[slot][ty + 16 * r][4 * tx + e] = px[e];
-          } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              if (i + e < nI) tile[slot][ty + 16 * r][4 * tx + e] = q[e];
-          }
+          for (int e = 0; e < 4; ++e)
+            if (i + e < nI) tile[slot][ty + 16 * r][4 * tx + e] = q[e];
         }
       }
     }
   }
   __syncthreads();
 
+  // (3) transposed reads from the tile, the functor, coalesced stores
   TO *dst = static_cast<TO *>(p.out) + base[0];
   const int64_t oI = p.strides[0][dI], oJ = p.strides[0][dJ];
 #pragma unroll
@@ -282,37 +323,20 @@ __global__ void __launch_bounds__(256) ew_tile2d(F f, EwParams p) {
     const int64_t j = j0 + 4 * tx;
     if (i >= nI || j >= nJ) continue;
     const bool full = (j + 3 < nJ);
-    TI v[NIN][4];
 #pragma unroll
     for (int o = 0; o < NIN; ++o) {
       if (p.col_major[o + 1]) {
         const int slot = p.col_major[o + 1] - 1;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[o][e] = tile[slot][4 * tx + e][ty + 16 * r];
-      } else {
-        const TI *src = static_cast<const TI *>(p.in[o]) + base[o + 1] + i * p.strides[o + 1][dI];
-        const int64_t sJ = p.strides[o + 1][dJ];
-        if (sJ == 0) {
-          TI x = *src;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) v[o][e] = x;
-        } else if (p.vec_mode[o + 1] == 1 && full) {
-          float4 x = __ldcs(reinterpret_cast<const float4 *>(src + j));
-          const TI *px = reinterpret_cast<const TI *>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) v[o][e] = px[e];
-        } else {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) v[o][e] = (j + e < nJ) ? src[(j + e) * sJ] : TI(0);
-        }
+        for (int e = 0; e < 4; ++e) v[r][o][e] = tile[slot][4 * tx + e][ty + 16 * r];
       }
     }
     TO res[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      if constexpr (NIN == 1) res[e] = f(v[0][e]);
-      if constexpr (NIN == 2) res[e] = f(v[0][e], v[1][e]);
-      if constexpr (NIN == 3) res[e] = f(v[0][e], v[1][e], v[2][e]);
+      if constexpr (NIN == 1) res[e] = f(v[r][0][e]);
+      if constexpr (NIN == 2) res[e] = f(v[r][0][e], v[r][1][e]);
+      if constexpr (NIN == 3) res[e] = f(v[r][0][e], v[r][1][e], v[r][2][e]);
     }
     TO *q = dst + i * oI + j * oJ;
     if (p.vec_mode[0] == 1 && full) {
@@ -406,7 +430,8 @@ template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NI
             p.vec_mode[o] = vec_ok(o, dJ) ? 1 : 0;
         }
         dim3 grid(unsigned(ceil_div(it.shape[dJ], TILE)), unsigned(ceil_div(it.shape[dI], TILE)), unsigned(lead));
-        ew_tile2d<F, NIN><<<grid, 256, 0, st>>>(f, p);
+        const size_t smem = size_t(n_col) * TILE * TILE_PITCH * sizeof(TI); // at most 2 slots = 33 KB: below the 48 KB default limit
+        ew_tile2d<F, NIN><<<grid, 256, smem, st>>>(f, p);
         check_launch("ew_tile2d");
         return;
       }

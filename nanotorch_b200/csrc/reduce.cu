@@ -690,6 +690,52 @@ __global__ void __launch_bounds__(256) extremum_apply_vec(const float *__restric
   __stcs(reinterpret_cast<float4 *>(out + outer * L + inner), make_float4(res[0], res[1], res[2], res[3]));
 }
 
+// One pass for ROWS slices of at most 16384 elements: a CTA keeps its whole slice in registers (VPT
+// 128-bit vectors per thread), counts the positions equal to the extremum, and writes the gradient from
+// the registers -- x is read once: 8 bytes per element instead of 12, no counter array, one launch.
+template <int VPT>
+__global__ void __launch_bounds__(256) extremum_rows_onepass(const float *__restrict__ x, const float *__restrict__ g,
+                                                             const float *__restrict__ m, float *__restrict__ out,
+                                                             SliceScalars sc, int64_t L) {
+  __shared__ int warp_cnt[8];
+  const int64_t row = blockIdx.x;
+  const float4 *pv = reinterpret_cast<const float4 *>(x + slice_offset(sc.x_keep, row));
+  const float mv = m[slice_offset(sc.m_keep, row)];
+  const float gv = g[slice_offset(sc.g_keep, row)];
+  const int nvec = int(L >> 2);
+  float4 v[VPT];
+  int n = 0;
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int i = threadIdx.x + u * 256;
+    if (i < nvec) {
+      v[u] = __ldcs(pv + i);
+      n += (v[u].x == mv) + (v[u].y == mv) + (v[u].z == mv) + (v[u].w == mv);
+    }
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) n += __shfl_xor_sync(0xffffffffu, n, s);
+  if ((threadIdx.x & 31) == 0) warp_cnt[threadIdx.x >> 5] = n;
+  __syncthreads();
+  int total = 0;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) total += warp_cnt[w];
+  const bool unique = total == 1;
+  float4 *po = reinterpret_cast<float4 *>(out + row * L);
+#pragma unroll
+  for (int u = 0; u < VPT; ++u) {
+    const int i = threadIdx.x + u * 256;
+    if (i < nvec) {
+      float4 r;
+      r.x = gv * ((v[u].x == mv && unique) ? 1.0f : 0.0f);
+      r.y = gv * ((v[u].y == mv && unique) ? 1.0f : 0.0f);
+      r.z = gv * ((v[u].z == mv && unique) ? 1.0f : 0.0f);
+      r.w = gv * ((v[u].w == mv && unique) ? 1.0f : 0.0f);
+      __stcs(po + i, r);
+    }
+  }
+}
+
 // Returns false when the views do not have one of the two shapes above (the caller then composes).
 static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt_view *m, const int64_t *axes,
                                     int32_t n_axes, float *out) {
@@ -729,6 +775,22 @@ static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt
   const bool cols = !rows && leading && pl.drop.ndim == 1 && pl.keep.ndim == 1 && pl.keep.strides[0] == 1;
   if (!rows && !cols) return false;
   if (pl.n_keep * pl.n_drop >= (int64_t(1) << 40)) return false;
+  if (rows) {
+    const int64_t L = pl.n_drop;
+    bool vec = (L % 4 == 0) && aligned16(xp) && aligned16(out);
+    for (int k = 0; k < sc.x_keep.ndim; ++k) vec = vec && (sc.x_keep.strides[k] % 4 == 0);
+    if (vec && L <= 16384 && pl.n_keep >= sm_count() && pl.n_keep <= 0x7fffffffLL) {
+      const unsigned grid = unsigned(pl.n_keep);
+      const int64_t per_thread = ceil_div(L / 4, 256);
+      if (per_thread <= 1) extremum_rows_onepass<1><<<grid, 256, 0, st>>>(xp, gp, mp, out, sc, L);
+      else if (per_thread <= 2) extremum_rows_onepass<2><<<grid, 256, 0, st>>>(xp, gp, mp, out, sc, L);
+      else if (per_thread <= 4) extremum_rows_onepass<4><<<grid, 256, 0, st>>>(xp, gp, mp, out, sc, L);
+      else if (per_thread <= 8) extremum_rows_onepass<8><<<grid, 256, 0, st>>>(xp, gp, mp, out, sc, L);
+      else extremum_rows_onepass<16><<<grid, 256, 0, st>>>(xp, gp, mp, out, sc, L);
+      check_launch("extremum_rows_onepass");
+      return true;
+    }
+  }
   size_t rounded = 0;
   int *count = static_cast<int *>(device_alloc(size_t(pl.n_keep) * sizeof(int), &rounded));
   NT_CUDA_CHECK(cudaMemsetAsync(count, 0, size_t(pl.n_keep) * sizeof(int), st));

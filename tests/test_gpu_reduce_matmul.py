@@ -273,3 +273,29 @@ def test_matmul_errors(nt):
         nt._C.matmul(a._C_view, b._C_view)  # native check: std::invalid_argument -> ValueError
     with pytest.raises(ValueError):
         nt._C.matmul(a._C_view, dev(nt, np.zeros((2, 4, 6), np.float32))._C_view)
+
+
+@pytest.mark.parametrize("L", [4, 260, 1024, 4100, 8192, 16384, 16388, 1023])
+def test_extremum_backward_row_slices_with_ties(nt, port, L):
+    """Max/min over the last dim with enough slices for the one-pass kernel (slice kept in registers,
+    L <= 16384 and a multiple of 4) and for the two-launch path beyond it; a third of the slices carry a
+    tied extremum (zero gradient there, the reference's integer-division quirk); upstream gradient random."""
+    rng = np.random.default_rng(L)
+    rows = 333
+    x = rng.standard_normal((rows, L)).astype(np.float32)
+    tied = rng.random(rows) < 0.33
+    for r in np.flatnonzero(tied):
+        i, j = rng.choice(L, 2, replace=False)
+        x[r, i] = x[r, j] = 9.0          # two positions share the maximum
+        x[r, (i + 1) % L if (i + 1) % L != j else (i + 2) % L] = -9.0
+    g = rng.standard_normal((rows,)).astype(np.float32)
+    for name, sign in (("max", 1.0), ("min", -1.0)):
+        xs = (x * sign).astype(np.float32)
+        t = dev(nt, xs, True)
+        red = getattr(t, name)((1,))
+        (red * dev(nt, g)).sum().backward()
+        m = xs.max(axis=1) if name == "max" else xs.min(axis=1)
+        want = O.extremum_backward(port, np.broadcast_to(g[:, None], xs.shape), xs,
+                                   np.broadcast_to(m[:, None], xs.shape), [1])
+        assert_bit_exact(t.grad.numpy(), want, f"{name} backward, L={L}")
+        assert (want[tied] == 0).all() and (np.abs(want[~tied]).sum(axis=1) > 0).all()
