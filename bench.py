@@ -676,7 +676,13 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
             "roofline": {
                 "kernel": "gemm_3xtf32 (tcgen05.mma kind::tf32, 3 products per fp32 product)",
                 "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                "frac": (achieved / tf32_peak) if achieved else None, "traffic": None,
+                "frac": (achieved / tf32_peak) if achieved else None,
+                # DRAM bytes per launch from the ncu capture of the step's two GEMM shapes at the full per-GPU
+                # batch (profiles/gemm_3xtf32_step_shapes_dram_traffic.md), weighted 15 : 8 as in one step;
+                # tile re-reads do not scale with the shard, so there is no figure for other shapes
+                "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH if (local == GLOBAL_BATCH and _C.get_matmul_mode() == 1) else None,
+                "traffic_unit": "bytes/launch (dram__bytes_read.sum + dram__bytes_write.sum)",
+                "algorithmic_bytes_per_launch": (15 * 939.5e6 + 8 * 1140.9e6) / 23 if local == GLOBAL_BATCH else None,
                 "peak_source": f"{peaks['source']}: sustained bf16 cuBLAS rate / 2 (TF32 issues at half the bf16 rate; "
                                f"no TF32 figure is recorded)",
                 "launches": gemm_launches, "avg_launch_ms": avg_ms,
@@ -700,6 +706,9 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
     if dist is not None:
         dist.destroy_process_group()
 
+
+# (15 * 2760.6 MB + 8 * 2998.1 MB) / 23: forward / input-gradient shape and weight-gradient shape of the step
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = 2.843e9
 
 PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
                  "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows", "gemm_step_shapes")
