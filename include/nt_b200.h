@@ -194,6 +194,12 @@ int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float 
 
 /* ------------------------------------------------------------------ matmul (src/cpp/ops/matmul.cu:236-273) */
 int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out);
+/* x @ w + bias in one call (no single counterpart: nn.Linear.forward composes matmul and a broadcast add,
+ * src/nanotorch/nn/module.py:64-76).  bias is 1-D with one fp32 value per output column.  Two rounded
+ * steps, exactly as the composed form: the product rounded to fp32, then the sum with the bias rounded
+ * again -- bit-identical to nt_matmul followed by nt_add.  In matmul mode 1 the second step runs in the
+ * GEMM kernel's epilogue (no extra launch, no second pass over the output). */
+int nt_linear(const nt_view *x, const nt_view *w, const nt_view *bias, nt_storage **out);
 /* fp32 product mode.
  *   0  exact FP32 on the CUDA cores (FMA, sequential in k: the rounding of the reference's CUDA kernels);
  *   1  (default) 3xTF32 on the tcgen05 tensor cores with promoted accumulation: chains of 256 values of k

@@ -379,6 +379,11 @@ min = _reduction("min")  # noqa: A001
 argmax = _reduction("argmax")
 argmin = _reduction("argmin")
 
+def linear(x: TensorView, w: TensorView, bias: TensorView) -> Storage:
+    """x @ w + bias with the bias add fused into the GEMM epilogue (addition to the reference's surface)."""
+    return _ret_storage(_lib.nt_linear, _vref(x), _vref(w), _vref(bias))
+
+
 # ---- in-place (src/cpp/ops/inplace_ops.cu:81-92)
 add_inplace = _inplace("add_inplace")
 sub_inplace = _inplace("sub_inplace")

@@ -310,6 +310,41 @@ class MatmulOp(Function):
         return B * (M * K + K * N + M * N) * sizeof(promote_dtypes(x1.dtype, x2.dtype))
 
 
+class LinearOp(Function):
+    """x @ W + b for a 2-D fp32 x on the device, as one call: the bias add runs in the GEMM epilogue.
+
+    Not a class of the reference (its Linear.forward composes MatmulOp and AddOp,
+    src/nanotorch/nn/module.py:64-76); forward bits and all three gradients are those of the composed
+    form: dX = g @ W^T, dW = x^T @ g (MatmulOp.backward), db = column sums of g (AddOp.backward's
+    unbroadcast)."""
+
+    @staticmethod
+    def applicable(x, W, b) -> bool:
+        return (x.ndim == 2 and W.ndim == 2 and b.ndim == 1 and b.shape[0] == W.shape[1]
+                and x.dtype == W.dtype == b.dtype == Dtype.Float32
+                and x.device == W.device == b.device == Device.Cuda and x.numel > 0 and W.numel > 0)
+
+    def forward(self, x, W, b):
+        self.save_for_backward(x, W)
+        self._bias_shape = b.shape
+        return Tensor._new_contiguous(_C.linear(x._C_view, W._C_view, b._C_view), (x.shape[0], W.shape[1]))
+
+    def backward(self, g):
+        x, W = self.saved_tensors
+        gx = g @ W.transpose(-2, -1) if _need(self, 0) else None
+        gW = x.transpose(-2, -1) @ g if _need(self, 1) else None
+        gb = unbroadcast(g, self._bias_shape) if _need(self, 2) else None
+        return gx, gW, gb
+
+    @classmethod
+    def flops(cls, x, W, b) -> int:
+        return 2 * x.shape[0] * W.shape[1] * x.shape[1] + x.shape[0] * W.shape[1]
+
+    @classmethod
+    def mem_bytes(cls, x, W, b) -> int:
+        return (x.numel + W.numel + b.numel + x.shape[0] * W.shape[1]) * 4
+
+
 # =============================================================================================
 # unary
 class _UnaryOp(Function):

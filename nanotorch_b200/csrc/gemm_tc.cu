@@ -203,6 +203,8 @@ struct TcArgs {
   int32_t num_kb;   // k-blocks of TC_BK
   int32_t batch;    // number of batches (plane index of `lo` = batch + b)
   int32_t c_vec;    // rows of C may be written 128 bits at a time
+  const float *bias;    // promoted kernel only: C[m][n] = fl(fl(sum) + bias[n * bias_stride]) when non-null
+  int64_t bias_stride;
   int *error_flag;
 };
 
@@ -532,6 +534,13 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (ok && m < g.M) {
       float *crow = g.C + (int64_t(b) * g.M + m) * g.N;
       const int64_t n = int64_t(n0) + half * 128;
+      if (g.bias) {
+        // the second rounded step of x @ W + b: the fp32 product that a separate launch would have
+        // stored, plus the bias, rounded once more (every lane reads the same bias word: one broadcast)
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (n + i < g.N) sum[i] = sum[i] + __ldg(g.bias + (n + i) * g.bias_stride);
+      }
 #pragma unroll
       for (int q = 0; q < 32; ++q) {
         const int64_t nn = n + 4 * q;
@@ -637,8 +646,12 @@ static void launch_split(const float *src, float *planes, int64_t batch, int64_t
 static std::atomic<int> g_promoted{1};
 void gemm_tc_set_promoted(bool on) { g_promoted.store(on ? 1 : 0); }
 
+// `bias` (N values, element stride bias_stride) is added in the epilogue of the promoted kernel only;
+// *bias_done tells the caller whether it was.
 bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_t M, int64_t N, int64_t K,
-                 int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn) {
+                 int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn,
+                 const float *bias, int64_t bias_stride, bool *bias_done) {
+  if (bias_done) *bias_done = false;
   // limits of one launch / one tensor map
   if (batch < 1 || batch > 32767 || M < 1 || N < 1 || K < 1) return false;
   if (ceil_div(M, TC_BM) > 65535 || ceil_div(N, TC_BN) > 0x7fffffff) return false;
@@ -667,6 +680,13 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
     g.batch = int32_t(batch);
     g.c_vec = (N % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
     g.error_flag = error_flag_ptr();
+    g.bias = nullptr;
+    g.bias_stride = 0;
+    if (bias && g_promoted.load()) {
+      g.bias = bias;
+      g.bias_stride = bias_stride;
+      if (bias_done) *bias_done = true;
+    }
     dim3 grid{unsigned(ceil_div(N, TC_BN)), unsigned(ceil_div(M, TC_BM)), unsigned(batch)};
     matmul_profile_begin();
     if (g_promoted.load())

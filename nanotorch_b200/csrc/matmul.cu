@@ -20,7 +20,8 @@ namespace ntb {
 
 // implemented in gemm_tc.cu; returns false when the shape/layout is outside what it supports
 bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_t M, int64_t N, int64_t K,
-                 int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn);
+                 int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn,
+                 const float *bias, int64_t bias_stride, bool *bias_done);
 void gemm_tc_set_promoted(bool on);
 
 static std::atomic<int> g_matmul_mode{1};
@@ -304,8 +305,10 @@ int nt_set_matmul_mode(int mode) {
 }
 int nt_get_matmul_mode(void) { return g_matmul_mode.load(); }
 
-int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
-  NT_API_BEGIN
+// x1 @ x2, plus -- when `bias` is given (fp32, N values) -- the broadcast add of the bias as a second
+// rounded step: in the tensor-core kernel's epilogue where that kernel runs, by an in-place add launch
+// otherwise.  Either way the bits are those of matmul followed by add.
+static nt_storage *matmul_impl(const nt_view *x1, const nt_view *x2, const nt_view *bias) {
   check_view(x1, "matmul");
   check_view(x2, "matmul");
   require_same_device(x1, x2, "matmul");
@@ -332,10 +335,8 @@ int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
 
   const int64_t total = nbatch * M * N;
   StorageRef o(storage_new(total, dt, NT_CUDA));
-  if (total == 0) {
-    *out = o.release();
-    return NT_OK;
-  }
+  if (total == 0) return o.release();
+  bool bias_done = false;
   const int64_t a_sm = x1->strides[nd - 2], a_sk = x1->strides[nd - 1];
   const int64_t b_sk = x2->strides[nd - 2], b_sn = x2->strides[nd - 1];
 
@@ -365,7 +366,10 @@ int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
         a_sb = bi.a_strides[bi.ndim - 1];
         b_sb = bi.b_strides[bi.ndim - 1];
       }
-      if (single) done = gemm_3xtf32(g.A, g.B, g.C, nbatch, M, N, K, a_sb, a_sm, a_sk, b_sb, b_sk, b_sn);
+      const float *bp = bias ? static_cast<const float *>(bias->storage->data) + bias->offset : nullptr;
+      if (single)
+        done = gemm_3xtf32(g.A, g.B, g.C, nbatch, M, N, K, a_sb, a_sm, a_sk, b_sb, b_sk, b_sn, bp,
+                           bias ? bias->strides[0] : 0, &bias_done);
     }
     if (!done) {
       matmul_profile_begin();
@@ -385,7 +389,44 @@ int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
       }
     });
   }
-  *out = o.release();
+  if (bias && !bias_done) {
+    // out += bias (broadcast over the rows) through the ordinary in-place add
+    nt_view ov{}, bv{};
+    ov.storage = o.s;
+    ov.ndim = nd;
+    bv.storage = bias->storage;
+    bv.ndim = nd;
+    bv.offset = bias->offset;
+    int64_t acc = 1;
+    for (int d = nd - 1; d >= 0; --d) {
+      ov.shape[d] = bv.shape[d] = (d == nd - 1) ? N : (d == nd - 2 ? M : x1->shape[d]);
+      ov.strides[d] = acc;
+      acc *= ov.shape[d];
+      bv.strides[d] = (d == nd - 1) ? bias->strides[0] : 0;
+    }
+    if (nt_add_inplace(&ov, &bv) != NT_OK) fail_runtime(std::string("linear: bias add failed: ") + nt_last_error());
+    o->version = 0; // a fresh result, not a mutated tensor
+  }
+  return o.release();
+}
+
+int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
+  NT_API_BEGIN
+  *out = matmul_impl(x1, x2, nullptr);
+  NT_API_END
+}
+
+int nt_linear(const nt_view *x, const nt_view *w, const nt_view *bias, nt_storage **out) {
+  NT_API_BEGIN
+  check_view(bias, "linear");
+  check_view(w, "linear");
+  if (bias->ndim != 1 || w->ndim < 2 || bias->shape[0] != w->shape[w->ndim - 1])
+    fail_invalid("linear: bias must be 1-D with one value per output column.");
+  if (bias->storage->dtype != NT_FLOAT32 || w->storage->dtype != NT_FLOAT32 || x->storage == nullptr ||
+      x->storage->dtype != NT_FLOAT32)
+    fail_invalid("linear: Float32 only.");
+  require_cuda(bias, "linear");
+  *out = matmul_impl(x, w, bias);
   NT_API_END
 }
 

@@ -12,7 +12,7 @@ import math
 from typing import Any, Sequence
 
 from . import _C, rand, zeros
-from .autograd import ReluOp, TanhOp, no_grad
+from .autograd import LinearOp, ReluOp, TanhOp, no_grad
 from .tensor import Tensor
 from ._C import Device, Dtype
 
@@ -63,6 +63,8 @@ class Linear(Module):
             raise NotImplementedError(f"Can only forward a 2D tensor for now, got {x.ndim}")
         if x.shape[1] != self._W.shape[0]:
             raise ValueError(f"Cannot align axes of size {x.shape[1]} and {self._W.shape[0]}.")
+        if self._b is not None and LinearOp.applicable(x, self._W, self._b):
+            return LinearOp.apply(x, self._W, self._b)  # same bits as the two steps below, one launch fewer
         z = x @ self._W
         if self._b is not None:
             z = z + self._b

@@ -123,3 +123,45 @@ def test_captured_step_replays_bit_exact(nt):
     assert np.array_equal(eager_losses, graph_losses), (eager_losses, graph_losses)
     for a, b in zip(eager_params, graph_params):
         assert_bit_exact(a, b, "parameters after replayed steps")
+
+
+@pytest.mark.parametrize("mode", [1, 3, 0, 2])
+def test_fused_linear_is_the_composed_form_bit_for_bit(nt, mode):
+    """nn.Linear's one-call path (bias added in the GEMM epilogue in mode 1, by an in-place add in the
+    other modes) against matmul followed by a broadcast add: forward and all three gradients."""
+    import nanotorch_b200.nn as nn
+
+    rng = np.random.default_rng(77)
+    nt._C.set_matmul_mode(mode)
+    try:
+        for m, k, n in [(64, 48, 10), (257, 100, 130), (512, 256, 384), (1000, 64, 4096)]:
+            layer = nn.Linear(k, n)
+            W, b = layer.parameters()
+            with nt.no_grad():
+                b += nt.Tensor.from_numpy(rng.standard_normal(n).astype(np.float32), "cuda")  # a non-zero bias
+            x_np = rng.standard_normal((m, k)).astype(np.float32)
+            g_np = rng.standard_normal((m, n)).astype(np.float32)
+            grads = []
+            outs = []
+            for fused in (True, False):
+                x = nt.Tensor.from_numpy(x_np, "cuda", requires_grad=True)
+                for p in (W, b):
+                    p.zero_grad()
+                z = layer(x) if fused else (x @ W) + b
+                assert (z.grad_fn.__class__.__name__ == "LinearOp") == fused
+                (z * nt.Tensor.from_numpy(g_np, "cuda")).sum().backward()
+                outs.append(z.numpy())
+                grads.append((x.grad.numpy(), W.grad.numpy(), b.grad.numpy()))
+            assert_bit_exact(outs[0], outs[1], f"forward {m}x{k}x{n} mode {mode}")
+            for got, want, what in zip(grads[0], grads[1], ("dX", "dW", "db")):
+                assert_bit_exact(got, want, f"{what} {m}x{k}x{n} mode {mode}")
+        # a strided bias view and the raw entry point's checks
+        W = nt.Tensor.from_numpy(rng.standard_normal((32, 20)).astype(np.float32), "cuda")
+        x = nt.Tensor.from_numpy(rng.standard_normal((16, 32)).astype(np.float32), "cuda")
+        wide = nt.Tensor.from_numpy(rng.standard_normal((40,)).astype(np.float32), "cuda")
+        got = nt.Tensor._new_contiguous(nt._C.linear(x._C_view, W._C_view, wide[::2]._C_view), (16, 20))
+        assert_bit_exact(got.numpy(), ((x @ W) + wide[::2]).numpy(), "strided bias")
+        with pytest.raises(ValueError):
+            nt._C.linear(x._C_view, W._C_view, wide._C_view)
+    finally:
+        nt._C.set_matmul_mode(1)

@@ -107,3 +107,16 @@ def test_shard_bounds_partition_the_batch():
         assert max(sizes) - min(sizes) <= 1
     with pytest.raises(ValueError):
         shard_bounds(8, 2, 2)
+
+
+def test_linear_one_call_path_is_device_only(nt):
+    """LinearOp (bias fused into the GEMM) is chosen for 2-D fp32 device tensors only; everything else
+    takes the composed matmul + add of the reference."""
+    from nanotorch_b200.autograd import LinearOp
+
+    x = nt.Tensor([[1.0, 2.0, 3.0, 4.0]])
+    W = nt.Tensor([[0.5] * 3] * 4)
+    b = nt.Tensor([0.0, 1.0, 2.0])
+    assert not LinearOp.applicable(x, W, b)              # Cpu storages
+    with pytest.raises(RuntimeError, match="requires Cuda"):
+        (x @ W) + b
