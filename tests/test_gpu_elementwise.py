@@ -246,3 +246,39 @@ def test_fused_backward_full_size(nt, port, big, name):
     else:
         scale = np.abs(G) * np.maximum(1.0, np.abs(chain / np.where(G == 0, 1, G))) + 1e-30
         assert_scaled(got, chain, scale, 2 * EPS, name)
+
+
+def test_default_tanh_and_sigmoid_equal_their_host_evaluation(nt, tmp_path):
+    """The default tanh and the sigmoid are proven on the HOST (tests/test_tanh_restatement.py: every
+    float argument within 2 ulp of the libm-based reference).  That proof carries over to the GPU only if
+    the device evaluates the same header to the same bits: compile nanotorch_b200/csrc/cr_math.h with gcc
+    and compare with the kernels' output bit for bit on 2^24 N(0,1) values, a sweep of U(-100, 100), the
+    small-argument region and the special values."""
+    import ctypes
+    import subprocess
+    from pathlib import Path
+
+    csrc = Path(nt.__file__).resolve().parent / "csrc"
+    src = tmp_path / "cr_host.c"
+    src.write_text('#include "cr_math.h"\n'
+                   "void eval(const float *x, float *t, float *s, long n) {\n"
+                   "  for (long i = 0; i < n; ++i) { t[i] = nt_tanh_fast_f32(x[i]); s[i] = nt_sigmoid_f32(x[i]); }\n}\n")
+    lib_path = tmp_path / "libcr_host.so"
+    subprocess.run(["gcc", "-O2", "-shared", "-fPIC", "-fno-fast-math", "-ffp-contract=off", f"-I{csrc}",
+                    "-o", str(lib_path), str(src), "-lm"], check=True)
+    host = ctypes.CDLL(str(lib_path))
+    rng = np.random.default_rng(99)
+    x = np.concatenate([
+        rng.standard_normal(1 << 24).astype(np.float32),
+        rng.uniform(-100, 100, 1 << 20).astype(np.float32),
+        (rng.standard_normal(1 << 18) * 2.0 ** rng.integers(-40, 0, 1 << 18)).astype(np.float32),
+        np.array([0.0, -0.0, np.inf, -np.inf, 1e-45, -1e-45, 0.015625, -0.015625, 88.7, -88.7228394, -88.72283,
+                  -104.0, 20.0, 40.0, 41.0, 3e38, -3e38], np.float32)])
+    t = np.empty_like(x)
+    s = np.empty_like(x)
+    host.eval(x.ctypes.data_as(ctypes.c_void_p), t.ctypes.data_as(ctypes.c_void_p), s.ctypes.data_as(ctypes.c_void_p),
+              ctypes.c_long(x.size))
+    d = dev(nt, x)
+    assert nt._C.get_tanh_mode() == nt._C.TANH_CORRECTLY_ROUNDED
+    assert_bit_exact(nt.tanh(d).numpy(), t, "tanh, device vs host evaluation of cr_math.h")
+    assert_bit_exact(nt.sigmoid(d).numpy(), s, "sigmoid, device vs host evaluation of cr_math.h")
