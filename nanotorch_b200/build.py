@@ -36,7 +36,7 @@ def _sources() -> list[Path]:
 
 
 def _headers() -> list[Path]:
-    return sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h"))
+    return sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + sorted(INCLUDE.glob("*.h"))
 
 
 def _stale(target: Path, deps: list[Path]) -> bool:
