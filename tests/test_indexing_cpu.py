@@ -108,6 +108,9 @@ def test_host_plan_uniqueness_and_errors(nt):
         plan_of(([0, 1, 2], [0, 1]))                      # index arrays that do not broadcast
     with pytest.raises(IndexError):
         t[0, 0, 0, [0]]                                   # too many indices
+    empty = plan_of(([],))                                # an empty index list selects nothing
+    assert empty.new_shape == (0, 6, 7) and empty.fancy_dims_data[0].dtype == nt.int64
+    assert plan_of((slice(None), [[]])).new_shape == (5, 1, 0, 7)
     # a basic index still returns a view of the same storage
     assert t[1:3, None, 2].storage is t.storage and t[1:3, None, 2].shape == (2, 1, 7)
 
