@@ -113,6 +113,38 @@ def transpose(x, dim0, dim1): return TransposeOp.apply(x, dim0, dim1)
 def flatten(x): return x.flatten()
 def clone(x): return x.clone()
 def equals(x1, x2): return x1.equals(x2)
+def eq(x, y): return x == y
+def gt(x, y): return x > y
+def geq(x, y): return x >= y
+def lt(x, y): return x < y
+def leq(x, y): return x <= y
+
+
+def _arg_extremum(name, kernel, x, axis, keepdim):
+    """src/nanotorch/ops.py:155-232: index of the extremum along one axis (int) or all axes (None)."""
+    import math
+    if isinstance(axis, int) and not isinstance(axis, bool):
+        full_axis = (axis,)
+    elif axis is None:
+        full_axis = tuple(range(x.ndim))
+    else:
+        raise ValueError(f"Axis must be int or None, found {type(axis)}")
+    if keepdim:
+        new_shape = tuple(1 if i in full_axis else s for i, s in enumerate(x.shape))
+    else:
+        new_shape = tuple(s for i, s in enumerate(x.shape) if i not in full_axis)
+    if x.is_empty:
+        if math.prod(new_shape) != 0:
+            raise IndexError(f"{name}() expects reduction dim to be specified for numel=0.")
+        return Tensor._new_contiguous(_C.zeros(math.prod(new_shape), x.dtype, x.device), new_shape)
+    return Tensor._new_contiguous(kernel(x._C_view, full_axis), new_shape)
+
+
+def argmin(x, axis=None, keepdim=False): return _arg_extremum("argmin", _C.argmin, x, axis, keepdim)
+def argmax(x, axis=None, keepdim=False): return _arg_extremum("argmax", _C.argmax, x, axis, keepdim)
+
+
+TensorLike = Tensor | bool | int | float
 
 
 # ---- factories (src/nanotorch/factories.py)
@@ -143,12 +175,24 @@ def ones(*shape, dtype=Dtype.Float32, requires_grad=False, device=Device.Cpu):
     return _new(_C.ones(math.prod(shape), dtype, std_device(device)), shape, requires_grad)
 
 
-def full(shape, value, dtype=None, requires_grad=False, device=Device.Cpu):
+def full(*shape, value, dtype=Dtype.Float32, requires_grad=False, device=Device.Cpu):
+    """A tensor filled with ``value`` (src/nanotorch/factories.py:83-112): ``full(2, 3, value=1.5)``."""
     import math
-    from .tensor import _dtype_of_scalar, std_device
-    shape = _shape_args((shape,)) if isinstance(shape, (tuple, list)) else (int(shape),)
-    dtype = dtype if dtype is not None else _dtype_of_scalar(value)
+    from .tensor import std_device
+    shape = _shape_args(shape)
     return _new(_C.full(math.prod(shape), value, dtype, std_device(device)), shape, requires_grad)
+
+
+def eye(n, dtype=Dtype.Float32, requires_grad=False, device=Device.Cpu):
+    """The (n, n) identity (src/nanotorch/factories.py:115-142); written by a kernel on the device."""
+    from .tensor import std_device
+    return _new(_C.eye(n, dtype, std_device(device)), (n, n), requires_grad)
+
+
+def arange(n, start=0, step=1, dtype=Dtype.Int64, requires_grad=False, device=Device.Cpu):
+    """``x[i] = start + i * step`` for ``i < n`` (src/nanotorch/factories.py:145-176)."""
+    from .tensor import std_device
+    return _new(_C.arange(n, start, step, dtype, std_device(device)), (n,), requires_grad)
 
 
 def rand(*shape, dtype=Dtype.Float32, requires_grad=False, device=Device.Cpu):
@@ -156,7 +200,24 @@ def rand(*shape, dtype=Dtype.Float32, requires_grad=False, device=Device.Cpu):
     import math
     shape = _shape_args(shape)
     from .tensor import std_device
+    if dtype <= Dtype.Int64:
+        raise ValueError("rand() cannot output non-float values.")
     return _new(_C.uniform(math.prod(shape), dtype, std_device(device)), shape, requires_grad)
+
+
+def randint(low, high, shape=None, dtype=Dtype.Int64, requires_grad=False, device=Device.Cpu):
+    """Random integers in [low, high): ``rand * (high - low) + low`` truncated through Int64, the
+    reference's own recipe (src/nanotorch/factories.py:212-252)."""
+    import math
+    from .tensor import std_device
+    if dtype == Dtype.Bool:
+        raise ValueError("randint() cannot output bool values.")
+    dims = () if shape is None else tuple(shape)
+    base = _new(_C.uniform(math.prod(dims) if dims else 1, Dtype.Float32, std_device(device)), dims, False)
+    base = (base * (high - low) + low).to(Dtype.Int64).to(dtype)
+    if requires_grad:
+        base.enable_grad()
+    return base
 
 
 def tensor(data, **kw):

@@ -63,3 +63,29 @@ def test_device_generator_matches_its_checker(nt, port):
             _C.set_rng_mode(7)
     finally:
         _C.set_rng_mode(_C.RNG_HOST_MT19937_64)
+
+
+def test_functional_forms_on_device(nt):
+    """nt.argmax/argmin/eq/gt/geq/lt/leq, randint, eye, arange through the public functions
+    (src/nanotorch/ops.py:63-85, 155-232; factories.py:115-252)."""
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((37, 130)).astype(np.float32)
+    y = rng.standard_normal((130,)).astype(np.float32)
+    tx, ty = nt.Tensor.from_numpy(x, "cuda"), nt.Tensor.from_numpy(y, "cuda")
+    assert np.array_equal(nt.argmax(tx, 1).numpy(), x.argmax(axis=1)) and nt.argmax(tx, 1).dtype == nt.int64
+    assert np.array_equal(nt.argmin(tx, 0, keepdim=True).numpy(), x.argmin(axis=0)[None, :])
+    assert int(nt.argmax(tx).numpy()) == int(x.argmax())
+    for fn, ref in ((nt.eq, np.equal), (nt.gt, np.greater), (nt.geq, np.greater_equal), (nt.lt, np.less),
+                    (nt.leq, np.less_equal)):
+        got = fn(tx, ty)
+        assert got.dtype == nt.bool_ and np.array_equal(got.numpy(), ref(x, y))
+    assert np.array_equal(nt.eq(tx, tx).numpy(), np.ones_like(x, dtype=bool))
+    nt.manual_seed(7)
+    r = nt.randint(-3, 9, (1000,), device="cuda")
+    assert r.dtype == nt.int64 and r.numpy().min() >= -3 and r.numpy().max() < 9 and len(np.unique(r.numpy())) >= 11
+    nt.manual_seed(7)
+    u = nt.rand(1000, device="cuda").numpy()
+    assert np.array_equal(r.numpy(), (u * np.float32(12) + np.float32(-3)).astype(np.int64))  # the reference's recipe
+    assert np.array_equal(nt.eye(5, device="cuda").numpy(), np.eye(5, dtype=np.float32))
+    assert np.array_equal(nt.arange(6, 2, 3, device="cuda").numpy(), 2 + 3 * np.arange(6))
+    assert nt.randint(0, 2, device="cuda").shape == ()

@@ -120,3 +120,26 @@ def test_linear_one_call_path_is_device_only(nt):
     assert not LinearOp.applicable(x, W, b)              # Cpu storages
     with pytest.raises(RuntimeError, match="requires Cuda"):
         (x @ W) + b
+
+
+def test_factories_and_functional_names_of_the_reference(nt):
+    """Signatures of src/nanotorch/factories.py and ops.py (Cpu storages: no kernel involved)."""
+    assert nt.full(2, 3, value=1.5).tolist() == [[1.5] * 3] * 2 and nt.full(2, value=7, dtype=nt.int64).tolist() == [7, 7]
+    assert nt.eye(3).tolist() == [[1.0, 0.0, 0.0], [0.0, 1.0, 0.0], [0.0, 0.0, 1.0]] and nt.eye(2, dtype=nt.bool_).dtype == nt.bool_
+    assert nt.arange(4, 1, 2).tolist() == [1, 3, 5, 7] and nt.arange(3).dtype == nt.int64
+    assert nt.arange(3, dtype=nt.float32).tolist() == [0.0, 1.0, 2.0] and nt.arange(0).shape == (0,)
+    assert nt.zeros(2, 2).shape == (2, 2) and nt.ones(3, dtype=nt.int32).tolist() == [1, 1, 1]
+    nt.manual_seed(42)
+    u = nt.rand(2)
+    assert abs(u.tolist()[0] - 0.7551555037498474) < 1e-6      # the reference's own known answer for seed 42
+    with pytest.raises(ValueError):
+        nt.rand(2, dtype=nt.int64)
+    with pytest.raises(ValueError):
+        nt.randint(0, 5, (3,), dtype=nt.bool_)
+    with pytest.raises(ValueError):
+        nt.argmax(nt.Tensor([1.0, 2.0]), axis=(0,))
+    with pytest.raises(IndexError):
+        nt.argmin(nt.zeros(0, 3), axis=0)
+    assert nt.argmax(nt.zeros(0, 3), axis=1).shape == (0,)
+    for name in ("eq", "gt", "geq", "lt", "leq", "argmax", "argmin", "randint", "TensorLike"):
+        assert hasattr(nt, name)
