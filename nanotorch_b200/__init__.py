@@ -11,6 +11,7 @@ from .autograd import (ALL_OPS_, AddOp, ExpandOp, ExpOp, Function, LogOp, Matmul
                        NegOp, PowOp, ReluOp, ReshapeOp, SigmoidOp, SqrtOp, SubOp, SumOp, TanhOp, TOp, TransposeOp,
                        TrueDivOp, no_grad, totensor)
 from .tensor import Tensor, broadcast_shapes, promote_dtypes, sizeof
+from . import cuda  # noqa: E402  (nt.cuda.is_available(), nt.cuda.sync(), as in the reference)
 
 bool_ = Dtype.Bool
 int32 = Dtype.Int32
