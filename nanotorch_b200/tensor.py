@@ -522,10 +522,7 @@ def _fancy_plan(shape: Shape, residual: tuple, device: Device) -> _FancyPlan:
             arr = _host_index_array(sel, shape[dim], dim)
             host_arrays.append(arr)
             raw.append(Tensor.from_numpy(arr, device))
-    try:
-        ind_shape = broadcast_shapes(*(t.shape for t in raw))
-    except RuntimeError as e:
-        raise IndexError(str(e)) from e
+    ind_shape = broadcast_shapes(*(t.shape for t in raw))  # RuntimeError when they do not broadcast, as in the reference
     plan = _FancyPlan()
     plan.fancy_dims_in_src = fancy_dims
     plan.fancy_dims_data = [t.expand(*ind_shape) for t in raw]
