@@ -94,12 +94,14 @@ Tensor.transpose = lambda self, dim0, dim1: TransposeOp.apply(self, dim0, dim1)
 
 
 # ---- functional forms (src/nanotorch/ops.py)
-def add(x1, x2, out=None): return AddOp.apply(x1, _t(x2, x1), out=out)
-def subtract(x1, x2, out=None): return SubOp.apply(x1, _t(x2, x1), out=out)
-def multiply(x1, x2, out=None): return MulOp.apply(x1, _t(x2, x1), out=out)
-def divide(x1, x2, out=None): return TrueDivOp.apply(x1, _t(x2, x1), out=out)
-def matmul(x1, x2): return MatmulOp.apply(x1, x2)
-def negate(x): return NegOp.apply(x)
+# The reference's forms are the Python operators (`x + y`, src/nanotorch/ops.py:42-60), so a scalar may
+# stand on either side; `out=` is an addition that forwards to the op's in-place form.
+def add(x1, x2, out=None): return x1 + x2 if out is None else AddOp.apply(x1, _t(x2, x1), out=out)
+def subtract(x1, x2, out=None): return x1 - x2 if out is None else SubOp.apply(x1, _t(x2, x1), out=out)
+def multiply(x1, x2, out=None): return x1 * x2 if out is None else MulOp.apply(x1, _t(x2, x1), out=out)
+def divide(x1, x2, out=None): return x1 / x2 if out is None else TrueDivOp.apply(x1, _t(x2, x1), out=out)
+def matmul(x1, x2): return x1 @ x2
+def negate(x): return -x
 def exp(x): return ExpOp.apply(x)
 def log(x): return LogOp.apply(x)
 def sqrt(x): return SqrtOp.apply(x)

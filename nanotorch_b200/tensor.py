@@ -434,8 +434,9 @@ class Tensor:
         self._grad = None
 
     def enable_grad(self) -> None:
-        if self.dtype <= Dtype.Int64:
-            raise RuntimeError("Cannot enable grad on a non-float tensor.")
+        """Enables gradient tracking after construction.  Unlike the constructor this does not look at
+        the dtype, as in the reference (src/nanotorch/core.py:536-538; its tests call
+        ``arange(60, requires_grad=True)`` on an Int64 range)."""
         self._requires_grad = True
 
     def backward(self) -> None:

@@ -93,7 +93,10 @@ def test_autograd_bookkeeping_errors(nt):
         t.backward()  # not a scalar
     assert t.requires_grad and t.is_leaf and t.grad is None
     with pytest.raises(RuntimeError):
-        nt.Tensor([1, 2]).enable_grad()
+        nt.Tensor([1, 2], requires_grad=True)     # the constructor checks the dtype ...
+    i = nt.Tensor([1, 2])
+    i.enable_grad()                               # ... enable_grad does not (src/nanotorch/core.py:536-538)
+    assert i.requires_grad and nt.arange(4, requires_grad=True).requires_grad
     with pytest.raises(TypeError):
         nt.Tensor([1, 2]).to(nt.Device.Cuda if False else nt.int64).mean()  # mean of an integer tensor
 
