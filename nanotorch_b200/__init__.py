@@ -10,7 +10,7 @@ from ._C import Device, Dtype
 from .autograd import (ALL_OPS_, AddOp, ExpandOp, ExpOp, Function, LogOp, MatmulOp, MaxOp, MeanOp, MinOp, MulOp,
                        NegOp, PowOp, ReluOp, ReshapeOp, SigmoidOp, SqrtOp, SubOp, SumOp, TanhOp, TOp, TransposeOp,
                        TrueDivOp, no_grad, totensor)
-from .tensor import Tensor, broadcast_shapes, promote_dtypes, sizeof
+from .tensor import Tensor, TensorLike, broadcast_shapes, promote_dtypes, sizeof
 from . import cuda  # noqa: E402  (nt.cuda.is_available(), nt.cuda.sync(), as in the reference)
 
 bool_ = Dtype.Bool
@@ -146,8 +146,6 @@ def _arg_extremum(name, kernel, x, axis, keepdim):
 def argmin(x, axis=None, keepdim=False): return _arg_extremum("argmin", _C.argmin, x, axis, keepdim)
 def argmax(x, axis=None, keepdim=False): return _arg_extremum("argmax", _C.argmax, x, axis, keepdim)
 
-
-TensorLike = Tensor | bool | int | float
 
 
 # ---- factories (src/nanotorch/factories.py)

@@ -316,8 +316,6 @@ class Tensor:
     def _to_contiguous(self, force: bool = False) -> "Tensor":
         if not force and self._is_contiguous():
             return self
-        if self.device == Device.Cpu:
-            raise RuntimeError("clone_contiguous_view_from: requires Cuda (this library has no CPU compute path).")
         return Tensor._new_contiguous(_C.clone_contiguous_view_from(self._C_view), self._shape)
 
     def _alias(self) -> "Tensor":
@@ -456,6 +454,10 @@ class Tensor:
             run_backward(self)
 
     __hash__ = None  # elementwise __eq__
+
+
+# what the operators accept on either side (src/nanotorch/core.py: TensorLike)
+TensorLike = Tensor | float | int | bool | list
 
 
 # ---------------------------------------------------------------------------------------------
