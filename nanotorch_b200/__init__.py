@@ -148,6 +148,16 @@ def argmax(x, axis=None, keepdim=False): return _arg_extremum("argmax", _C.argma
 
 
 
+def compute_on_device(t: Tensor, fn):
+    """``fn(t)`` for a factory whose recipe is a few ops on a freshly generated tensor (randint, the
+    Kaiming initialisation).  There are no Cpu kernels in this library: a Cpu tensor is moved to the
+    device, the ops run there, and the result comes back -- same values as the reference computes on
+    the host, no host arithmetic.  Without a device the ops are issued where the tensor is."""
+    if t.device == Device.Cpu and _C.is_cuda_available():
+        return fn(t.to(Device.Cuda)).to(Device.Cpu)
+    return fn(t)
+
+
 # ---- factories (src/nanotorch/factories.py)
 def _shape_args(shape) -> tuple:
     if len(shape) == 1 and isinstance(shape[0], (tuple, list)):
@@ -215,7 +225,7 @@ def randint(low, high, shape=None, dtype=Dtype.Int64, requires_grad=False, devic
         raise ValueError("randint() cannot output bool values.")
     dims = () if shape is None else tuple(shape)
     base = _new(_C.uniform(math.prod(dims) if dims else 1, Dtype.Float32, std_device(device)), dims, False)
-    base = (base * (high - low) + low).to(Dtype.Int64).to(dtype)
+    base = compute_on_device(base, lambda t: (t * (high - low) + low).to(Dtype.Int64).to(dtype))
     if requires_grad:
         base.enable_grad()
     return base

@@ -11,7 +11,7 @@ from __future__ import annotations
 import math
 from typing import Any, Sequence
 
-from . import _C, rand, zeros
+from . import _C, compute_on_device, rand, zeros
 from .autograd import LinearOp, ReluOp, TanhOp, no_grad
 from .tensor import Tensor
 from ._C import Device, Dtype
@@ -37,7 +37,7 @@ def _kaiming_W(fan_in: int, fan_out: int, device) -> Tensor:
     if fan_in <= 0 or fan_out <= 0:
         raise ValueError(f"Cannot initialize Linear with {fan_in=}, {fan_out=} (non-positive).")
     z = math.sqrt(6 / fan_in)
-    return 2 * rand(fan_in, fan_out, device=device) * z - z
+    return compute_on_device(rand(fan_in, fan_out, device=device), lambda u: 2 * u * z - z)
 
 
 class Linear(Module):
