@@ -40,6 +40,11 @@ class Dtype(enum.IntEnum):
     def __str__(self) -> str:
         return f"Dtype.{self.name}"
 
+    def __bool__(self) -> bool:
+        # a pybind11 enum value is always truthy; the reference's Python layer relies on it
+        # (`auto_dtype or Dtype.Float32`, src/nanotorch/core.py:620), and Bool has the value 0
+        return True
+
 
 class Device(enum.Enum):
     """Data storage devices (src/cpp/allocator.h:10)."""

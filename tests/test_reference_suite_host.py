@@ -16,6 +16,8 @@ only.  Two runs:
    tooling is loaded from the checkout and each op's declared input specification is attached to this
    package's class of the same name; only the 100-fold repetition marked slow there is left out).
 
+3. The other way round: the reference's own Python package on this library's ``_C`` shim.
+
 Skipped without a checkout."""
 
 import os
@@ -109,6 +111,41 @@ def test_on_the_reference_cpu_backend_everything_passes(tmp_path):
     passed, failed = _run(tmp_path, SWAP_BACKEND, OP_FILES + ["tests/test_autograd.py"], extra=("-k", "not test_ops_specs_extensive"))
     assert not failed, "\n".join(f"{name}: {text[:300]}" for name, text in failed[:20])
     assert passed >= 1230, passed
+
+
+def test_the_references_python_layer_runs_on_this_librarys_shim(tmp_path):
+    """The other direction (option B): the reference's OWN Python package, its files
+    linked in place, with ``nanotorch/_C.py`` forwarding to ``nanotorch_b200._C`` instead of the pybind11
+    module.  Its tests build Cpu tensors, so whatever reaches a kernel fails with "requires Cuda"; nothing
+    else may fail -- Dtype/Device enum behaviour, Storage's buffer protocol, from_iterable, TensorView,
+    the factories and the error classes are what the reference's Python layer expects of ``_C``."""
+    pytest.importorskip("torch")
+    src = REFERENCE / "src" / "nanotorch"
+    pkg = tmp_path / "refpy" / "nanotorch"
+    for path in src.rglob("*.py"):
+        dst = pkg / path.relative_to(src)
+        dst.parent.mkdir(parents=True, exist_ok=True)
+        os.symlink(path, dst)
+    (pkg / "_C.py").write_text("from nanotorch_b200._C import *  # noqa: F401,F403\n"
+                               "from nanotorch_b200._C import Device, Dtype, Storage, TensorView  # noqa: F401\n")
+    report = tmp_path / "report.xml"
+    env = dict(os.environ, PYTHONPATH=f"{tmp_path / 'refpy'}{os.pathsep}{REPO}")
+    files = OP_FILES + ["tests/test_autograd.py"]
+    proc = subprocess.run([sys.executable, "-m", "pytest", "-q", "-p", "no:cacheprovider", f"--junitxml={report}",
+                           *[str(REFERENCE / f) for f in files]], cwd=tmp_path, env=env, capture_output=True, text=True)
+    assert report.exists(), proc.stdout[-2000:] + proc.stderr[-2000:]
+    passed, other = 0, []
+    for case in ET.parse(report).getroot().iter("testcase"):
+        if case.find("skipped") is not None:
+            continue
+        problems = list(case.findall("failure")) + list(case.findall("error"))
+        text = " ".join((p.get("message") or "") + (p.text or "") for p in problems)
+        if not problems:
+            passed += 1
+        elif "requires Cuda" not in text:
+            other.append(f"{case.get('classname')}::{case.get('name')}: {text[:300]}")
+    assert not other, "\n".join(other[:20])
+    assert passed >= 400, passed
 
 
 GOLDEN_RUN = r'''
