@@ -224,6 +224,24 @@ class Tensor:
         return self._shape[0] if self._shape else 0
 
     def __repr__(self) -> str:
+        """The reference's format (src/nanotorch/core.py:141-164): values for 0-d, 1-D (first and last three
+        beyond 7 elements) and 2-D tensors (first and last two rows beyond 5), a summary line otherwise.
+        Only the printed elements are copied from the device, not the whole tensor as the reference does."""
+        def compact(row: "Tensor") -> str:
+            n = row.shape[0]
+            if n < 8:
+                return str(row.cpu().tolist())
+            head, tail = row[:3].cpu().tolist(), row[n - 3:].cpu().tolist()
+            return "[" + ", ".join(str(v) for v in head) + ", ..., " + ", ".join(str(v) for v in tail) + "]"
+
+        if self.ndim == 0:
+            return f"nt.Tensor({self.cpu().tolist()})"
+        if self.ndim == 1:
+            return f"nt.Tensor({compact(self)})"
+        if self.ndim == 2:
+            rows = list(range(len(self))) if len(self) <= 5 else [0, 1, None, -2, -1]
+            lines = ["..." if i is None else compact(self[i]) for i in rows]
+            return "nt.Tensor(" + ("\n" + " " * 10).join(lines) + ")"
         return f"nt.Tensor(shape={self.shape}, {self.numel} x <{self.dtype.name}>, d: {self.device.name})"
 
     @property

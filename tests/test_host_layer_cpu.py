@@ -146,3 +146,16 @@ def test_factories_and_functional_names_of_the_reference(nt):
     assert nt.argmax(nt.zeros(0, 3), axis=1).shape == (0,)
     for name in ("eq", "gt", "geq", "lt", "leq", "argmax", "argmin", "randint", "TensorLike"):
         assert hasattr(nt, name)
+
+
+def test_repr_has_the_references_format(nt):
+    """src/nanotorch/core.py:141-164 -- checked against the reference's own output when this was written."""
+    assert repr(nt.Tensor(3.5)) == "nt.Tensor(3.5)"
+    assert repr(nt.Tensor(list(range(7)))) == "nt.Tensor([0, 1, 2, 3, 4, 5, 6])"
+    assert repr(nt.Tensor(list(range(20)))) == "nt.Tensor([0, 1, 2, ..., 17, 18, 19])"
+    assert repr(nt.Tensor([[1.0, 2.0], [3.0, 4.0]])) == "nt.Tensor([1.0, 2.0]\n          [3.0, 4.0])"
+    six = nt.Tensor([[10 * r + c for c in range(10)] for r in range(6)])
+    assert repr(six) == ("nt.Tensor([0, 1, 2, ..., 7, 8, 9]\n          [10, 11, 12, ..., 17, 18, 19]\n          ...\n"
+                         "          [40, 41, 42, ..., 47, 48, 49]\n          [50, 51, 52, ..., 57, 58, 59])")
+    assert repr(nt.zeros(2, 2, 2)) == "nt.Tensor(shape=(2, 2, 2), 8 x <Float32>, d: Cpu)"
+    assert repr(six.T[1:3]) == "nt.Tensor([1, 11, 21, 31, 41, 51]\n          [2, 12, 22, 32, 42, 52])"   # through a view
