@@ -499,6 +499,71 @@ def reference_cuda_column() -> dict:
     return out
 
 
+def reference_cpu_column(limit_s: float = 90.0) -> dict:
+    """Optional comparison column (--ref-cpu): the reference's own CPU kernels (oracle/_ref) on the per-op
+    configurations, single thread as the reference runs them, operands already in its storages, best of 2
+    after a warm-up, perf_counter around the native call.  Elementwise and reductions at full size; each
+    matmul on a bounded sample of its rows (the full 4096^3 product takes minutes).  Needs no GPU."""
+    from oracle import oracle as O
+
+    if not O.ref_available():
+        return {"unavailable": "oracle/_ref is not built"}
+    o = O.RefOracle()
+    m = o.m
+    r = np.random.default_rng
+    t_start = time.perf_counter()
+
+    def best(fn, reps=2):
+        fn()
+        ts = []
+        for _ in range(reps):
+            t = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t)
+        return min(ts) * 1e3
+
+    def view(array):
+        return o._tv(np.ascontiguousarray(array, dtype=np.float32))  # (TensorView, storage kept alive)
+
+    out: dict = {}
+    N = 4096
+    (va, sa), (vb, sb) = view(r(10).uniform(-1, 1, (N, N))), view(r(11).uniform(-1, 1, (N, N)))
+    (vn, sn), (vp, sp_) = view(r(14).standard_normal((N, N))), view(r(15).uniform(0.1, 10, (N, N)))
+    _, sv = view(r(13).uniform(-1, 1, (N,)))
+    v_row = m.TensorView(sv, [N, N], [0, 1], 0)       # row broadcast: stride 0
+    vb_t = m.TensorView(sb, [N, N], [1, N], 0)        # transposed view
+    ew = [("add.contiguous", lambda: m.add(va, vb), 3), ("truediv.contiguous", lambda: m.divide(va, vp), 3),
+          ("add.broadcast_row", lambda: m.add(va, v_row), 2), ("add.transposed", lambda: m.add(va, vb_t), 3),
+          ("exp.forward", lambda: m.exp(vn), 2), ("tanh.forward", lambda: m.tanh(vn), 2),
+          ("sigmoid.forward", lambda: m.sigmoid(vn), 2), ("relu.forward", lambda: m.relu(vn), 2),
+          ("log.forward", lambda: m.log(vp), 2), ("pow2.forward", lambda: m.pow(va, 2.0), 2)]
+    for name, fn, streams in ew:
+        if time.perf_counter() - t_start > limit_s:
+            break
+        ms = best(fn)
+        out[name] = {"ms": round(ms, 2), "GB/s": round(streams * N * N * 4 / ms / 1e6, 2)}
+    M = 8192
+    vx, sx = view(r(20).standard_normal((M, M)))
+    F32 = o.F32
+    for name, fn in (("sum.dim0", lambda: m.sum(vx, [0], F32)), ("sum.dim1", lambda: m.sum(vx, [1], F32)),
+                     ("sum.full", lambda: m.sum(vx, [0, 1], F32)), ("max.dim1", lambda: m.max(vx, [1]))):
+        if time.perf_counter() - t_start > limit_s:
+            break
+        ms = best(fn, reps=1)
+        out[name] = {"ms": round(ms, 2), "GB/s": round(M * M * 4 / ms / 1e6, 2)}
+    rows = 64  # of the left operand's rows
+    for label, (m_, k_, n_) in {"4096x4096x4096": (4096, 4096, 4096), "8192x1024x4096": (8192, 1024, 4096)}.items():
+        if time.perf_counter() - t_start > limit_s:
+            break
+        (vA, sA), (vB, sB) = view(r(30).uniform(-1, 1, (rows, k_))), view(r(31).uniform(-1, 1, (k_, n_)))
+        ms = best(lambda: m.matmul(vA, vB), reps=1)
+        out[f"matmul.{label}.forward"] = {"sample": f"{rows} of {m_} rows", "ms_sample": round(ms, 1),
+                                          "GFLOP/s": round(2.0 * rows * k_ * n_ / ms / 1e6, 2)}
+    out["_notes"] = (f"the reference's CPU kernels, 1 thread of {os.cpu_count()} (it has no threading), perf_counter "
+                     "around the native call, best of 2 after a warm-up; bytes as in the GPU sweep; matmul on a row sample")
+    return out
+
+
 def product_arm(args, rank: int, local_rank: int, world: int) -> None:
     import nanotorch_b200 as nt
     import nanotorch_b200.nn as nn
@@ -778,10 +843,15 @@ def main() -> None:
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op sweep and the CPU baseline sample")
     ap.add_argument("--ref-cuda", action="store_true",
                     help="also time the reference's own CUDA kernels (oracle/_ref) on this GPU for a comparison column")
+    ap.add_argument("--ref-cpu", action="store_true",
+                    help="time the reference's CPU kernels on the per-op configurations (needs no GPU), print JSON, exit")
     ap.add_argument("--case", default=None, help=f"run one small case for a profiler capture and exit: {PROFILE_CASES}")
     args = ap.parse_args()
     if args.case:
         profile_case(args.case)
+        return
+    if args.ref_cpu:
+        print(json.dumps({"impl": "reference", "ops_cpu": reference_cpu_column()}), flush=True)
         return
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
     rank = int(os.environ.get("RANK", "0"))
