@@ -200,7 +200,7 @@ def build_model(nt, nn):
     nt.manual_seed(0)
     layers = []
     for i in range(LAYERS):
-        layers.append(nn.Linear(WIDTH, WIDTH))
+        layers.append(nn.Linear(WIDTH, WIDTH, device="cuda"))
         if i < LAYERS - 1:
             layers.append(nn.Tanh())
     return nn.Sequential(*layers)

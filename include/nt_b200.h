@@ -76,6 +76,18 @@ void *nt_stream(void);                /* the cudaStream_t every kernel is launch
 int nt_launch_count(uint64_t *out);   /* kernels launched by this library since load (bench evidence) */
 int nt_allocator_stats(uint64_t *bytes_reserved, uint64_t *bytes_in_use, uint64_t *n_cuda_malloc);
 int nt_allocator_trim(void);          /* return cached blocks to the driver */
+int nt_allocator_requests(uint64_t *out); /* requests made to the device arena since load, cache hits included */
+
+/* Every spin in device code (the mbarrier waits of the tensor-core GEMM pipeline) is bounded: past the
+ * limit the kernel records which role gave up, stops issuing, and returns; the next synchronising call
+ * (nt_cuda_sync, a download, to(Cpu)) reports it as NT_ERR_RUNTIME and clears it, and the context stays
+ * usable.  No counterpart in the reference, whose kernels never wait on one another.  The limit is in SM
+ * clocks, default 2^31 (about a second).  nt_wait_probe launches a one-thread kernel that waits, with
+ * that same helper and limit, on a barrier nothing arrives on: the way to exercise the time-out path
+ * without faulting or hanging anything. */
+int nt_set_wait_limit_clocks(int64_t clocks);
+int64_t nt_get_wait_limit_clocks(void);
+int nt_wait_probe(void);
 
 /* Timing on the library stream (no counterpart in the reference, which times with perf_counter
  * around a device sync, scripts/profile_ops.py:61-89). */
@@ -271,9 +283,27 @@ int nt_sgd_update(const nt_view *param, const nt_view *grad, float lr, float gra
 /* ------------------------------------------------------------------ data-parallel exchange (NCCL; no counterpart in the reference) */
 #define NT_COMM_ID_BYTES 128
 int nt_comm_unique_id(uint8_t id[NT_COMM_ID_BYTES]);
+/* The rendezvous waits for every rank; it is bounded: NT_ERR_RUNTIME after NT_COMM_TIMEOUT_MS (default
+ * 300 000) or the explicit limit, instead of hanging on a rank that never joins.  NT_NCCL_MAX_CTAS in the
+ * environment caps the CTAs NCCL may use per collective (they share the SMs with the backward GEMMs). */
 int nt_comm_init(int rank, int world, const uint8_t id[NT_COMM_ID_BYTES]);
+int nt_comm_init_timeout(int rank, int world, const uint8_t id[NT_COMM_ID_BYTES], int64_t timeout_ms);
+/* A bucket: nt_comm_group_begin orders the communication stream after everything enqueued on the compute
+ * stream so far; the all-reduces issued until nt_comm_group_end leave as one NCCL launch.  Works without
+ * a communicator too (one rank): it then only orders the side stream. */
+int nt_comm_group_begin(void);
+int nt_comm_group_end(void);
 int nt_comm_allreduce_sum(nt_storage *s);       /* in place, fp32, on the communication stream; ordered after prior work */
-int nt_comm_wait(void);                         /* make the compute stream wait for outstanding collectives */
+/* nt_sgd_update enqueued on the communication stream, behind the collectives issued so far: the update of
+ * one layer overlaps the backward kernels of the layers below it.  The caller vouches that no kernel still
+ * to be enqueued on the compute stream before the next nt_comm_wait reads the parameter. */
+int nt_comm_sgd_update(const nt_view *param, const nt_view *grad, float lr, float grad_scale);
+int nt_comm_wait(void);                         /* make the compute stream wait for the communication stream (device-side join) */
+/* Host-side wait for the communication stream with a time limit.  Past it the communicator is aborted
+ * (ncclCommAbort takes the stuck collective kernels down, so the stream drains) and NT_ERR_RUNTIME is
+ * returned: a peer that died between steps shows up here instead of as a hang. */
+int nt_comm_sync(int64_t timeout_ms);
+int nt_comm_abort(void);
 int nt_comm_destroy(void);
 
 #ifdef __cplusplus

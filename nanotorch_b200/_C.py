@@ -538,6 +538,30 @@ def allocator_trim() -> None:
     _check(_lib.nt_allocator_trim())
 
 
+def allocator_requests() -> int:
+    """Requests made to the device arena since load (served from its cache or by cudaMalloc)."""
+    n = C.c_uint64(0)
+    _check(_lib.nt_allocator_requests(C.byref(n)))
+    return n.value
+
+
+_lib.nt_get_wait_limit_clocks.restype = C.c_int64
+
+
+def set_wait_limit_clocks(clocks: int) -> None:
+    """Limit, in SM clocks, of every bounded spin in device code (default 2**31)."""
+    _check(_lib.nt_set_wait_limit_clocks(C.c_int64(int(clocks))))
+
+
+def get_wait_limit_clocks() -> int:
+    return _lib.nt_get_wait_limit_clocks()
+
+
+def wait_probe() -> None:
+    """Launch the one-thread kernel that waits (bounded) on a barrier nothing arrives on."""
+    _check(_lib.nt_wait_probe())
+
+
 TANH_CORRECTLY_ROUNDED = 0
 TANH_BIT_EXACT_LIBM = 1
 
@@ -626,6 +650,38 @@ def comm_init(rank: int, world: int, unique_id: bytes) -> None:
         raise ValueError("comm_init: unique id must be 128 bytes")
     buf = (C.c_uint8 * COMM_ID_BYTES).from_buffer_copy(unique_id)
     _check(_lib.nt_comm_init(int(rank), int(world), buf))
+
+
+def comm_init_timeout(rank: int, world: int, unique_id: bytes, timeout_ms: int) -> None:
+    """comm_init with an explicit limit on the rendezvous: RuntimeError if a rank has not joined in time."""
+    if len(unique_id) != COMM_ID_BYTES:
+        raise ValueError("comm_init: unique id must be 128 bytes")
+    buf = (C.c_uint8 * COMM_ID_BYTES).from_buffer_copy(unique_id)
+    _check(_lib.nt_comm_init_timeout(int(rank), int(world), buf, C.c_int64(int(timeout_ms))))
+
+
+def comm_group_begin() -> None:
+    """Open a bucket: orders the communication stream after the compute stream; the all-reduces issued
+    until comm_group_end go out as one NCCL launch."""
+    _check(_lib.nt_comm_group_begin())
+
+
+def comm_group_end() -> None:
+    _check(_lib.nt_comm_group_end())
+
+
+def comm_sgd_update(param: "TensorView", grad: "TensorView", lr: float, grad_scale: float = 1.0) -> None:
+    """sgd_update enqueued on the communication stream, behind the collectives issued so far."""
+    _check(_lib.nt_comm_sgd_update(_vref(param), _vref(grad), C.c_float(lr), C.c_float(grad_scale)))
+
+
+def comm_sync(timeout_ms: int) -> None:
+    """Host-side wait for the communication stream with a time limit; aborts the communicator past it."""
+    _check(_lib.nt_comm_sync(C.c_int64(int(timeout_ms))))
+
+
+def comm_abort() -> None:
+    _check(_lib.nt_comm_abort())
 
 
 def comm_allreduce_sum(s: Storage) -> None:

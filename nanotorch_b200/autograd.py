@@ -293,9 +293,9 @@ class MatmulOp(Function):
         if _need(self, 0):
             g1 = unbroadcast(g @ b.transpose(-2, -1), x1.shape).reshape(*x1.shape)
         if _need(self, 1):
-            # unbroadcast against the 2-D form of a 1-D right operand, then hand the gradient back in
-            # the operand's own shape (the reference returns it as (k, 1); the values are the same)
-            g2 = unbroadcast(a.transpose(-2, -1) @ g, b_orig.shape).reshape(*x2.shape)
+            # a 1-D right operand was rebound to its (k, 1) form above, and its gradient keeps that shape,
+            # exactly as the reference returns it (autograd/ops_binary.py:253-267)
+            g2 = unbroadcast(a.transpose(-2, -1) @ g, b_orig.shape).reshape(*b_orig.shape)
         return g1, g2
 
     @classmethod
@@ -645,8 +645,10 @@ ALL_OPS_ = [AddOp, ExpOp, ExpandOp, LogOp, MatmulOp, MeanOp, MulOp, NegOp, PowOp
 
 # =============================================================================================
 # backward pass
-# id(leaf tensor) -> callable(leaf): called right after the leaf's gradient has been written (used by
-# the data-parallel trainer to start that parameter's all-reduce while backward continues).
+# id(leaf tensor) -> callable(leaf): called ONCE per backward pass, right after the last contribution to
+# that leaf's gradient has been added (a leaf used several times in the graph gets one call, with the
+# summed gradient).  The data-parallel trainer starts the parameter's all-reduce from it while the
+# rest of backward continues.
 leaf_grad_hooks: dict[int, Any] = {}
 
 
@@ -672,6 +674,13 @@ def run_backward(root: Tensor) -> None:
         for inp in node.grad_fn.inputs:
             if isinstance(inp, Tensor) and inp.requires_grad and inp.grad_fn is not None and id(inp) not in seen:
                 stack.append((inp, False))
+    # contributions each hooked leaf is still to receive in this pass
+    pending: dict[int, int] = {}
+    if leaf_grad_hooks:
+        for node in order:
+            for a in node.grad_fn.inputs:
+                if isinstance(a, Tensor) and a.requires_grad and a.grad_fn is None and id(a) in leaf_grad_hooks:
+                    pending[id(a)] = pending.get(id(a), 0) + 1
     with no_grad():  # gradients are values, not graph nodes
         for node in reversed(order):
             fn = node.grad_fn
@@ -680,11 +689,13 @@ def run_backward(root: Tensor) -> None:
             tensor_inputs = [a for a in fn.inputs if isinstance(a, Tensor)]
             grads = fn.backward(node._grad)
             for x, gx in zip(tensor_inputs, grads):
-                if gx is None or not x.requires_grad:
+                if not x.requires_grad:
                     continue
-                x._grad = gx if x._grad is None else x._grad + gx
-                if x.grad_fn is None and leaf_grad_hooks:
-                    hook = leaf_grad_hooks.get(id(x))
-                    if hook is not None:
-                        hook(x)
+                if gx is not None:
+                    x._grad = gx if x._grad is None else x._grad + gx
+                left = pending.get(id(x))
+                if left is not None and x.grad_fn is None:
+                    pending[id(x)] = left - 1
+                    if left == 1 and x._grad is not None:
+                        leaf_grad_hooks[id(x)](x)
             node._grad = None

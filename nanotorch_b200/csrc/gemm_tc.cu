@@ -59,11 +59,22 @@ struct SplitArgs {
   int mode;              // 0 generic, 1 unit stride along k (128-bit), 2 unit stride along r (128-bit + transpose)
 };
 
+// hi = tf32(x), except that a finite x whose rounding would overflow to infinity keeps the largest
+// finite TF32 value (the remainder then fits in lo); lo = tf32(x - hi), or 0 when x is not finite
+// (inf - inf would turn an infinity into a NaN before any product is formed).
+__device__ __forceinline__ float split_hi(float x) {
+  float h = tf32_round(x);
+  if (isinf(h) && !isinf(x)) h = copysignf(__uint_as_float(0x7F7FE000u), x);
+  return h;
+}
+__device__ __forceinline__ float split_lo(float x, float h) {
+  return (__float_as_uint(h) & 0x7F800000u) == 0x7F800000u ? 0.0f : tf32_round(x - h);
+}
 __device__ __forceinline__ void split_store4(const SplitArgs &a, int64_t idx, float x0, float x1, float x2, float x3) {
-  const float h0 = tf32_round(x0), h1 = tf32_round(x1), h2 = tf32_round(x2), h3 = tf32_round(x3);
+  const float h0 = split_hi(x0), h1 = split_hi(x1), h2 = split_hi(x2), h3 = split_hi(x3);
   __stcs(reinterpret_cast<float4 *>(a.hi + idx), make_float4(h0, h1, h2, h3));
   __stcs(reinterpret_cast<float4 *>(a.lo + idx),
-         make_float4(tf32_round(x0 - h0), tf32_round(x1 - h1), tf32_round(x2 - h2), tf32_round(x3 - h3)));
+         make_float4(split_lo(x0, h0), split_lo(x1, h1), split_lo(x2, h2), split_lo(x3, h3)));
 }
 
 // One CTA converts a 64 (r) x 64 (k) tile.  Kp is a multiple of 32, so every 4-group of k inside Kp is
@@ -152,12 +163,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
                : "memory");
   return ok != 0;
 }
-// Bounded wait: returns false when the barrier did not flip within ~2^31 clocks.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait: returns false when the barrier did not flip within `limit` SM clocks (2^31 unless the
+// host lowered it with nt_set_wait_limit_clocks).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > (1LL << 31)) return false;
+    if (clock64() - t0 > limit) return false;
   }
   return true;
 }
@@ -206,6 +218,7 @@ struct TcArgs {
   const float *bias;    // promoted kernel only: C[m][n] = fl(fl(sum) + bias[n * bias_stride]) when non-null
   int64_t bias_stride;
   int *error_flag;
+  long long wait_limit; // SM clocks a pipeline wait may take before the kernel gives up
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -216,6 +229,7 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   // barriers: full[s] at bar_base + 8 s, empty[s] at + 32 + 8 s, accumulator-ready at + 64; tmem slot at + 72
   const uint32_t full0 = bar_base, empty0 = bar_base + 32, acc_bar = bar_base + 64;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + (bar_base - smem_u32(smem_raw)) + 72);
+  volatile int *poison_slot = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN, b = blockIdx.z;
@@ -227,6 +241,9 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
     mbar_init(acc_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // a wait already ran out in this launch (or an earlier one since the last synchronisation): the
+    // whole CTA agrees to do nothing instead of spending another wait limit per role
+    *poison_slot = *reinterpret_cast<volatile int *>(g.error_flag);
   }
   if (warp == 1) { // one warp allocates the accumulator columns
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
@@ -236,14 +253,15 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
+  const bool poisoned = *poison_slot != 0;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && !poisoned) {
       uint32_t phase = 0;
       int s = 0;
       for (int kb = 0; kb < g.num_kb; ++kb) {
-        if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) {
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1, g.wait_limit)) {
           atomicExch(g.error_flag, 1);
           break;
         }
@@ -262,12 +280,12 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && !poisoned) {
       uint32_t phase = 0;
       int s = 0;
       bool ok = true;
       for (int kb = 0; kb < g.num_kb; ++kb) {
-        if (!mbar_wait(full0 + 8 * s, phase)) {
+        if (!mbar_wait(full0 + 8 * s, phase, g.wait_limit)) {
           atomicExch(g.error_flag, 2);
           ok = false;
           break;
@@ -300,14 +318,14 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   } else {
     // ------------------------------------------------------------------ epilogue, warps 2..5
     const int quad = warp & 3; // the 32-lane group of tensor memory this warp may read
-    bool ok = mbar_wait(acc_bar, 0);
-    if (!ok) atomicExch(g.error_flag, 3);
+    bool ok = !poisoned && mbar_wait(acc_bar, 0, g.wait_limit);
+    if (!ok && !poisoned) atomicExch(g.error_flag, 3);
     ok = ok && (*reinterpret_cast<volatile int *>(g.error_flag) == 0);
     tcgen05_fence_after();
     const int64_t m = int64_t(m0) + quad * 32 + lane;
     float *crow = g.C + (int64_t(b) * g.M + m) * g.N;
 #pragma unroll 1
-    for (int c = 0; c < TC_BN; c += 32) {
+    for (int c = 0; c < (poisoned ? 0 : TC_BN); c += 32) {
       uint32_t v[32], w[32];
       const uint32_t taddr = tmem_acc + (uint32_t(quad * 32) << 16) + uint32_t(c);
       asm volatile(
@@ -354,7 +372,7 @@ gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 
   // If anything timed out, give copies that are still in flight time to land before the shared
   // memory of this CTA is handed to another one.
-  if (*reinterpret_cast<volatile int *>(g.error_flag) != 0) {
+  if (!poisoned && *reinterpret_cast<volatile int *>(g.error_flag) != 0) {
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000) {
     }
@@ -400,6 +418,7 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   // full[s] at +8 s, empty[s] at +32 + 8 s, acc_full[b] at +64 + 8 b, acc_empty[b] at +80 + 8 b, tmem slot at +96
   const uint32_t full0 = bar_base, empty0 = bar_base + 32, acc_full0 = bar_base + 64, acc_empty0 = bar_base + 80;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem_raw + (bar_base - smem_u32(smem_raw)) + 96);
+  volatile int *poison_slot = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN, b = blockIdx.z;
@@ -415,6 +434,7 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       mbar_init(acc_empty0 + 8 * i, 8); // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    *poison_slot = *reinterpret_cast<volatile int *>(g.error_flag); // see gemm_3xtf32_kernel
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
@@ -424,13 +444,14 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   __syncthreads();
   tcgen05_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
+  const bool poisoned = *poison_slot != 0;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && !poisoned) {
       uint32_t phase = 0;
       int s = 0;
       for (int kb = 0; kb < g.num_kb; ++kb) {
-        if (!mbar_wait(empty0 + 8 * s, phase ^ 1)) {
+        if (!mbar_wait(empty0 + 8 * s, phase ^ 1, g.wait_limit)) {
           atomicExch(g.error_flag, 1);
           break;
         }
@@ -448,14 +469,14 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && !poisoned) {
       uint32_t phase = 0;
       int s = 0, kb = 0;
       bool ok = true;
       for (int p = 0; p < num_periods && ok; ++p) {
         const int buf = p & 1;
         // the epilogue must have drained this half (two periods ago) before it is overwritten
-        if (!mbar_wait(acc_empty0 + 8 * buf, ((p >> 1) & 1) ^ 1)) {
+        if (!mbar_wait(acc_empty0 + 8 * buf, ((p >> 1) & 1) ^ 1, g.wait_limit)) {
           atomicExch(g.error_flag, 4);
           ok = false;
           break;
@@ -465,7 +486,7 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         const int kb_end = min(kb + TC_PERIOD_KB, g.num_kb);
         bool first = true;
         for (; kb < kb_end; ++kb) {
-          if (!mbar_wait(full0 + 8 * s, phase)) {
+          if (!mbar_wait(full0 + 8 * s, phase, g.wait_limit)) {
             atomicExch(g.error_flag, 2);
             ok = false;
             break;
@@ -505,10 +526,10 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     float sum[128];
 #pragma unroll
     for (int i = 0; i < 128; ++i) sum[i] = 0.0f;
-    bool ok = true;
-    for (int p = 0; p < num_periods; ++p) {
+    bool ok = !poisoned;
+    for (int p = 0; p < (poisoned ? 0 : num_periods); ++p) {
       const int buf = p & 1;
-      if (ok && !mbar_wait(acc_full0 + 8 * buf, (p >> 1) & 1)) {
+      if (ok && !mbar_wait(acc_full0 + 8 * buf, (p >> 1) & 1, g.wait_limit)) {
         atomicExch(g.error_flag, 3);
         ok = false;
       }
@@ -555,7 +576,7 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
   }
 
-  if (*reinterpret_cast<volatile int *>(g.error_flag) != 0) {
+  if (!poisoned && *reinterpret_cast<volatile int *>(g.error_flag) != 0) {
     const long long t0 = clock64();
     while (clock64() - t0 < 2000000) {
     }
@@ -604,6 +625,8 @@ static int *g_error_flag = nullptr;
 static int *error_flag_ptr() {
   int *&flag = g_error_flag;
   if (!flag) {
+    if (is_capturing())
+      fail_runtime("gemm_3xtf32: first use inside a graph capture; run the step once eagerly before capturing it.");
     size_t rounded;
     flag = static_cast<int *>(device_alloc(sizeof(int), &rounded));
     NT_CUDA_CHECK(cudaMemsetAsync(flag, 0, sizeof(int), stream()));
@@ -643,6 +666,35 @@ static void launch_split(const float *src, float *planes, int64_t batch, int64_t
   check_launch("split_pack");
 }
 
+void gemm_tc_prepare() {
+  static bool configured = false;
+  if (!configured) {
+    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(TC_SMEM_BYTES)));
+    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_promoted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(TC_SMEM_BYTES)));
+    configured = true;
+  }
+  error_flag_ptr();
+}
+
+// One CTA, one thread: the same bounded wait the GEMM pipeline uses, on a barrier that nothing ever
+// arrives on.  It must give up after the configured limit, record code 5 and return -- the test of the
+// time-out path that needs no fault: the context stays usable and the flag is read at the next
+// synchronisation like any pipeline time-out.
+__global__ void wait_probe_kernel(int *error_flag, long long limit) {
+  __shared__ __align__(8) uint64_t bar;
+  const uint32_t b = smem_u32(&bar);
+  mbar_init(b, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  if (!mbar_wait(b, 0, limit)) atomicExch(error_flag, 5);
+}
+
+void gemm_tc_wait_probe() {
+  int *flag = error_flag_ptr();
+  wait_probe_kernel<<<1, 1, 0, stream()>>>(flag, wait_limit_clocks());
+  check_launch("wait_probe_kernel");
+}
+
 static std::atomic<int> g_promoted{1};
 void gemm_tc_set_promoted(bool on) { g_promoted.store(on ? 1 : 0); }
 
@@ -656,13 +708,7 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
   if (batch < 1 || batch > 32767 || M < 1 || N < 1 || K < 1) return false;
   if (ceil_div(M, TC_BM) > 65535 || ceil_div(N, TC_BN) > 0x7fffffff) return false;
   if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) return false;
-  static bool configured = false;
-  if (!configured) {
-    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(TC_SMEM_BYTES)));
-    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_promoted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       int(TC_SMEM_BYTES)));
-    configured = true;
-  }
+  gemm_tc_prepare();
   const int64_t Kp = ceil_div(K, 32) * 32;
   size_t ra = 0, rb = 0;
   float *pa = static_cast<float *>(device_alloc(size_t(2 * batch * M * Kp) * 4, &ra));
@@ -680,6 +726,7 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
     g.batch = int32_t(batch);
     g.c_vec = (N % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
     g.error_flag = error_flag_ptr();
+    g.wait_limit = wait_limit_clocks();
     g.bias = nullptr;
     g.bias_stride = 0;
     if (bias && g_promoted.load()) {

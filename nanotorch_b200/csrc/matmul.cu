@@ -305,6 +305,12 @@ int nt_set_matmul_mode(int mode) {
 }
 int nt_get_matmul_mode(void) { return g_matmul_mode.load(); }
 
+int nt_wait_probe(void) {
+  NT_API_BEGIN
+  gemm_tc_wait_probe();
+  NT_API_END
+}
+
 // x1 @ x2, plus -- when `bias` is given (fp32, N values) -- the broadcast add of the bias as a second
 // rounded step: in the tensor-core kernel's epilogue where that kernel runs, by an in-place add launch
 // otherwise.  Either way the bits are those of matmul followed by add.

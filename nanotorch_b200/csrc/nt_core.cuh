@@ -97,13 +97,33 @@ template <class F> auto dispatch_float(int dt, F &&f) {
 // ------------------------------------------------------------------------------------------
 // Runtime singletons
 cudaStream_t stream();       // the one compute stream (non-blocking)
-cudaStream_t comm_stream();  // collectives
+cudaStream_t comm_stream();  // collectives, and the parameter updates that follow them
+cudaStream_t compute_stream(); // the compute stream itself, whatever redirection is active
+// While one of these lives, stream() returns `to`: kernels launched by the ordinary entry points go to
+// that stream instead (used to run a parameter update on the communication stream, right behind the
+// collective that produced its gradient).  Single-threaded use, like the rest of the library.
+struct StreamRedirect {
+  cudaStream_t prev;
+  explicit StreamRedirect(cudaStream_t to);
+  ~StreamRedirect();
+  StreamRedirect(const StreamRedirect &) = delete;
+  StreamRedirect &operator=(const StreamRedirect &) = delete;
+};
 void count_launch(uint64_t n = 1);
 // matmul kernels call these around their launches (no-ops unless profiling is enabled)
 void matmul_profile_begin();
 void matmul_profile_end();
 bool cuda_ok();              // a device is present and usable
 int gemm_tc_take_error();    // device-side error flag of the tensor-core GEMM (0 = none); call after a sync
+void check_device_errors();  // after a stream synchronisation: raises if a bounded device-side wait ran out
+long long wait_limit_clocks(); // limit of every bounded spin in device code, in SM clocks
+bool is_capturing();         // a CUDA-graph capture is in progress on the compute stream
+// Persistent device state that kernels expect to find zeroed (ticket counters of the reductions, the
+// error flag of the tensor-core GEMM) and one-off function attributes: created eagerly, never inside
+// a stream capture, where the zeroing would be recorded instead of executed.
+void reduce_prepare();
+void gemm_tc_prepare();
+void gemm_tc_wait_probe();    // launches the bounded-wait probe kernel
 int sm_count();
 void destroy_all_graphs();   // captured graphs hold NCCL work: they must go before the communicator does
 

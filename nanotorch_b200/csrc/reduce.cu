@@ -331,6 +331,9 @@ struct Ticket {
 static unsigned *tickets(int64_t need) {
   static Ticket t;
   if (need > t.capacity) {
+    if (is_capturing())
+      fail_runtime("reduction: the ticket counters must grow, which cannot happen inside a graph capture; run the "
+                   "step once eagerly before capturing it.");
     int64_t cap = need < 65536 ? 65536 : need;
     size_t rounded;
     void *p = device_alloc(size_t(cap) * sizeof(unsigned), &rounded);
@@ -341,6 +344,8 @@ static unsigned *tickets(int64_t need) {
   }
   return t.ptr;
 }
+
+void reduce_prepare() { tickets(1); }
 
 struct Plan {
   KeepIndex keep{}, drop{};

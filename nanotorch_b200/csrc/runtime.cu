@@ -24,6 +24,7 @@ struct Runtime {
   cudaStream_t compute = nullptr;
   cudaStream_t comm = nullptr;
   cudaStream_t copy = nullptr;
+  cudaStream_t redirect = nullptr;                     // when set, stream() hands this one out (StreamRedirect)
   cudaEvent_t copy_gate = nullptr, copy_done = nullptr;
   bool mm_profile = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> mm_events;
@@ -39,6 +40,8 @@ struct Runtime {
   std::set<int> live_graphs;
   std::map<int, cudaGraphExec_t> graph_exec;
   uint64_t bytes_reserved = 0, bytes_in_use = 0, n_malloc = 0;
+  uint64_t n_requests = 0;                             // device_alloc calls, served from the cache or not
+  std::atomic<long long> wait_limit{1LL << 31};        // SM clocks a bounded device-side spin may take
   size_t pin_cached_bytes = 0;
   std::atomic<uint64_t> launches{0};
   std::mt19937_64 rng{std::random_device{}()};
@@ -91,13 +94,44 @@ cudaStream_t stream() {
   Runtime &r = rt();
   std::lock_guard<std::mutex> lk(r.mu);
   ensure_streams_locked(r);
+  return r.redirect ? r.redirect : r.compute;
+}
+cudaStream_t compute_stream() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  ensure_streams_locked(r);
   return r.compute;
+}
+StreamRedirect::StreamRedirect(cudaStream_t to) {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  prev = r.redirect;
+  r.redirect = to;
+}
+StreamRedirect::~StreamRedirect() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  r.redirect = prev;
 }
 cudaStream_t comm_stream() {
   Runtime &r = rt();
   std::lock_guard<std::mutex> lk(r.mu);
   ensure_streams_locked(r);
   return r.comm;
+}
+bool is_capturing() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  return r.capturing != 0;
+}
+long long wait_limit_clocks() { return rt().wait_limit.load(std::memory_order_relaxed); }
+void check_device_errors() {
+  const int tc_err = gemm_tc_take_error();
+  if (tc_err != 0)
+    fail_runtime("gemm_3xtf32: a bounded device-side wait ran out (code " + std::to_string(tc_err) +
+                 ": 1 = producer waiting for a free stage, 2 = MMA waiting for data, 3 = epilogue waiting for "
+                 "the accumulator, 4 = MMA waiting for a drained accumulator, 5 = the wait probe); results of "
+                 "the launches since the last synchronisation are invalid.");
 }
 int sm_count() {
   Runtime &r = rt();
@@ -179,6 +213,7 @@ void *device_alloc(size_t nbytes, size_t *rounded) {
   ensure_streams_locked(r);
   size_t sz = round_block(nbytes);
   *rounded = sz;
+  r.n_requests += 1;
   if (r.capturing) {
     auto &gc = r.graph_cache[r.capturing];
     auto git = gc.find(sz);
@@ -477,6 +512,7 @@ static nt_storage *to_device_impl(nt_storage *s, int device) {
     NT_CUDA_CHECK(cudaMemcpyAsync(out->data, s->data, nbytes, kind, st));
     // The host side of either direction may be reused or read right after the call returns.
     NT_CUDA_CHECK(cudaStreamSynchronize(st));
+    if (kind == cudaMemcpyDeviceToHost && !is_capturing()) check_device_errors(); // values are about to be read
   }
   return out.release();
 }
@@ -503,11 +539,7 @@ int nt_cuda_sync(void) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream()));
     NT_CUDA_CHECK(cudaStreamSynchronize(comm_stream()));
     NT_CUDA_CHECK(cudaStreamSynchronize(rt().copy));
-    const int tc_err = gemm_tc_take_error();
-    if (tc_err != 0)
-      fail_runtime("gemm_3xtf32: a pipeline wait ran out (code " + std::to_string(tc_err) +
-                   ": 1 = producer waiting for a free stage, 2 = MMA waiting for data, 3 = epilogue waiting for "
-                   "the accumulator); the affected products are invalid.");
+    check_device_errors();
   }
   NT_API_END
 }
@@ -561,6 +593,22 @@ int nt_allocator_stats(uint64_t *bytes_reserved, uint64_t *bytes_in_use, uint64_
   if (n_cuda_malloc) *n_cuda_malloc = r.n_malloc;
   NT_API_END
 }
+
+int nt_allocator_requests(uint64_t *out) {
+  NT_API_BEGIN
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  *out = r.n_requests;
+  NT_API_END
+}
+
+int nt_set_wait_limit_clocks(int64_t clocks) {
+  NT_API_BEGIN
+  if (clocks < 1000) fail_invalid("nt_set_wait_limit_clocks: at least 1000 clocks.");
+  rt().wait_limit.store(clocks, std::memory_order_relaxed);
+  NT_API_END
+}
+int64_t nt_get_wait_limit_clocks(void) { return rt().wait_limit.load(std::memory_order_relaxed); }
 
 int nt_allocator_trim(void) {
   NT_API_BEGIN
@@ -626,6 +674,11 @@ int nt_matmul_profile_read(double *total_ms, int64_t *launches) {
 int nt_graph_begin_capture(int *graph_id) {
   NT_API_BEGIN
   cudaStream_t st = stream();
+  // state that kernels expect to find zeroed must exist before the capture starts: created inside
+  // it, its zeroing would only be recorded, and eager launches issued before the first replay
+  // would find it uninitialised
+  reduce_prepare();
+  gemm_tc_prepare();
   Runtime &r = rt();
   std::lock_guard<std::mutex> lk(r.mu);
   if (r.capturing) fail_runtime("nt_graph_begin_capture: a capture is already in progress.");
@@ -819,6 +872,7 @@ int nt_storage_download(const nt_storage *src, void *host_dst, int64_t nbytes) {
     cudaStream_t st = stream();
     NT_CUDA_CHECK(cudaMemcpyAsync(host_dst, src->data, size_t(nbytes), cudaMemcpyDeviceToHost, st));
     NT_CUDA_CHECK(cudaStreamSynchronize(st));
+    check_device_errors(); // the caller is about to read these values
   }
   NT_API_END
 }

@@ -41,9 +41,12 @@ def _kaiming_W(fan_in: int, fan_out: int, device) -> Tensor:
 
 
 class Linear(Module):
-    """x @ W + b with W of shape (fan_in, fan_out)."""
+    """x @ W + b with W of shape (fan_in, fan_out).
 
-    def __init__(self, fan_in: int, fan_out: int, bias: bool = True, device: Device | str = Device.Cuda) -> None:
+    Built on the Cpu and moved with ``.to(device)``, as in the reference (src/nanotorch/nn/module.py:45-63);
+    ``device`` (an addition) builds the parameters in place on that device instead."""
+
+    def __init__(self, fan_in: int, fan_out: int, bias: bool = True, device: Device | str = Device.Cpu) -> None:
         with no_grad():
             self._W = _kaiming_W(fan_in, fan_out, device)
         self._W.enable_grad()

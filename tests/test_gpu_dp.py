@@ -47,7 +47,7 @@ WORKER = textwrap.dedent(r"""
         layers.append(nn.Linear(dims[i], dims[i + 1]))
         if i < 2:
             layers.append(nn.Tanh())
-    model = nn.Sequential(*layers)
+    model = nn.Sequential(*layers).to("cuda")
     B = 512
     X = np.random.default_rng(40).standard_normal((B, dims[0])).astype(np.float32)
     Y = np.random.default_rng(41).standard_normal((B, dims[-1])).astype(np.float32)
@@ -92,7 +92,15 @@ def _run(world: int, script: Path, out: Path):
                    MASTER_PORT=str(port), NT_REPO=str(REPO), NT_OUT=str(out), NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE,
                                       stderr=subprocess.STDOUT, text=True))
-    outs = [p.communicate(timeout=600)[0] for p in procs]
+    outs = []
+    try:
+        for p in procs:
+            outs.append(p.communicate(timeout=600)[0])
+    except subprocess.TimeoutExpired:
+        for p in procs:  # leave no rank behind on the shared GPUs
+            p.kill()
+            p.wait()
+        raise
     for rank, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {rank} of {world} failed:\n{o[-3000:]}"
     return np.load(out)

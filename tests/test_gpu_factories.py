@@ -55,7 +55,7 @@ def test_device_generator_matches_its_checker(nt, port):
         # parameter initialisation without a host loop or a host-to-device copy
         import nanotorch_b200.nn as nn
 
-        layer = nn.Linear(512, 256)
+        layer = nn.Linear(512, 256, device="cuda")
         w = layer.parameters()[0].numpy()
         bound = np.sqrt(6.0 / 512)
         assert w.shape == (512, 256) and np.abs(w).max() <= bound and w.std() > 0.5 * bound / np.sqrt(3)

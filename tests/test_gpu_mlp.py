@@ -17,7 +17,7 @@ def build(nt, dims, act):
         layers.append(nn.Linear(dims[i], dims[i + 1]))
         if i < len(dims) - 2:
             layers.append(act())
-    return nn.Sequential(*layers)
+    return nn.Sequential(*layers).to("cuda")  # built on the Cpu and moved, as the reference's scripts do
 
 
 @pytest.mark.parametrize("mode", [2, 0, 1])
@@ -125,6 +125,83 @@ def test_captured_step_replays_bit_exact(nt):
         assert_bit_exact(a, b, "parameters after replayed steps")
 
 
+@pytest.mark.parametrize("graph_mode", [False, True])
+def test_side_stream_update_equals_plain_sgd(nt, graph_mode):
+    """DataParallelSGD with one rank: no collective, but every bucket's update runs on the communication
+    stream the moment backward has finished that bucket's gradients.  Same bits as GradientDescent after
+    six steps, eagerly and as a replayed CUDA graph (the cross-stream edges are part of the capture)."""
+    import nanotorch_b200.nn as nn
+    from nanotorch_b200.dp import Communicator, DataParallelSGD
+
+    X = nt.Tensor.from_numpy(np.random.default_rng(1).standard_normal((512, 640)).astype(np.float32), "cuda")
+    Y = nt.Tensor.from_numpy(np.random.default_rng(2).standard_normal((512, 64)).astype(np.float32), "cuda")
+
+    def run(side: bool):
+        model = build(nt, [640, 768, 768, 64], nn.Tanh)
+        if side:
+            opt = DataParallelSGD(model.parameters(), 1e-2, Communicator(0, 1, None))
+            assert [len(b) for b in opt._buckets] == [2, 2, 2]
+        else:
+            opt = nn.GradientDescent(model.parameters(), lr=1e-2)
+
+        def step():
+            loss = nt.mean((model(X) - Y) ** 2)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            return loss
+
+        losses = [float(step().numpy()) for _ in range(2)]
+        if side and graph_mode:
+            g = nt._C.Graph()
+            with g.capture():
+                loss = step()
+            for _ in range(4):
+                g.replay()
+                losses.append(float(loss.numpy()))
+            g.close()
+        else:
+            losses += [float(step().numpy()) for _ in range(4)]
+        if side:
+            opt.detach()
+        return np.array(losses), [p.numpy() for p in model.parameters()]
+
+    plain_losses, plain_params = run(False)
+    side_losses, side_params = run(True)
+    assert np.array_equal(plain_losses, side_losses), (plain_losses, side_losses)
+    for a, b in zip(plain_params, side_params):
+        assert_bit_exact(a, b, "parameters after six steps")
+
+
+def test_training_script_flow(nt):
+    """The steps of the reference's training script (scripts/train_mlp_basic.py:30-58) as it writes them:
+    data made on the Cpu and moved, a matrix @ 1-D product for the targets, modules built on the Cpu and
+    moved with .to(device), batches taken by slicing, squeeze() on the prediction, the loss read with
+    .cpu().item().  The loss must fall."""
+    import nanotorch_b200.nn as nn
+
+    nt.manual_seed(3)
+    device = "cuda"
+    n, f, h, bs = 4096, 64, 64, 512
+    X = nt.rand(n, f).to(device)
+    y = (X @ nt.randint(-10, 10, (f,)).to(device) + 3.14).to(device)
+    model = nn.Sequential(nn.Linear(f, h), nn.ReLU(), nn.Linear(h, h), nn.Tanh(), nn.Linear(h, 1)).to(device)
+    optimizer = nn.GradientDescent(model.parameters(), lr=1e-4)
+    first = last = None
+    for _ in range(3):
+        for i in range(0, n, bs):
+            xb, yb_true = X[i:i + bs], y[i:i + bs]
+            yb_pred = model(xb)
+            loss = nt.mean((yb_pred.squeeze() - yb_true) ** 2)
+            optimizer.zero_grad()
+            loss.backward()
+            optimizer.step()
+            last = loss.cpu().item()
+            first = last if first is None else first
+    assert np.isfinite(last) and last < first
+    assert isinstance(yb_true[0].cpu().item(), float) and isinstance(yb_pred[0].cpu().item(), float)
+
+
 @pytest.mark.parametrize("mode", [1, 3, 0, 2])
 def test_fused_linear_is_the_composed_form_bit_for_bit(nt, mode):
     """nn.Linear's one-call path (bias added in the GEMM epilogue in mode 1, by an in-place add in the
@@ -135,7 +212,7 @@ def test_fused_linear_is_the_composed_form_bit_for_bit(nt, mode):
     nt._C.set_matmul_mode(mode)
     try:
         for m, k, n in [(64, 48, 10), (257, 100, 130), (512, 256, 384), (1000, 64, 4096)]:
-            layer = nn.Linear(k, n)
+            layer = nn.Linear(k, n, device="cuda")
             W, b = layer.parameters()
             with nt.no_grad():
                 b += nt.Tensor.from_numpy(rng.standard_normal(n).astype(np.float32), "cuda")  # a non-zero bias

@@ -156,8 +156,11 @@ def test_matmul_golden(nt, golden, case, mode):
         ta, tb = dev(nt, a, True), dev(nt, b, True)
         res = ta @ tb
         (res * dev(nt, g)).sum().backward()
+        # shapes included: a 1-D right operand gets its gradient back as (k, 1), as in the reference
+        # (autograd/ops_binary.py:253-267)
+        assert tb.grad.shape == golden[f"mm/{case}/gb"].shape
         checks = [(res.numpy(), golden[f"mm/{case}/out"]), (ta.grad.numpy(), golden[f"mm/{case}/ga"]),
-                  (tb.grad.numpy().reshape(-1), golden[f"mm/{case}/gb"].reshape(-1))]
+                  (tb.grad.numpy(), golden[f"mm/{case}/gb"])]
         for got, want in checks:
             if mode == 2 and case != "bcast_batch":
                 assert_bit_exact(got, want, case)  # bcast_batch sums the batch gradient in another order
