@@ -200,8 +200,9 @@ int nt_argmin(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage 
  * with NT_ERR_INVALID -- use nt_sum for those.  Shapes that need no split have no limit.  The first call on a device looks up the array's device
  * address; make that first call before any stream capture.  All calls share the one array and each
  * leaves its partial sums behind: two calls that overlap on the GPU (different streams or
- * processes' threads) race; calls issued through this library's single stream do not.  Runs on
- * the library stream, asynchronously. */
+ * processes' threads) race; calls issued through this library's single stream do not.  The looked-up
+ * address is cached per device without a lock: like the rest of the library (the allocator aside) the
+ * entry point is for one calling thread at a time.  Runs on the library stream, asynchronously. */
 int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float *out);
 
 /* ------------------------------------------------------------------ matmul (src/cpp/ops/matmul.cu:236-273) */

@@ -391,16 +391,27 @@ template <class T> __global__ void fill_kernel(T *out, int64_t n, T value) {
   for (; i < n; i += step) out[i] = value;
 }
 
-// Storage::cast semantics (src/cpp/storage.cpp:54-62): to Bool is `s != 0`, everything else static_cast.
+// Storage::cast semantics (src/cpp/storage.cpp:54-62): to Bool is `s != 0`, everything else static_cast
+// -- which the reference always evaluates on the host, also for Cuda storages (it round-trips them).
+// A floating-point value outside the integer type's range, or NaN, is undefined in C++; on the x86-64
+// hosts the reference runs on the conversion instruction returns the "integer indefinite" value, the
+// most negative integer, and that is what its tensors then hold.  The device's own conversion would
+// saturate (and turn NaN into 0), so the range test is explicit here.
+template <class S, class D> __device__ __forceinline__ D cast_value(S x) {
+  if constexpr (std::is_same_v<D, bool>) {
+    return x ? true : false;
+  } else if constexpr (std::is_floating_point_v<S> && std::is_same_v<D, int32_t>) {
+    return (x > S(-2147483649.0) && x < S(2147483648.0)) ? static_cast<int32_t>(x) : INT32_MIN;
+  } else if constexpr (std::is_floating_point_v<S> && std::is_same_v<D, int64_t>) {
+    return (x >= S(-9223372036854775808.0) && x < S(9223372036854775808.0)) ? static_cast<int64_t>(x) : INT64_MIN;
+  } else {
+    return static_cast<D>(x);
+  }
+}
 template <class S, class D> __global__ void cast_kernel(const S *in, D *out, int64_t n) {
   int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   int64_t step = int64_t(gridDim.x) * blockDim.x;
-  for (; i < n; i += step) {
-    if constexpr (std::is_same_v<D, bool>)
-      out[i] = in[i] ? true : false;
-    else
-      out[i] = static_cast<D>(in[i]);
-  }
+  for (; i < n; i += step) out[i] = cast_value<S, D>(in[i]);
 }
 
 // eye(n): ones where row == column, i.e. at every (n + 1)-th element (src/cpp/factory.cu:51-59)

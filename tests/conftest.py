@@ -22,6 +22,13 @@ def golden():
 
 
 @pytest.fixture(scope="session")
+def golden_extra():
+    """Second fixture file of the same generator: casts over every dtype pair, comparisons with NaN and
+    signed zeros, pow with other exponents, min/max over NaN / signed-zero slices, non-finite matmul."""
+    return np.load(REPO / "tests" / "golden" / "reference_cpu_extra.npz")
+
+
+@pytest.fixture(scope="session")
 def port():
     from oracle.oracle import PortOracle
 

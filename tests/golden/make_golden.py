@@ -252,6 +252,79 @@ def rng_cases(nt, out: dict):
     out["rng/seed0"] = A(nt.rand(16))
 
 
+def _typed(nt, a: np.ndarray):
+    dt = {"bool": nt.bool_, "int32": nt.int32, "int64": nt.int64, "float32": nt.float32, "float64": nt.float64}[a.dtype.name]
+    return nt.Tensor(a.tolist(), dtype=dt)
+
+
+CAST_INPUTS = {
+    "float32": np.array([np.nan, np.inf, -np.inf, 0.0, -0.0, 0.5, -0.5, 1.9, -1.9, 2147483520.0, 2147483648.0,
+                         -2147483648.0, -2147483904.0, 3e9, -3e9, 1e10, 9.2e18, 9.3e18, -9.3e18, 1e20, 1e-45, 16777217.0,
+                         255.0, 256.0, -1.0, 1.0], np.float32),
+    "float64": np.array([np.nan, np.inf, -np.inf, 0.0, -0.0, 0.5, -0.5, 1.9, -1.9, 2147483647.0, 2147483647.5, 2147483648.0,
+                         -2147483648.0, -2147483648.9, -2147483649.0, 3e9, 9.2e18, 9.3e18, -9.3e18, 1e300, 1e-320, 3.5e38,
+                         16777217.0, 0.1, -1.0, 1.0], np.float64),
+    "int64": np.array([0, 1, -1, 2**31 - 1, 2**31, -(2**31), -(2**31) - 1, 2**40 + 3, 2**24 + 1, 2**53 + 1, 2**63 - 1,
+                       -(2**63), 255, 256, 123456789012], np.int64),
+    "int32": np.array([0, 1, -1, 2**31 - 1, -(2**31), 2**24 + 1, 255, 256, 16777217], np.int32),
+    "bool": np.array([True, False, True], np.bool_),
+}
+
+
+def extra_cases(nt, out: dict):
+    """Cases the first fixture file does not hold: Storage::cast over every dtype pair with out-of-range,
+    NaN and rounding inputs; comparisons with NaN and signed zeros in Float32/Float64/Int64; pow with
+    other exponents than 2 (forward and PowOp backward); min/max over slices holding NaN or both zeros;
+    matmul with non-finite and huge operands."""
+    for src, a in CAST_INPUTS.items():
+        out[f"cast/in/{src}"] = a
+        for dst in ("bool", "int32", "int64", "float32", "float64"):
+            t = _typed(nt, a).to({"bool": nt.bool_, "int32": nt.int32, "int64": nt.int64, "float32": nt.float32,
+                                  "float64": nt.float64}[dst])
+            out[f"cast/{src}/{dst}"] = A(t)
+    # comparisons
+    rng = np.random.default_rng(600)
+    specials = np.array([np.nan, 0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, 1e-45], np.float64)
+    for kind in ("float32", "float64", "int64"):
+        if kind == "int64":
+            x = rng.integers(-3, 4, (9, 8)).astype(np.int64)
+            y = rng.integers(-3, 4, (8, 9)).astype(np.int64)
+        else:
+            x = rng.choice(specials, (9, 8)).astype(kind)
+            y = rng.choice(specials, (8, 9)).astype(kind)
+        out[f"cmp/in/{kind}/x"], out[f"cmp/in/{kind}/y"] = x, y
+        tx, ty = _typed(nt, x), _typed(nt, y).T          # second operand through a transposed view
+        out[f"cmp/{kind}/eq"], out[f"cmp/{kind}/gt"], out[f"cmp/{kind}/ge"] = A(tx == ty), A(tx > ty), A(tx >= ty)
+        out[f"cmp/{kind}/lt"], out[f"cmp/{kind}/le"] = A(tx < ty), A(tx <= ty)
+    # pow
+    base = np.concatenate([rng.uniform(-3, 3, 400), rng.uniform(0.01, 20, 180),
+                           [0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, np.nan, 1e-45, -1e-45, 1e-20, 1e20, -1e20, 2.0, 0.5]]).astype(np.float32)
+    G = rng.standard_normal(base.shape).astype(np.float32)
+    out["powx/in/x"], out["powx/in/G"] = base, G
+    for e in (3.0, -2.0, -1.0, 0.5, 3.7, 4.0, 0.0, 1.0, 2.0, -0.5):
+        x = T(nt, base, True)
+        y = x ** e
+        out[f"powx/{e}/out"] = A(y)
+        (y * T(nt, G)).sum().backward()
+        out[f"powx/{e}/gx"] = A(x.grad)
+    # min / max over slices with NaN and signed zeros (the sequential combiner is order dependent there)
+    ext = np.array([[1.0, np.nan, 3.0, 2.0], [3.0, np.nan, 1.0, 2.0], [1.0, 2.0, 3.0, np.nan], [np.nan, 1.0, 2.0, 3.0],
+                    [0.0, -0.0, -1.0, -2.0], [-0.0, 0.0, -1.0, -2.0], [0.0, -0.0, 1.0, 2.0], [-0.0, 0.0, 1.0, 2.0],
+                    [np.nan, np.nan, np.nan, np.nan], [-np.inf, -np.inf, -np.inf, -np.inf]], np.float32)
+    out["ext/in/x"] = ext
+    out["ext/max"], out["ext/min"] = A(T(nt, ext).max(1)), A(T(nt, ext).min(1))
+    # matmul with non-finite and huge operands
+    a = rng.uniform(-1, 1, (6, 8)).astype(np.float32)
+    b = rng.uniform(-1, 1, (8, 5)).astype(np.float32)
+    a[0, 2], a[1, 3], a[2, 4] = np.inf, np.nan, -np.inf
+    a[3, :] = 3.0e38 / 8            # finite, products near FLT_MAX
+    a[4, 1] = 3.4e38                # rounds to infinity in TF32
+    b[:, 4] = 0.25
+    b[1, 2] = 0.0
+    out["mmx/a"], out["mmx/b"] = a, b
+    out["mmx/out"] = A(T(nt, a) @ T(nt, b))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("NT_REFERENCE", "/root/reference"),
@@ -269,6 +342,11 @@ def main():
     np.savez_compressed(HERE / "reference_cpu.npz", **out)
     size = (HERE / "reference_cpu.npz").stat().st_size
     print(f"wrote {len(out)} arrays, {size / 1024:.0f} KiB")
+    extra: dict[str, np.ndarray] = {}
+    with np.errstate(all="ignore"):
+        extra_cases(nt, extra)
+    np.savez_compressed(HERE / "reference_cpu_extra.npz", **extra)
+    print(f"wrote {len(extra)} arrays, {(HERE / 'reference_cpu_extra.npz').stat().st_size / 1024:.0f} KiB")
 
 
 if __name__ == "__main__":

@@ -1,0 +1,255 @@
+"""GPU parity on the cases the other files leave out (through the C ABI):
+
+  - pow with exponents other than 2 -- the hand-written products and reciprocals for 3, -1, -2 and the
+    double-precision path for the rest -- at 2^24 elements against the CPU oracle (<= 2 ulp), over special
+    values against the reference's own outputs, and PowOp's backward for exponents 3, 4, -1;
+  - Storage::cast over every dtype pair: the reference's tables (out-of-range and NaN inputs included),
+    and 2^22-element inputs, also through strided and reversed views;
+  - comparisons and `equals` on strided / reversed Float32, Float64 and Int64 views with NaN and signed zeros;
+  - the exact-mode matmul (mode 2) at 2048^3, bit for bit against the oracle's triple loop on sampled rows;
+  - min / max over slices holding NaN or zeros of both signs: what this library returns is pinned;
+  - matmul with infinite, NaN and near-FLT_MAX operands in every mode;
+  - the bounded device-side wait: made to run out on purpose, reported as an error, context still usable.
+"""
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.util import assert_bit_exact, assert_scaled, assert_ulp, ulp_distance
+
+pytestmark = pytest.mark.gpu
+
+NP = {"bool": np.bool_, "int32": np.int32, "int64": np.int64, "float32": np.float32, "float64": np.float64}
+
+
+def dev(nt, a, requires_grad=False):
+    return nt.Tensor.from_numpy(a, "cuda", requires_grad=requires_grad)
+
+
+def nt_dtype(nt, name):
+    return {"bool": nt.bool_, "int32": nt.int32, "int64": nt.int64, "float32": nt.float32, "float64": nt.float64}[name]
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("e", [3.0, -2.0, -1.0, 0.5, 3.7, 4.0, 0.0, 1.0, -0.5])
+def test_pow_special_values_vs_reference(nt, golden_extra, e):
+    x = golden_extra["powx/in/x"]
+    got = (dev(nt, x) ** e).numpy()
+    assert_ulp(got, golden_extra[f"powx/{e}/out"], 2, f"pow {e}")
+
+
+@pytest.mark.parametrize("e", [3.0, -2.0, -1.0, 0.5, 3.7])
+def test_pow_full_size(nt, port, e):
+    n = 1 << 24
+    rng = np.random.default_rng(int(abs(e) * 10) + 50)
+    if e == int(e):
+        x = rng.uniform(-3, 3, n).astype(np.float32)
+        x[:4096] = (rng.uniform(0.3, 3.0, 4096) * 1e-19).astype(np.float32)   # 1/x^2 near the top of the range
+        x[4096:8192] = rng.uniform(1e12, 1e13, 4096).astype(np.float32)       # x^3 near the top of the range
+    else:
+        x = rng.uniform(0.1, 10, n).astype(np.float32)
+    with np.errstate(all="ignore"):
+        want = port.unary("pow", x, e)
+    got = (dev(nt, x.reshape(4096, 4096)) ** e).numpy().reshape(-1)
+    worst = assert_ulp(got, want, 2, f"pow {e} at 2^24")
+    print(f"pow {e}: worst {worst} ulp, {int((ulp_distance(got, want) > 0).sum())} of {n} elements differ")
+
+
+@pytest.mark.parametrize("e", [3.0, 4.0, -1.0])
+def test_pow_backward_full_size(nt, port, e):
+    """(g * e) * x ** (e - 1): exponents 3, 4 and -1 land on the product / reciprocal special cases."""
+    n = 1 << 24
+    rng = np.random.default_rng(int(e) + 70)
+    x = rng.uniform(0.2, 3, n).astype(np.float32) * rng.choice([-1.0, 1.0], n).astype(np.float32)
+    g = rng.standard_normal(n).astype(np.float32)
+    tx = dev(nt, x.reshape(4096, 4096), True)
+    ((tx ** e) * dev(nt, g.reshape(4096, 4096))).sum().backward()
+    want = O.pow_backward(port, g, x, e)
+    assert_ulp(tx.grad.numpy().reshape(-1), want, 2, f"pow {e} backward")
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("src", list(NP))
+def test_cast_tables(nt, golden_extra, src):
+    a = golden_extra[f"cast/in/{src}"]
+    t = dev(nt, a)
+    for dst in NP:
+        got = t.to(nt_dtype(nt, dst)).numpy()
+        want = golden_extra[f"cast/{src}/{dst}"]
+        assert got.dtype == want.dtype
+        if dst.startswith("float"):
+            same = (got.view(f"u{got.itemsize}") == want.view(f"u{want.itemsize}")) | (np.isnan(got) & np.isnan(want))
+            assert same.all(), (src, dst, got, want)
+        else:
+            assert np.array_equal(got, want), (src, dst, got, want)
+
+
+@pytest.mark.parametrize("src", ["float32", "float64", "int64", "int32"])
+def test_cast_large_and_through_views(nt, src):
+    rng = np.random.default_rng(81)
+    R, C = 2048, 2048
+    if src.startswith("float"):
+        a = (rng.standard_normal((R, C)) * 10.0 ** rng.integers(-3, 12, (R, C))).astype(NP[src])
+        a[rng.integers(0, R, 500), rng.integers(0, C, 500)] = np.nan
+        a[rng.integers(0, R, 500), rng.integers(0, C, 500)] = np.inf
+    else:
+        hi = 2 ** 62 if src == "int64" else 2 ** 31 - 1
+        a = rng.integers(-hi, hi, (R, C)).astype(NP[src])
+    t = dev(nt, a)
+    for dst in NP:
+        if dst == src:
+            continue
+        with np.errstate(all="ignore"):
+            want = a.astype(NP[dst])
+            want_view = np.ascontiguousarray(a[::-1, 1::3]).astype(NP[dst])
+        got = t.to(nt_dtype(nt, dst)).numpy()
+        got_view = t[::-1, 1::3].to(nt_dtype(nt, dst)).numpy()   # reversed rows, every third column
+        for g_, w_ in ((got, want), (got_view, want_view)):
+            if dst.startswith("float"):
+                assert ((g_ == w_) | (np.isnan(g_) & np.isnan(w_))).all(), (src, dst)
+            else:
+                assert np.array_equal(g_, w_), (src, dst)
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("kind", ["float32", "float64", "int64"])
+def test_comparisons_on_views(nt, golden_extra, kind):
+    x, y = golden_extra[f"cmp/in/{kind}/x"], golden_extra[f"cmp/in/{kind}/y"]
+    tx, ty = dev(nt, x), dev(nt, y).T
+    for key, got in (("eq", tx == ty), ("gt", tx > ty), ("ge", tx >= ty), ("lt", tx < ty), ("le", tx <= ty)):
+        assert np.array_equal(got.numpy(), golden_extra[f"cmp/{kind}/{key}"]), (kind, key)
+    # larger, through reversed / stepped / broadcast views, against numpy (IEEE comparisons are unambiguous)
+    rng = np.random.default_rng(91)
+    specials = np.array([np.nan, 0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, 2.5], np.float64)
+    if kind == "int64":
+        a, b = rng.integers(-4, 5, (513, 1030)).astype(np.int64), rng.integers(-4, 5, (1030, 1026)).astype(np.int64)
+    else:
+        a, b = rng.choice(specials, (513, 1030)).astype(NP[kind]), rng.choice(specials, (1030, 1026)).astype(NP[kind])
+    ta, tb = dev(nt, a), dev(nt, b)
+    va, na = ta[::-1, ::2], a[::-1, ::2]                         # (513, 515): reversed rows, stepped columns
+    vb, nb = tb.T[::2, 5:520][:513], b.T[::2, 5:520][:513]       # transposed, stepped, offset
+    with np.errstate(all="ignore"):
+        for name, got, want in (("eq", va == vb, na == nb), ("gt", va > vb, na > nb), ("ge", va >= vb, na >= nb)):
+            assert np.array_equal(got.numpy(), want), (kind, name)
+        row = tb[3, :515]
+        assert np.array_equal((va > row).numpy(), na > b[3, :515]), "row broadcast"
+    assert nt._C.equals(va._C_view, va._C_view) == (not np.isnan(na.astype(np.float64)).any())
+    assert not nt._C.equals(va._C_view, vb._C_view)
+
+
+# ---------------------------------------------------------------------------------------------
+def test_exact_matmul_2048_cubed_bit_for_bit(nt, port):
+    """Mode 2 restates the reference's CPU loop (one rounded multiply, one rounded add, ascending k): every
+    output row depends on its own row of A only, so 96 rows of the 2048^3 product pin the whole kernel."""
+    rng = np.random.default_rng(30)
+    A = rng.uniform(-1, 1, (2048, 2048)).astype(np.float32)
+    B = rng.uniform(-1, 1, (2048, 2048)).astype(np.float32)
+    nt._C.set_matmul_mode(2)
+    try:
+        got = (dev(nt, A) @ dev(nt, B)).numpy()
+        got_t = (dev(nt, np.ascontiguousarray(A.T)).T @ dev(nt, np.ascontiguousarray(B.T)).T).numpy()
+    finally:
+        nt._C.set_matmul_mode(1)
+    rows = np.concatenate([np.arange(32), rng.choice(np.arange(32, 2048), 64, replace=False)])
+    want = port.matmul(A[rows], B)
+    assert_bit_exact(got[rows], want, "2048^3, mode 2")
+    assert_bit_exact(got_t[rows], want, "2048^3, mode 2, both operands through transposed views")
+
+
+# ---------------------------------------------------------------------------------------------
+def test_extremum_over_nan_and_signed_zero_slices_is_pinned(nt, golden_extra):
+    """The reference folds a slice sequentially: a NaN replaces the running extremum and the next element
+    replaces the NaN, so its answer for a slice that holds a NaN depends on the element order; of +0 and -0
+    the first one wins.  This library reduces in parallel.  Pinned here: a slice without NaN is unaffected by
+    NaNs elsewhere in the tensor (bit-exact, and equal to the reference's), the extremum of a slice that
+    holds a NaN is either NaN or one of its non-NaN elements, a zero extremum is a zero (of either sign), an
+    all -inf slice gives the reference's -FLT_MAX for max."""
+    x = golden_extra["ext/in/x"]
+    t = dev(nt, x)
+    for name, want in (("max", golden_extra["ext/max"]), ("min", golden_extra["ext/min"])):
+        got = getattr(t, name)(1).numpy()
+        for i, row in enumerate(x):
+            if np.isnan(row).any():
+                assert np.isnan(got[i]) or got[i] in row[~np.isnan(row)], (name, i, got[i])
+            elif want[i] == 0:
+                assert got[i] == 0, (name, i, got[i])
+            else:
+                assert got[i] == want[i], (name, i, got[i], want[i])
+    # large: one NaN row and one all-zero-mixed row among ordinary rows, all three kernels' layouts
+    rng = np.random.default_rng(93)
+    big = rng.standard_normal((300, 5000)).astype(np.float32)
+    big[7, 1234] = np.nan
+    big[9, :] = np.where(rng.integers(0, 2, 5000) == 1, 0.0, -0.0) - np.abs(big[9, :]) * (rng.integers(0, 50, 5000) > 0)
+    tb = dev(nt, big)
+    clean = np.ones(300, bool)
+    clean[7] = False
+    for axes, ref in (((1,), big.max(axis=1)), ((0,), None)):
+        got = tb.max(axes).numpy()
+        if ref is not None:
+            assert np.array_equal(got[clean], ref[clean])
+            assert np.isnan(got[7]) or got[7] in big[7]
+            assert got[9] == 0
+        else:
+            cols = np.arange(5000) != 1234
+            assert np.array_equal(got[cols], np.max(big[:, cols], axis=0))
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode", [2, 0, 1, 3])
+def test_matmul_nonfinite_operands(nt, golden_extra, mode):
+    """Exact modes reproduce the reference's table (infinities, NaN row, products near FLT_MAX).  The
+    3xTF32 modes split x = hi + lo: a NaN operand gives NaN where the reference gives NaN; an infinite
+    operand gives a non-finite value (an infinity of the right sign, or NaN where the split's cross terms
+    meet inf * 0 or inf - inf) where the reference gives an infinity; finite operands up to FLT_MAX,
+    including those whose TF32 rounding would overflow, give the finite product."""
+    a, b, want = golden_extra["mmx/a"], golden_extra["mmx/b"], golden_extra["mmx/out"]
+    nt._C.set_matmul_mode(mode)
+    try:
+        got = (dev(nt, a) @ dev(nt, b)).numpy()
+    finally:
+        nt._C.set_matmul_mode(1)
+    finite = np.isfinite(want)
+    if mode == 2:
+        assert_bit_exact(got, want, "mode 2")
+        return
+    assert np.array_equal(np.isnan(got[1]), np.isnan(want[1])) and np.isnan(got[1]).all()
+    if mode == 0:
+        assert np.array_equal(got[~finite & ~np.isnan(want)], want[~finite & ~np.isnan(want)])
+    else:
+        assert (~np.isfinite(got[~finite])).all()
+        inf_rows = got[[0, 2]]
+        ok = np.isnan(inf_rows) | (inf_rows == want[[0, 2]])
+        assert ok.all(), inf_rows
+    bound = np.abs(a[3:].astype(np.float64)) @ np.abs(b.astype(np.float64))
+    assert np.isfinite(got[3:]).all()
+    assert_scaled(got[3:], want[3:], bound, 1e-4, f"finite rows, mode {mode}")
+
+
+# ---------------------------------------------------------------------------------------------
+def test_bounded_wait_runs_out_and_is_reported(nt):
+    """Every spin in device code has a limit; past it the kernel records a code and returns.  The probe
+    kernel waits, with the helper and the limit the GEMM pipeline uses, on a barrier nothing arrives on.
+    With the limit lowered to 10^5 clocks it must return at once, the next synchronisation must raise
+    RuntimeError naming the probe's code, and the context must stay usable (no fault, no hang)."""
+    _C = nt._C
+    a = dev(nt, np.ones((64, 64), np.float32))
+    (a @ a).numpy()                       # the tensor-core path is initialised and healthy
+    before = _C.get_wait_limit_clocks()
+    assert before == 1 << 31
+    with pytest.raises(ValueError):
+        _C.set_wait_limit_clocks(10)
+    _C.set_wait_limit_clocks(100_000)
+    try:
+        _C.wait_probe()
+        with pytest.raises(RuntimeError, match=r"bounded device-side wait ran out \(code 5"):
+            _C.cuda_sync()
+        _C.cuda_sync()                    # reported once, then cleared
+        _C.wait_probe()
+        with pytest.raises(RuntimeError, match="code 5"):
+            a.numpy()                     # a download reports it too: values are never read past a time-out
+    finally:
+        _C.set_wait_limit_clocks(before)
+    got = (a @ a).numpy()                 # the context still works
+    assert np.array_equal(got, np.full((64, 64), 64.0, np.float32))
+    _C.cuda_sync()

@@ -204,3 +204,61 @@ def test_port_matches_reference_native_module(port):
     assert_bit_exact(port.matmul(A, B), ref.matmul(A, B), "matmul")
     assert_bit_exact(port.matmul(A.swapaxes(-1, -2)[..., :4, :4], B[..., :4]), ref.matmul(A.swapaxes(-1, -2)[..., :4, :4], B[..., :4]))
     assert_bit_exact(port.uniform(123, 100), ref.uniform(123, 100), "uniform")
+
+
+# ---------------------------------------------------------------------------------------------
+# second fixture file (tests/golden/reference_cpu_extra.npz, same generator)
+POW_EXPONENTS = [3.0, -2.0, -1.0, 0.5, 3.7, 4.0, 0.0, 1.0, 2.0, -0.5]
+
+
+@pytest.mark.parametrize("e", POW_EXPONENTS)
+def test_pow_other_exponents(golden_extra, port, e):
+    """x ** e and PowOp's backward over negatives, zeros, infinities, NaN and denormals."""
+    x, G = golden_extra["powx/in/x"], golden_extra["powx/in/G"]
+    with np.errstate(all="ignore"):
+        assert_bit_exact(port.unary("pow", x, e), golden_extra[f"powx/{e}/out"], f"pow {e}")
+        assert_bit_exact(O.pow_backward(port, G, x, e), golden_extra[f"powx/{e}/gx"], f"pow {e} backward")
+
+
+def test_compare_with_nan_and_signed_zeros(golden_extra, port):
+    x, y = golden_extra["cmp/in/float32/x"], golden_extra["cmp/in/float32/y"]
+    for name, key in (("pw_equal", "eq"), ("pw_greater", "gt"), ("pw_greater_eq", "ge")):
+        assert np.array_equal(port.binary(name, x, y.T), golden_extra[f"cmp/float32/{key}"]), name
+    # the reference's < and <= are the swapped forms of > and >= (src/nanotorch/ops.py)
+    assert np.array_equal(port.binary("pw_greater", np.ascontiguousarray(y.T), x), golden_extra["cmp/float32/lt"])
+    assert np.array_equal(port.binary("pw_greater_eq", np.ascontiguousarray(y.T), x), golden_extra["cmp/float32/le"])
+    # IEEE comparisons are unambiguous: numpy gives the same tables for every dtype
+    for kind in ("float32", "float64", "int64"):
+        a, b = golden_extra[f"cmp/in/{kind}/x"], golden_extra[f"cmp/in/{kind}/y"].T
+        with np.errstate(all="ignore"):
+            for key, fn in (("eq", np.equal), ("gt", np.greater), ("ge", np.greater_equal), ("lt", np.less), ("le", np.less_equal)):
+                assert np.array_equal(fn(a, b), golden_extra[f"cmp/{kind}/{key}"]), (kind, key)
+
+
+def test_extremum_over_nan_and_signed_zero_slices(golden_extra, port):
+    """The reference's sequential combiner on slices holding NaN (a NaN replaces the running value, the
+    next element replaces the NaN) and both zeros (the first one wins)."""
+    x = golden_extra["ext/in/x"]
+    assert_bit_exact(port.reduce("max", x, [1]), golden_extra["ext/max"], "max")
+    assert_bit_exact(port.reduce("min", x, [1]), golden_extra["ext/min"], "min")
+
+
+def test_matmul_nonfinite_operands(golden_extra, port):
+    with np.errstate(all="ignore"):
+        assert_bit_exact(port.matmul(golden_extra["mmx/a"], golden_extra["mmx/b"]), golden_extra["mmx/out"], "matmul")
+
+
+def test_cast_tables_are_the_host_conversions(golden_extra):
+    """Storage::cast is a host loop of static_casts in the reference (src/cpp/storage.cpp:47-65), also for
+    Cuda storages.  The C conversions of this machine give the same tables, out-of-range and NaN inputs
+    included (the conversion instruction's "integer indefinite" result)."""
+    for src in ("float32", "float64", "int64", "int32", "bool"):
+        a = golden_extra[f"cast/in/{src}"]
+        for dst in ("bool", "int32", "int64", "float32", "float64"):
+            with np.errstate(all="ignore"):
+                want = a.astype(dst)
+            got = golden_extra[f"cast/{src}/{dst}"]
+            if dst.startswith("float"):
+                assert_bit_exact(got.astype(np.float32), want.astype(np.float32), f"{src}->{dst}")
+            else:
+                assert np.array_equal(got, want), (src, dst, got, want)
