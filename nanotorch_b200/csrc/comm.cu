@@ -238,9 +238,8 @@ int nt_comm_allreduce_sum(nt_storage *s) {
 
 int nt_comm_sgd_update(const nt_view *param, const nt_view *grad, float lr, float grad_scale) {
   // same kernel and checks as nt_sgd_update, enqueued on the communication stream
-  Nccl &n = nccl();
   try {
-    if (!n.side_work) comm_after_compute(); // nothing precedes it there yet: order it after the gradient's producer
+    comm_after_compute(); // after the kernels that produced the gradient, whatever else is queued there
   } catch (const Error &e) {
     set_last_error(e.msg);
     return e.code;

@@ -18,6 +18,8 @@ only.  Two runs:
 
 3. The other way round: the reference's own Python package on this library's ``_C`` shim.
 
+4. On a GPU (``-m gpu``): the reference's CUDA-parametrised tests, live on libnt_b200.so.
+
 Skipped without a checkout."""
 
 import os
@@ -146,6 +148,37 @@ def test_the_references_python_layer_runs_on_this_librarys_shim(tmp_path):
             other.append(f"{case.get('classname')}::{case.get('name')}: {text[:300]}")
     assert not other, "\n".join(other[:20])
     assert passed >= 400, passed
+
+
+@pytest.mark.gpu
+def test_on_a_gpu_the_cuda_parametrised_tests_pass(tmp_path):
+    """The reference's CUDA-parametrised tests against libnt_b200.so on a device.
+
+    Most of the reference's tests take a ``device`` fixture with a "cpu" and a "cuda" parameter
+    (tests/conftest.py:5-20), and the "cuda" half is skipped where no device is present.  Here, on a GPU,
+    through the same in-place alias, that half runs on this library -- Python layer and kernels together:
+    the CPU-vs-CUDA differential tests of every unary op (tests/test_ops/test_tensor_unary_ops.py:92-142),
+    the random batched products (tests/test_ops/test_tensor_binary_ops.py:344-357), reductions over
+    views, in-place semantics, the autograd known answers.  Every test that ran with the "cuda" parameter
+    must pass.  Tests that build Cpu tensors reach no kernel here (this library computes on the device
+    only): those may fail with the "requires Cuda" error and with nothing else.  Needs a checkout of the
+    reference (NT_REFERENCE): skipped where there is none."""
+    import nanotorch_b200 as nt
+
+    if not nt.is_available():
+        pytest.skip("no CUDA device")
+    passed, failed = _run(tmp_path, "", OP_FILES + ["tests/test_autograd.py"], extra=("-k", "not test_ops_specs_extensive"))
+    cuda_failed = [(n, t) for n, t in failed if "[cuda" in n or "-cuda" in n]
+    other = [(n, t) for n, t in failed if (n, t) not in cuda_failed and "requires Cuda" not in t]
+    report = tmp_path / "report.xml"
+    cuda_total = sum(1 for case in ET.parse(report).getroot().iter("testcase")
+                     if ("[cuda" in (case.get("name") or "") or "-cuda" in (case.get("name") or ""))
+                     and case.find("skipped") is None)
+    print(f"reference suite on the device: {passed} passed, {len(failed)} failed ({len(cuda_failed)} of them cuda-parametrised, "
+          f"{len(other)} others not explained by 'requires Cuda'); {cuda_total} cuda-parametrised tests ran")
+    assert not cuda_failed, "\n".join(f"{n}: {t[:400]}" for n, t in cuda_failed[:25])
+    assert not other, "\n".join(f"{n}: {t[:400]}" for n, t in other[:25])
+    assert cuda_total >= 800, cuda_total
 
 
 GOLDEN_RUN = r'''
