@@ -53,6 +53,51 @@ def measured_peaks() -> dict:
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def measure_gemm_peaks(seconds: float = 3.0) -> dict:
+    """Denominators that MEASURED_PEAKS.json does not hold, taken the way it takes the bf16 one: cuBLAS
+    through torch.matmul at 8192^3 on this GPU, CUDA events, best of 10 (burst) and back to back for a
+    few seconds (sustained, under the power cap).  TF32: fp32 operands with TF32 products allowed -- the
+    tensor-pipe peak the 3xTF32 kernel is measured against.  FP32: the same product with TF32 off --
+    cuBLAS SGEMM on the CUDA cores, the denominator of the exact-mode SIMT kernel.  torch is only the
+    way to reach cuBLAS here; nothing of it is on the product path."""
+    import torch
+
+    n = 8192
+    flops = 2.0 * n ** 3
+    a = torch.randn(n, n, device="cuda", dtype=torch.float32)
+    b = torch.randn(n, n, device="cuda", dtype=torch.float32)
+    c = torch.empty(n, n, device="cuda", dtype=torch.float32)
+    out = {}
+    for name, allow, budget in (("tf32", True, seconds), ("fp32", False, 1.0)):
+        torch.backends.cuda.matmul.allow_tf32 = allow
+        for _ in range(3):
+            torch.matmul(a, b, out=c)
+        torch.cuda.synchronize()
+        best = 1e30
+        for _ in range(10 if allow else 4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b, out=c)
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        out[f"{name}_tflops"] = flops / best / 1e9
+        iters = max(4, int(budget * 1e3 / best))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            torch.matmul(a, b, out=c)
+        e1.record()
+        e1.synchronize()
+        out[f"{name}_tflops_sustained"] = flops * iters / e0.elapsed_time(e1) / 1e9
+    torch.backends.cuda.matmul.allow_tf32 = False
+    del a, b, c
+    torch.cuda.empty_cache()
+    out["how"] = ("cuBLAS via torch.matmul, fp32 8192^3, CUDA events: best of 10 (burst) and back to back for ~3 s "
+                  "(sustained); tf32 = allow_tf32 on, fp32 = off (SGEMM on the CUDA cores)")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons of one GPU, sampled every 200 ms while running."""

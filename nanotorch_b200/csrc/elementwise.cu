@@ -119,8 +119,9 @@ __device__ __forceinline__ float pow_f32(float a, float e, int special) {
   case 5: return 1.0f / a;
   case 6: {
     // a*a is a denormal (fewer than 24 significant bits) below |a| ~ 1.1e-19 while 1/a^2 is still
-    // finite down to |a| ~ 5.4e-20: that sliver takes the double-precision quotient
-    if (fabsf(a) < 1.1e-19f) return (float)(1.0 / ((double)a * (double)a));
+    // finite down to |a| ~ 5.4e-20, and a*a overflows above |a| ~ 1.8e19 while 1/a^2 is still a non-zero
+    // denormal: both slivers take the double-precision quotient
+    if (fabsf(a) < 1.1e-19f || fabsf(a) > 1.8e19f) return (float)(1.0 / ((double)a * (double)a));
     return 1.0f / (a * a);
   }
   default: return (float)pow((double)a, (double)e);

@@ -29,13 +29,19 @@ struct RSum {
   static __device__ __forceinline__ float neutral() { return 0.0f; }
   static __device__ __forceinline__ float combine(float a, float b) { return a + b; }
 };
+// NaN: the reference folds a slice sequentially and a NaN replaces the running extremum, only to be
+// replaced itself by the next element, so its answer depends on where in the slice the NaN sits.  A
+// parallel reduction cannot follow an order-dependent rule; fmaxf / fminf return the other operand when
+// one is NaN, so the extremum of the non-NaN elements comes out whatever the order, and a slice of
+// nothing but NaN gives the neutral element every accumulator starts from.  Of +0 and -0 the maximum is
+// +0 and the minimum -0 (the reference keeps whichever comes first).
 struct RMax {
   static __device__ __forceinline__ float neutral() { return -3.402823466e+38f; }
-  static __device__ __forceinline__ float combine(float a, float b) { return (a > b) ? a : b; }
+  static __device__ __forceinline__ float combine(float a, float b) { return fmaxf(a, b); }
 };
 struct RMin {
   static __device__ __forceinline__ float neutral() { return 3.402823466e+38f; }
-  static __device__ __forceinline__ float combine(float a, float b) { return (a < b) ? a : b; }
+  static __device__ __forceinline__ float combine(float a, float b) { return fminf(a, b); }
 };
 
 template <class Op> __device__ __forceinline__ float warp_reduce(float v) {
