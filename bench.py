@@ -210,6 +210,7 @@ def reference_arm(args, rank: int) -> None:
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    line["cpu_baseline"].update(extrapolated_full_batch(oracle))
     print(json.dumps(line))
 
 
@@ -234,10 +235,29 @@ def cpu_baseline_sample(limit_s: float = 20.0) -> dict:
         O.mlp_step(oracle, params, X, Y, LR, "tanh")
         times.append(time.perf_counter() - t)
     best = min(times)
-    return {"value": batch / best, "unit": "samples/s", "cores": 1, "kind": oracle.kind,
-            "sample": f"best of {len(times)} steps on a batch of {batch} of the 16384 rows through the full "
-                      f"8x4096^2 model (forward+backward+SGD), single thread: the reference's CPU path has no "
-                      f"threading; host has {os.cpu_count()} cores"}
+    out = {"value": batch / best, "unit": "samples/s", "cores": 1, "kind": oracle.kind,
+           "sample": f"best of {len(times)} steps on a batch of {batch} of the 16384 rows through the full "
+                     f"8x4096^2 model (forward+backward+SGD), single thread: the reference's CPU path has no "
+                     f"threading; host has {os.cpu_count()} cores"}
+    out.update(extrapolated_full_batch(oracle))
+    return out
+
+
+def extrapolated_full_batch(oracle, rows: int = 48) -> dict:
+    """One full-size layer product of the step (activations x 4096^2 weights) on the reference's CPU path,
+    timed on `rows` of the 16384 rows; the full-batch step is 23 such products over all rows (the
+    elementwise work is three orders of magnitude smaller), so its rate follows by proportion.  Labelled
+    as extrapolated: nobody ran the ~10-hour step."""
+    A = np.random.default_rng(40).standard_normal((rows, WIDTH)).astype(np.float32)
+    W = np.random.default_rng(31).uniform(-0.04, 0.04, (WIDTH, WIDTH)).astype(np.float32)
+    t = time.perf_counter()
+    oracle.matmul(A, W)
+    dt = time.perf_counter() - t
+    gflops = 2.0 * rows * WIDTH * WIDTH / dt / 1e9
+    step_s = 2.0 * GLOBAL_BATCH * WIDTH * WIDTH * 23 / (gflops * 1e9)
+    return {"full_size_layer_product_gflops": round(gflops, 3), "layer_product_sample": f"{rows} of 16384 rows x 4096 x 4096",
+            "extrapolated_full_batch_value": GLOBAL_BATCH / step_s, "extrapolated_full_batch_seconds_per_step": round(step_s, 1),
+            "extrapolated": True}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -352,7 +372,36 @@ def time_ops(nt, peaks: dict) -> dict:
         av = [t._C_view for t in A[:k]]
         record("pow2.backward", stream_time([lambda i=i: _C.pow_backward(gv[i], av[i], 2.0) for i in range(k)]),
                3 * numel * 4)
-        del A, Nn, Pp, G, saved, gv, av
+        # binary backward: mul' = (x2*g, x1*g), div' = (g/x2, ((-x1)/x2^2)*g): g, x1, x2 -> dx1, dx2 = 5 N floats
+        Bk = copies(dev(host["b"].astype(np.float32)), k)
+        Dk = copies(dev(host["d"].astype(np.float32)), k)
+        bv, dv2 = [t._C_view for t in Bk], [t._C_view for t in Dk]
+        record("mul.backward", stream_time(
+            [lambda i=i: (_C.multiply(bv[i], gv[i]), _C.multiply(av[i], gv[i])) for i in range(k)]), 5 * numel * 4)
+        record("truediv.backward", stream_time(
+            [lambda i=i: (_C.divide(gv[i], dv2[i]), _C.div_backward_x2(gv[i], av[i], dv2[i])) for i in range(k)]), 5 * numel * 4)
+        # one operand seen through a transposed view: its gradient x1*g is written in x2's own (transposed) order
+        bt = [t.T._C_view for t in Bk]
+        record("mul.transposed.backward", stream_time(
+            [lambda i=i: (_C.multiply(bt[i], gv[i]), _C.multiply(av[i], gv[i])) for i in range(k)]), 5 * numel * 4)
+        # row-broadcast operand [N] against [N,N]: dx1 = v*g, dv = column sums of x1*g (the unbroadcast):
+        # g, x1 -> dx1, tmp -> dv.  5 N + (N + C) floats as the survey accounts them
+        vrow = v_.expand(N, N)._C_view
+
+        def mul_bcast_backward(i):
+            dx1 = _C.multiply(vrow, gv[i])
+            tmp = _C.multiply(av[i], gv[i])
+            return dx1, _C.sum(_C.TensorView(tmp, (N, N), (N, 1), 0), [0], F32)
+
+        record("mul.broadcast_row.backward", stream_time([lambda i=i: mul_bcast_backward(i) for i in range(k)]),
+               (6 * numel + N) * 4)
+        record("add.broadcast_row.grad_of_row", stream_time([lambda i=i: _C.sum(gv[i], [0], F32) for i in range(k)]),
+               (numel + N) * 4)
+        # pow through the strided paths
+        at = [t.T._C_view for t in A[:k]]
+        record("pow2.transposed", stream_time([lambda i=i: _C.pow(at[i], 2.0) for i in range(k)]), 2 * numel * 4)
+        record("pow2.broadcast_row", stream_time([lambda: _C.pow(vrow, 2.0)] * 3), (numel + N) * 4)
+        del A, Nn, Pp, G, saved, gv, av, Bk, Dk, bv, dv2, bt, at
 
         # ---- reductions
         M = 8192
@@ -366,14 +415,8 @@ def time_ops(nt, peaks: dict) -> dict:
             record(f"sum.{label}", stream_time([lambda i=i: _C.sum(xv[i], ax, F32) for i in range(k)]), M * M * 4)
             record(f"max.{label}", stream_time([lambda i=i: _C.max(xv[i], ax) for i in range(k)]), M * M * 4)
             record(f"min.{label}", stream_time([lambda i=i: _C.min(xv[i], ax) for i in range(k)]), M * M * 4)
-            n_out = M * M // count[axes]
-            denom = _C.TensorView(_C.full(1, float(count[axes]), F32, CUDA), (n_out,), (0,), 0)
-
-            def mean_call(i):  # MeanOp.forward: sum, then a true division by the count
-                s_ = _C.sum(xv[i], ax, F32)
-                return _C.divide(_C.TensorView(s_, (n_out,), (1,), 0), denom)
-
-            record(f"mean.{label}", stream_time([lambda i=i: mean_call(i) for i in range(k)]), M * M * 4)
+            cnt = count[axes]  # MeanOp.forward: the sum divided by the count where the reduction finishes
+            record(f"mean.{label}", stream_time([lambda i=i: _C.mean_f32(xv[i], ax, cnt) for i in range(k)]), M * M * 4)
         y3v = y3._C_view
         for op, kern in (("sum", lambda v: _C.sum(v, [2], F32)), ("max", lambda v: _C.max(v, [2])),
                          ("min", lambda v: _C.min(v, [2]))):
@@ -398,6 +441,16 @@ def time_ops(nt, peaks: dict) -> dict:
         record("max.backward", stream_time([lambda i=i: _C.extremum_backward(g_full, xv[i], m_full[i], [1])
                                             for i in range(k)], iters=20), 2 * M * M * 4)
         del m1, m_full
+        # max / min backward over the leading dim and over the whole tensor: two launches over x (count the
+        # positions equal to the extremum with integer atomics, then write g * unique-mask), read x + write dx
+        for label, axes, kept in (("dim0", [0], (1, M)), ("full", [0, 1], (1, 1))):
+            for op in ("max", "min"):
+                mm = [getattr(t, op)(tuple(axes)) for t in X]
+                mf = [m.reshape(*kept).expand(M, M)._C_view for m in mm]
+                gk = dev(np.ones(kept, np.float32)).expand(M, M)._C_view
+                record(f"{op}.backward.{label}", stream_time(
+                    [lambda i=i: _C.extremum_backward(gk, xv[i], mf[i], axes) for i in range(k)], iters=20), 2 * M * M * 4)
+                del mm, mf
         # ---- index-array gather / scatter of whole rows by a permutation (read + write = 8 bytes/element)
         perm_view = [dev(r(22).permutation(M).astype(np.int64))._C_view]
         plan = dict(fancy_dims_in_src=[0], fancy_dims_data=perm_view, out_axis_is_fancy=[True, False],
@@ -430,7 +483,8 @@ def time_ops(nt, peaks: dict) -> dict:
                 ms.append(e0.elapsed_ms(e1))
             return statistics.median(ms)
 
-        tf32_peak = peaks["bf16_tflops"] / 2
+        tf32_peak = peaks["tf32_tflops"]      # burst figure: these launches are timed alone
+        fp32_peak = peaks["fp32_tflops"]
         for label, (m, kk, n, bt) in {"4096x4096x4096": (4096, 4096, 4096, 1), "8192x1024x4096": (8192, 1024, 4096, 1),
                                       "32x512x512x512": (512, 512, 512, 32)}.items():
             shape_a = (bt, m, kk) if bt > 1 else (m, kk)
@@ -453,7 +507,10 @@ def time_ops(nt, peaks: dict) -> dict:
                         total, launches = _C.matmul_profile_read()
                         _C.matmul_profile_enable(False)
                         res[which] = {"ms": round(ms, 4), "TFLOP/s": round(flops / ms / 1e9, 2)}
+                        if mode == 0:
+                            res[which]["frac_of_fp32_sgemm_peak"] = round(flops / ms / 1e9 / fp32_peak, 3)
                         if mode == 1:
+                            res[which]["frac_of_tf32_peak"] = round(flops / ms / 1e9 / tf32_peak, 3)
                             kms = total / max(launches, 1)
                             res[which]["gemm_kernel_ms"] = round(kms, 4)
                             res[which]["tensor_TFLOP/s_3_products"] = round(3 * flops / ms / 1e9, 1)
@@ -463,11 +520,80 @@ def time_ops(nt, peaks: dict) -> dict:
                 finally:
                     _C.set_matmul_mode(1)
             del Am, Bm, Gc
+    out["mlp_784_256_10"] = time_config_1(nt)
     out["_notes"] = ("HBM-bound ops: back-to-back launches through the _C boundary over rotating buffer sets larger "
                      "than 4x L2, one event pair around 40 launches; bytes are the reference's mem_bytes() accounting "
                      "(sum/max/min count the input only); matmul: L2 flushed by a 512 MB fill between single timed "
                      "launches, `ms` includes the operand split kernels, gemm_kernel_ms is the tcgen05 kernel alone; "
-                     "tf32 peak taken as measured burst bf16 / 2")
+                     "TF32 and FP32 peaks are cuBLAS rates measured in this run (burst)")
+    return out
+
+
+def time_config_1(nt) -> dict:
+    """configs[0]: Linear(784,256)-ReLU-Linear(256,10), MSE, batch 256, seed-0 init, SGD lr 0.01 -- a step is
+    ~40 small launches, so it is issue-bound: timed eagerly (launches issued from Python) and as one
+    CUDA-graph replay per step."""
+    import nanotorch_b200.nn as nn
+
+    _C = nt._C
+    nt.manual_seed(0)
+    model = nn.Sequential(nn.Linear(784, 256), nn.ReLU(), nn.Linear(256, 10)).to("cuda")
+    X = nt.Tensor.from_numpy(np.random.default_rng(1).standard_normal((256, 784)).astype(np.float32), "cuda")
+    Y = nt.Tensor.from_numpy(np.random.default_rng(2).standard_normal((256, 10)).astype(np.float32), "cuda")
+    opt = nn.GradientDescent(model.parameters(), lr=0.01)
+
+    def step():
+        loss = nt.mean((model(X) - Y) ** 2)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return loss
+
+    for _ in range(10):
+        loss = step()
+    first = float(loss.numpy())
+    steps = 100
+    l0 = _C.launch_count()
+    e0 = _C.Event().record()
+    for _ in range(steps):
+        loss = step()
+    e1 = _C.Event().record()
+    ms_eager = e0.elapsed_ms(e1) / steps
+    launches = (_C.launch_count() - l0) // steps
+    graph = _C.Graph()
+    with graph.capture():
+        gl = step()
+    for _ in range(5):
+        graph.replay()
+    _C.cuda_sync()
+    e0 = _C.Event().record()
+    for _ in range(steps):
+        graph.replay()
+    e1 = _C.Event().record()
+    ms_graph = e0.elapsed_ms(e1) / steps
+    last = float(gl.numpy())
+    graph.close()
+    return {"samples/s_eager": round(256 / ms_eager * 1e3, 1), "samples/s_graph": round(256 / ms_graph * 1e3, 1),
+            "ms_per_step_eager": round(ms_eager, 4), "ms_per_step_graph": round(ms_graph, 4), "launches_per_step": launches,
+            "loss_after_10_steps": first, "loss_after_215_steps": last}
+
+
+def compact_ops(ops: dict) -> dict:
+    """name -> [GB/s, fraction of the measured HBM copy rate] for the HBM-bound rows,
+    name.pass -> [TFLOP/s, fraction] for the matmul rows (3xtf32: of the measured TF32 peak, algorithmic
+    2MNK flops, the 3 tensor products per fp32 product not counted; fp32_simt: of the measured SGEMM rate)."""
+    out = {}
+    for name, row in ops.items():
+        if name.startswith("_"):
+            continue
+        if "GB/s" in row:
+            out[name] = [row["GB/s"], row["frac_of_measured_hbm"]]
+        elif name.startswith("matmul."):
+            for which, r in row.items():
+                frac = r.get("frac_of_tf32_peak", r.get("frac_of_fp32_sgemm_peak"))
+                out[f"{name}.{which}"] = [r["TFLOP/s"], frac]
+        elif name == "mlp_784_256_10":
+            out[name] = row
     return out
 
 
@@ -539,9 +665,10 @@ def reference_cuda_column() -> dict:
     # both gradients multiply by a transposed VIEW and drop to the one-thread-per-output kernel
     ms = best(lambda: m.matmul(va, view(b, (N, N), (1, N))), reps=1)
     out["matmul.4096x4096x4096.grad_a"] = {"ms": round(ms, 3), "TFLOP/s": round(flops / ms / 1e9, 2)}
-    out["_notes"] = ("the reference's generic kernels (no sm_100 path exists in the reference) recompiled with "
-                     "-gencode arch=compute_100,code=sm_100; wall-clock perf_counter + device sync per call")
-    return out
+    compact = {k: v.get("GB/s", v.get("TFLOP/s")) for k, v in out.items()}
+    compact["_units"] = ("GB/s (TFLOP/s for matmul): the reference's own generic CUDA kernels recompiled with "
+                         "-gencode arch=compute_100,code=sm_100, perf_counter + device sync per call, best of 5")
+    return compact
 
 
 def reference_cpu_column(limit_s: float = 90.0) -> dict:
@@ -643,13 +770,56 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    comm = Communicator(rank, world, exchange_id)
+    comm = Communicator(rank, world, exchange_id, timeout_s=300.0)
     peaks = measured_peaks()
+    try:  # the TF32 / FP32 denominators, measured on this GPU before anything else runs (every rank alike)
+        import torch
+
+        torch.cuda.set_device(local_rank)
+        peaks.update(measure_gemm_peaks())
+        peaks["gemm_peaks_source"] = "measured in this run"
+    except Exception as e:  # noqa: BLE001 -- no torch, or no room: fall back to the stated cross-check
+        peaks.update({"tf32_tflops": peaks["bf16_tflops"] / 2, "tf32_tflops_sustained": peaks["bf16_tflops_sustained"] / 2,
+                      "fp32_tflops": 74.0, "fp32_tflops_sustained": 74.0,
+                      "gemm_peaks_source": f"not measured ({type(e).__name__}); TF32 taken as measured bf16 / 2, FP32 as the "
+                                           f"nominal 148 SMs x 128 lanes x 2 x 1.965 GHz"})
     sampler = ClockSampler(local_rank).__enter__()  # runs for the whole benchmark; regions are cut out by time
     lo, hi = shard_bounds(GLOBAL_BATCH, rank, world)
     local = hi - lo
 
+    def all_mean(values):
+        """Mean over ranks of per-rank values (equal shards: the global-batch loss from the shard losses)."""
+        if dist is None:
+            return [float(v) for v in values]
+        import torch
+
+        t = torch.tensor([float(v) for v in values], dtype=torch.float64)
+        dist.all_reduce(t)
+        return (t / world).tolist()
+
+    # ---------------- cross-world parity: 5 steps from the seed-0 state, global-batch loss and a checksum of
+    # the first layer's weights; identical at every N up to the summation order of the gradient exchange
     model = build_model(nt, nn)
+    opt = DataParallelSGD(model.parameters(), LR, comm)
+    Xg = np.random.default_rng(40).standard_normal((GLOBAL_BATCH, WIDTH), dtype=np.float32)
+    Yg = np.random.default_rng(41).standard_normal((GLOBAL_BATCH, WIDTH), dtype=np.float32)
+    Xp, Yp = nt.Tensor.from_numpy(Xg[lo:hi], "cuda"), nt.Tensor.from_numpy(Yg[lo:hi], "cuda")
+    del Xg, Yg
+    parity_losses = []
+    for _ in range(5):
+        loss = nt.mean((model(Xp) - Yp) ** 2)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        parity_losses.append(float(loss.numpy()))
+    global_loss = all_mean(parity_losses)
+    w0 = model.parameters()[0].numpy().astype(np.float64)
+    w0_checksum, w0_abs_checksum = float(w0.sum()), float(np.abs(w0).sum())
+    del Xp, Yp, w0, loss
+    opt.detach()
+    del model, opt
+
+    model = build_model(nt, nn)   # seed 0 again: the timed part starts from the initial state
     opt = DataParallelSGD(model.parameters(), LR, comm)
     # two synthetic global batches (alternated by the end-to-end loop); this rank's rows only
     host = []
@@ -712,6 +882,42 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
     graph_launches = _C.launch_count() - launches0
     last_loss = float(graph_loss.numpy())
     ms_graph = max_over_ranks(ms_graph)
+
+    # ---------------- N > 1: the same captured step without the collectives (everything else alike: buckets,
+    # updates on the side stream, 1/world scale).  The difference to the real step is what the exchange costs:
+    # its exposed tail plus the SMs NCCL takes from the backward GEMMs while it runs.
+    ms_no_exchange = None
+    if world > 1:
+        opt.detach()
+        quiet = Communicator(0, 1, None)
+        opt_q = DataParallelSGD(model.parameters(), LR, quiet)
+        opt_q._grad_scale = 1.0 / world
+
+        def step_q():
+            loss_q = nt.mean((model(Xd[0]) - Yd[0]) ** 2)
+            opt_q.zero_grad()
+            loss_q.backward()
+            opt_q.step()
+            return loss_q
+
+        step_q()
+        gq = _C.Graph()
+        with gq.capture():
+            step_q()
+        for _ in range(args.warmup):
+            gq.replay()
+        barrier()
+        e0 = _C.Event().record()
+        for _ in range(args.steps):
+            gq.replay()
+        e1 = _C.Event().record()
+        ms_no_exchange = max_over_ranks(e0.elapsed_ms(e1)) / args.steps
+        barrier()
+        gq.close()
+        opt_q.detach()
+        for p in model.parameters():   # the real optimizer's hooks again
+            from nanotorch_b200.autograd import leaf_grad_hooks
+            leaf_grad_hooks[id(p)] = opt._on_grad
     use_graph = ms_graph <= ms_eager
     ms_resident = ms_graph if use_graph else ms_eager
     clock_window = (t_graph0, t_graph1) if use_graph else (t_eager0, t_eager1)
@@ -763,10 +969,11 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
     if rank == 0:
         m, k, n = local, WIDTH, WIDTH
-        tensor_flops_per_launch = 3 * 2.0 * m * n * k   # three TF32 products per fp32 product
+        flops_per_launch = 2.0 * m * n * k            # algorithmic: one fp32 multiply-add per (m, n, k)
         avg_ms = gemm_ms / max(gemm_launches, 1)
-        tf32_peak = peaks["bf16_tflops_sustained"] / 2
-        achieved = tensor_flops_per_launch / avg_ms / 1e9 if gemm_launches else None
+        tf32_peak = peaks["tf32_tflops_sustained"]    # the kernel is timed inside a long, power-capped step
+        achieved = flops_per_launch / avg_ms / 1e9 if gemm_launches else None
+        full = local == GLOBAL_BATCH and _C.get_matmul_mode() == 1
         line = {
             "metric": "mlp_train_samples_per_s", "value": value, "unit": "samples/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_resident / args.steps,
@@ -775,35 +982,56 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
             "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_rank_batch": local, "width": WIDTH,
                        "layers": LAYERS, "matmul_mode": "3xTF32 (tcgen05)" if _C.get_matmul_mode() == 1 else "fp32",
                        "parallelism": f"dp{world}", "l2": "inputs larger than L2 (weights 537 MB, activations 268 MB each)",
-                       "final_loss": last_loss,
+                       # cross-world parity: the global-batch loss of the first 5 steps from the seed-0 state and
+                       # the fp64 sum (and sum of magnitudes) of the first layer's weights after them; they agree
+                       # between N = 1, 2, 4, 8 up to the summation order of the gradient exchange (rel 1e-5)
+                       "global_loss": global_loss, "w0_checksum_after_5_steps": w0_checksum,
+                       "w0_abs_checksum_after_5_steps": w0_abs_checksum,
+                       "rank0_local_loss_after_timed_steps": last_loss,
                        "step_issue": "one CUDA-graph replay per step" if use_graph else "eager launches",
                        "ms_per_step_eager": ms_eager / args.steps, "ms_per_step_graph": ms_graph / args.steps,
+                       "value_eager": samples / (ms_eager / 1e3), "value_graph": samples / (ms_graph / 1e3),
+                       "ms_per_step_graph_without_exchange": ms_no_exchange,
+                       "exchange_cost_ms_per_step": (ms_graph / args.steps - ms_no_exchange) if ms_no_exchange else None,
                        "kernels_per_step": launches // args.steps, "graph_replays_timed": graph_launches},
             "e2e": {"value": e2e_value, "unit": "samples/s", "h2d_bytes_per_step": 2 * nbytes * world,
                     "d2h_bytes_per_step": 4 * world, "ms_per_step": ms_e2e / args.steps},
             "gpu_launches": launches,
             "clocks": sampler.summary(*clock_window),
             "roofline": {
-                "kernel": "gemm_3xtf32 (tcgen05.mma kind::tf32, 3 products per fp32 product)",
-                "bound": "tensor", "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s",
-                "frac": (achieved / tf32_peak) if achieved else None,
-                # DRAM bytes per launch from the ncu capture of the step's two GEMM shapes at the full per-GPU
-                # batch (profiles/gemm_3xtf32_step_shapes_dram_traffic.md), weighted 15 : 8 as in one step;
-                # tile re-reads do not scale with the shard, so there is no figure for other shapes
-                "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH if (local == GLOBAL_BATCH and _C.get_matmul_mode() == 1) else None,
-                "traffic_unit": "bytes/launch (dram__bytes_read.sum + dram__bytes_write.sum)",
-                "algorithmic_bytes_per_launch": (15 * 939.5e6 + 8 * 1140.9e6) / 23 if local == GLOBAL_BATCH else None,
-                "peak_source": f"{peaks['source']}: sustained bf16 cuBLAS rate / 2 (TF32 issues at half the bf16 rate; "
-                               f"no TF32 figure is recorded)",
+                "kernel": "gemm_3xtf32 (tcgen05.mma kind::tf32; fp32 product = 3 TF32 products)",
+                "bound": "tensor", "unit": "TFLOP/s",
+                # algorithmic work 2*M*N*K per launch over the average launch time, against the TF32 rate
+                # cuBLAS sustains on this GPU; a 3xTF32 product issues three tensor-core products per
+                # multiply-add, so 1/3 is the ceiling of this fraction
+                "achieved": achieved, "peak": tf32_peak, "frac": (achieved / tf32_peak) if achieved else None,
+                "frac_ceiling_3_products": 1.0 / 3.0,
+                "tensor_pipe": {"achieved": 3 * achieved if achieved else None, "peak": tf32_peak,
+                                "frac": (3 * achieved / tf32_peak) if achieved else None,
+                                "what": "TF32 tensor FLOP/s actually issued (3 per algorithmic one) over the same peak"},
+                "peak_source": f"{peaks['gemm_peaks_source']}: cuBLAS TF32 8192^3 sustained {peaks['tf32_tflops_sustained']:.0f}, "
+                               f"burst {peaks['tf32_tflops']:.0f}; cross-check bf16/2 from MEASURED_PEAKS.json "
+                               f"({peaks['source']}) = {peaks['bf16_tflops_sustained'] / 2:.0f} sustained / "
+                               f"{peaks['bf16_tflops'] / 2:.0f} burst; cuBLAS SGEMM (no tensor cores) {peaks['fp32_tflops']:.0f}",
                 "launches": gemm_launches, "avg_launch_ms": avg_ms,
-                "algorithmic_fp32_tflops": (2.0 * m * n * k / avg_ms / 1e9) if gemm_launches else None,
+                "flops_per_launch": flops_per_launch,
+                # DRAM bytes of one launch, from the ncu capture of the step's two GEMM shapes at the full
+                # per-GPU batch, weighted 15 : 8 as in one step; none for other shapes (re-reads do not scale)
+                "traffic": GEMM_TRAFFIC_BYTES_PER_LAUNCH if full else None,
+                "traffic_unit": "bytes/launch (dram__bytes_read.sum + dram__bytes_write.sum)",
+                "traffic_source": GEMM_TRAFFIC_SOURCE if full else None,
+                "algorithmic_bytes_per_launch": GEMM_ALGORITHMIC_BYTES_PER_LAUNCH if full else None,
             },
         }
         if world == 1 and not args.no_ops:
-            line["ops"] = time_ops(nt, peaks)
+            ops = time_ops(nt, peaks)
+            line["roofline"]["per_op"] = compact_ops(ops)
+            line["roofline"]["hbm_peak_gbs"] = peaks["hbm_gbs"]
             line["cpu_baseline"] = cpu_baseline_sample()
-        if world == 1 and args.ref_cuda:
-            line["reference_cuda"] = reference_cuda_column()
+            if not args.no_ref_cuda:
+                line["roofline"]["reference_cuda_kernels_on_this_gpu"] = reference_cuda_column()
+            if args.ops_detail:
+                Path(args.ops_detail).write_text(json.dumps(ops, indent=1))
         print(json.dumps(line), flush=True)
     barrier()
     # graphs that captured collectives go before the communicator they use
@@ -819,9 +1047,14 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
 # (15 * 2760.6 MB + 8 * 2998.1 MB) / 23: forward / input-gradient shape and weight-gradient shape of the step
 GEMM_TRAFFIC_BYTES_PER_LAUNCH = 2.843e9
+GEMM_TRAFFIC_SOURCE = "profiles/gemm_3xtf32_step_shapes_dram_traffic.md (ncu --set full, one launch per shape)"
+# fp32 operands read once, hi/lo planes written and read once, output written once, same 15 : 8 weighting
+GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (15 * 939.5e6 + 8 * 1140.9e6) / 23
 
 PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
-                 "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows", "gemm_step_shapes")
+                 "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows", "gemm_step_shapes",
+                 "sgemm4096", "max_backward8192_dim0", "sum_short_rows", "sgd4096", "cast4096", "scatter8192_ordered", "add_sliced_3d",
+                 "mean8192_dim1")
 
 
 def profile_case(name: str, launches: int = 3) -> None:
@@ -866,6 +1099,40 @@ def profile_case(name: str, launches: int = 3) -> None:
         fn = lambda: _C.gather_from_axes(  # noqa: E731
             x=x._C_view, new_shape=[8192, 8192], fancy_dims_in_src=[0], fancy_dims_data=[perm._C_view],
             out_axis_is_fancy=[True, False], out_axis_target=[0, 1], checked=True)
+    elif name == "sgemm4096":  # the exact-FP32 SIMT kernel (matmul mode 0)
+        a, b = dev(r(30).uniform(-1, 1, (4096, 4096))), dev(r(31).uniform(-1, 1, (4096, 4096)))
+        _C.set_matmul_mode(0)
+        launches = 2
+        fn = lambda: _C.matmul(a._C_view, b._C_view)  # noqa: E731
+    elif name == "max_backward8192_dim0":  # two launches over x: extremum_count_*, extremum_apply*
+        x = dev(r(20).standard_normal((8192, 8192)))
+        m = x.max((0,)).reshape(1, 8192).expand(8192, 8192)
+        g = dev(np.ones((8192,))).reshape(1, 8192).expand(8192, 8192)
+        fn = lambda: _C.extremum_backward(g._C_view, x._C_view, m._C_view, [0])  # noqa: E731
+    elif name == "sum_short_rows":  # one warp per row (reduce_rows_warp)
+        x = dev(r(20).standard_normal((262144, 256)))
+        fn = lambda: _C.sum(x._C_view, [1], nt.float32)  # noqa: E731
+    elif name == "mean8192_dim1":  # the sum kernel with the division in its finish
+        x = dev(r(20).standard_normal((8192, 8192)))
+        fn = lambda: _C.mean_f32(x._C_view, [1], 8192)  # noqa: E731
+    elif name == "sgd4096":
+        p_, g_ = dev(r(31).uniform(-0.04, 0.04, (4096, 4096))), dev(r(32).standard_normal((4096, 4096)))
+        fn = lambda: _C.sgd_update(p_._C_view, g_._C_view, 1e-3, 0.125)  # noqa: E731
+    elif name == "cast4096":
+        x = dev(r(14).standard_normal((4096, 4096)) * 100)
+        fn = lambda: _C.cast(x.storage, nt.int32)  # noqa: E731
+    elif name == "scatter8192_ordered":
+        x = dev(r(20).standard_normal((8192, 8192)))
+        tgt = x.clone()
+        perm = nt.Tensor.from_numpy(r(22).permutation(8192).astype(np.int64), "cuda")
+        fn = lambda: _C.scatter_to_axes(  # noqa: E731
+            src=x._C_view, out=tgt._C_view, fancy_dims_in_src=[0], fancy_dims_data=[perm._C_view],
+            out_axis_is_fancy=[True, False], out_axis_target=[0, 1], checked=True, unique=False)
+    elif name == "add_sliced_3d":  # a view that does not collapse: the general index-math path of ew_strided
+        a = dev(r(10).uniform(-1, 1, (64, 520, 520)))
+        b = dev(r(11).uniform(-1, 1, (64, 520, 520)))
+        av, bv = a[:, 3:515, 1:513], b[:, 5:517, 7:519]
+        fn = lambda: _C.add(av._C_view, bv._C_view)  # noqa: E731
     elif name.startswith("sum8192"):
         x = dev(r(20).standard_normal((8192, 8192)))
         axes = {"sum8192_dim0": [0], "sum8192_dim1": [1], "sum8192_full": [0, 1]}[name]
@@ -886,8 +1153,9 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-ops", action="store_true", help="skip the per-op sweep and the CPU baseline sample")
-    ap.add_argument("--ref-cuda", action="store_true",
-                    help="also time the reference's own CUDA kernels (oracle/_ref) on this GPU for a comparison column")
+    ap.add_argument("--no-ref-cuda", action="store_true",
+                    help="skip the comparison column: the reference's own CUDA kernels (oracle/_ref) on this GPU")
+    ap.add_argument("--ops-detail", default=None, help="write the full per-op table (all fields) to this JSON file")
     ap.add_argument("--ref-cpu", action="store_true",
                     help="time the reference's CPU kernels on the per-op configurations (needs no GPU), print JSON, exit")
     ap.add_argument("--case", default=None, help=f"run one small case for a profiler capture and exit: {PROFILE_CASES}")

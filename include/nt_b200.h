@@ -183,6 +183,11 @@ int nt_pow(const nt_view *x, const nt_scalar *exponent, nt_storage **out);
 
 /* ------------------------------------------------------------------ reductions (src/cpp/ops/reduction_ops.cu:225-259) */
 int nt_sum(const nt_view *x, const int64_t *axes, int32_t n_axes, int dtype, nt_storage **out);
+/* MeanOp's two kernels (sum, then a true division by the element count; autograd/ops_reduction.py:112-127)
+ * in one launch for Float32 views: the rounded fp32 sum is divided by `count` where the reduction finishes,
+ * same bits as nt_sum followed by nt_divide.  *out stays NULL when the view takes none of the single-launch
+ * fp32 reduction kernels; the caller then composes the two steps. */
+int nt_mean_f32(const nt_view *x, const int64_t *axes, int32_t n_axes, float count, nt_storage **out);
 int nt_max(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out);
 int nt_min(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out);
 int nt_argmax(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out); /* Int64 output */

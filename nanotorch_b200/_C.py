@@ -368,6 +368,15 @@ def sum(x: TensorView, axis: Sequence[int], dtype: Dtype) -> Storage:  # noqa: A
     return _ret_storage(_lib.nt_sum, _vref(x), arr, C.c_int32(n), int(_dtype(dtype)))
 
 
+def mean_f32(x: TensorView, axis: Sequence[int], count: int) -> "Storage | None":
+    """Float32 sum divided by `count` in the launch that finishes the sum (the bits of sum followed by
+    divide); None when the view takes none of the single-launch reduction kernels."""
+    arr, n = _axes(axis)
+    out = C.c_void_p()
+    _check(_lib.nt_mean_f32(_vref(x), arr, C.c_int32(n), C.c_float(float(count)), C.byref(out)))
+    return Storage._wrap(out.value) if out.value else None
+
+
 def _reduction(name):
     fn = getattr(_lib, "nt_" + name)
 

@@ -524,8 +524,18 @@ class MeanOp(_ReductionOp):
         if dtype < Dtype.Float32:
             raise TypeError("Cannot take mean of integer tensor, cast to fp.")
         self._axis = normalize_axes(axis, x)
-        total = x.sum(axis=self._axis, keepdim=keepdim, dtype=dtype)
         self._orig_shape = x.shape
+        if _fused(x) and dtype == Dtype.Float32 and not x.is_empty:
+            # sum and the true division by the count in one launch (same bits as the two steps below);
+            # the count is exact in fp32 up to 2^24 elements per slice, beyond that the composed form runs
+            new_shape = _reduced_shapes(x, self._axis, keepdim)
+            denom = x.numel // max(1, math.prod(new_shape))
+            if denom <= (1 << 24):
+                fused = _C.mean_f32(x._C_view, self._axis, denom)
+                if fused is not None:
+                    self._denom = denom
+                    return Tensor._new_contiguous(fused, new_shape)
+        total = x.sum(axis=self._axis, keepdim=keepdim, dtype=dtype)
         self._denom = x.numel // total.numel
         return total / self._denom  # true division by the count, not a multiply by its reciprocal
 

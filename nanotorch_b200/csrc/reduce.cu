@@ -70,7 +70,9 @@ __device__ __forceinline__ int64_t keep_offset(const KeepIndex &k, int64_t lin) 
 template <class Op>
 __global__ void __launch_bounds__(256) reduce_rows(const float *__restrict__ in, float *__restrict__ out,
                                                    float *__restrict__ partials, unsigned *__restrict__ tickets,
-                                                   KeepIndex keep, int64_t L, int S, int64_t chunk) {
+                                                   KeepIndex keep, int64_t L, int S, int64_t chunk, float divisor) {
+  // divisor != 0: the finished value is divided by it (one IEEE division of the rounded fp32 result:
+  // the bits of a sum kernel followed by a divide kernel -- MeanOp's two steps in one launch)
   __shared__ float warp_part[8];
   __shared__ bool is_last;
   const int64_t row = blockIdx.x / S;
@@ -120,7 +122,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const float *__restrict__ in,
     v = warp_reduce<Op>(v);
   }
   if (S == 1) {
-    if (threadIdx.x == 0) out[row] = v;
+    if (threadIdx.x == 0) out[row] = (divisor != 0.0f) ? v / divisor : v;
     return;
   }
   // single-pass grid finish
@@ -143,7 +145,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const float *__restrict__ in,
     acc = (lane < 8) ? warp_part[lane] : Op::neutral();
     acc = warp_reduce<Op>(acc);
     if (lane == 0) {
-      out[row] = acc;
+      out[row] = (divisor != 0.0f) ? acc / divisor : acc;
       tickets[row] = 0; // leave the counter ready for the next launch
     }
   }
@@ -152,7 +154,7 @@ __global__ void __launch_bounds__(256) reduce_rows(const float *__restrict__ in,
 // Short rows: one warp per row, eight rows per CTA.
 template <class Op>
 __global__ void __launch_bounds__(256) reduce_rows_warp(const float *__restrict__ in, float *__restrict__ out,
-                                                        KeepIndex keep, int64_t n_rows, int64_t L) {
+                                                        KeepIndex keep, int64_t n_rows, int64_t L, float divisor) {
   const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (row >= n_rows) return;
   const int lane = threadIdx.x & 31;
@@ -170,7 +172,7 @@ __global__ void __launch_bounds__(256) reduce_rows_warp(const float *__restrict_
     for (int64_t j = lane; j < L; j += 32) a = Op::combine(a, p[j]);
   }
   a = warp_reduce<Op>(a);
-  if (lane == 0) out[row] = a;
+  if (lane == 0) out[row] = (divisor != 0.0f) ? a / divisor : a;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -181,7 +183,7 @@ template <class Op, int VEC>
 __global__ void __launch_bounds__(256) reduce_cols(const float *__restrict__ in, float *__restrict__ out,
                                                    float *__restrict__ partials, unsigned *__restrict__ tickets,
                                                    KeepIndex keep_outer, int64_t R, int64_t C, int64_t sR,
-                                                   int64_t rows_per_split) {
+                                                   int64_t rows_per_split, float divisor) {
   constexpr int TW = 32 * VEC; // tile width in columns
   __shared__ float part[8][TW];
   __shared__ bool is_last;
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(256) reduce_cols(const float *__restrict__ in,
   }
   const int64_t out_base = z * C;
   if (S == 1) {
-    if (owner) out[out_base + c] = v;
+    if (owner) out[out_base + c] = (divisor != 0.0f) ? v / divisor : v;
     return;
   }
   if (owner) partials[(z * S + split) * C + c] = v;
@@ -257,7 +259,7 @@ __global__ void __launch_bounds__(256) reduce_cols(const float *__restrict__ in,
   if (owner) {
     float a = Op::neutral();
     for (int s = 0; s < S; ++s) a = Op::combine(a, __ldcg(partials + (z * S + s) * C + c));
-    out[out_base + c] = a;
+    out[out_base + c] = (divisor != 0.0f) ? a / divisor : a;
   }
   if (threadIdx.x == 0) tickets[tile_id] = 0;
 }
@@ -394,7 +396,7 @@ static Plan make_plan(const nt_view *x, const int64_t *axes, int32_t n_axes) {
   return pl;
 }
 
-template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, float *out) {
+template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, float *out, float divisor = 0.0f) {
   const float *in = static_cast<const float *>(x->storage->data) + x->offset;
   cudaStream_t st = stream();
   const int sms = sm_count();
@@ -406,7 +408,7 @@ template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, f
     if (L < 1024 && n_rows >= 64) {
       int64_t blocks = ceil_div(n_rows, 8);
       if (blocks > 0x7fffffffLL) return false;
-      reduce_rows_warp<Op><<<unsigned(blocks), 256, 0, st>>>(in, out, pl.keep, n_rows, L);
+      reduce_rows_warp<Op><<<unsigned(blocks), 256, 0, st>>>(in, out, pl.keep, n_rows, L, divisor);
       check_launch("reduce_rows_warp");
       return true;
     }
@@ -425,7 +427,7 @@ template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, f
       partials = static_cast<float *>(device_alloc(size_t(n_rows * S) * sizeof(float), &rounded));
       tk = tickets(n_rows);
     }
-    reduce_rows<Op><<<unsigned(n_rows * S), 256, 0, st>>>(in, out, partials, tk, pl.keep, L, int(S), chunk);
+    reduce_rows<Op><<<unsigned(n_rows * S), 256, 0, st>>>(in, out, partials, tk, pl.keep, L, int(S), chunk, divisor);
     if (partials) device_free(partials, rounded); // stream-ordered reuse: later work queues behind this launch
     check_launch("reduce_rows");
     return true;
@@ -461,9 +463,9 @@ template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, f
     }
     dim3 grid{unsigned(tiles), unsigned(S), unsigned(Z)};
     if (vec)
-      reduce_cols<Op, 4><<<grid, 256, 0, st>>>(in, out, partials, tk, outer, R, C, sR, rows_per_split);
+      reduce_cols<Op, 4><<<grid, 256, 0, st>>>(in, out, partials, tk, outer, R, C, sR, rows_per_split, divisor);
     else
-      reduce_cols<Op, 1><<<grid, 256, 0, st>>>(in, out, partials, tk, outer, R, C, sR, rows_per_split);
+      reduce_cols<Op, 1><<<grid, 256, 0, st>>>(in, out, partials, tk, outer, R, C, sR, rows_per_split, divisor);
     if (partials) device_free(partials, rounded);
     check_launch("reduce_cols");
     return true;
@@ -901,7 +903,7 @@ int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float 
   if (row_len < 1024 && n_rows >= 64) {
     int64_t blocks = ceil_div(n_rows, 8);
     if (blocks > 0x7fffffffLL) fail_invalid("nt_sum_rows_noalloc: too many rows for one launch.");
-    reduce_rows_warp<RSum><<<unsigned(blocks), 256, 0, st>>>(in, out, keep, n_rows, row_len);
+    reduce_rows_warp<RSum><<<unsigned(blocks), 256, 0, st>>>(in, out, keep, n_rows, row_len, 0.0f);
     check_launch("reduce_rows_warp");
     return NT_OK;
   }
@@ -920,7 +922,7 @@ int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float 
   if (S > 1) // tickets must start at zero whatever the previous call left behind
     NT_CUDA_CHECK(cudaMemsetAsync(scratch->tickets, 0, size_t(n_rows) * sizeof(unsigned), st));
   reduce_rows<RSum><<<unsigned(n_rows * S), 256, 0, st>>>(in, out, scratch->partials, scratch->tickets, keep, row_len,
-                                                        int(S), chunk);
+                                                        int(S), chunk, 0.0f);
   check_launch("reduce_rows");
   NT_API_END
 }
@@ -928,6 +930,19 @@ int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float 
 int nt_sum(const nt_view *x, const int64_t *axes, int32_t n_axes, int dtype, nt_storage **out) {
   NT_API_BEGIN
   *out = reduce_impl<GSum, RSum>(x, axes, n_axes, dtype, "sum");
+  NT_API_END
+}
+int nt_mean_f32(const nt_view *x, const int64_t *axes, int32_t n_axes, float count, nt_storage **out) {
+  NT_API_BEGIN
+  *out = nullptr;
+  check_view(x, "mean");
+  require_cuda(x, "mean");
+  if (n_axes < 0 || n_axes > x->ndim) fail_runtime("mean: bad axis list.");
+  if (x->storage->dtype != NT_FLOAT32 || count == 0.0f) return NT_OK;
+  Plan pl = make_plan(x, axes, n_axes);
+  if (pl.n_keep == 0 || pl.n_drop == 0) return NT_OK;
+  StorageRef o(storage_new(pl.n_keep, NT_FLOAT32, NT_CUDA));
+  if (try_fast_f32<RSum>(x, pl, static_cast<float *>(o->data), count)) *out = o.release();
   NT_API_END
 }
 int nt_max(const nt_view *x, const int64_t *axes, int32_t n_axes, nt_storage **out) {
