@@ -772,17 +772,6 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
     comm = Communicator(rank, world, exchange_id, timeout_s=300.0)
     peaks = measured_peaks()
-    try:  # the TF32 / FP32 denominators, measured on this GPU before anything else runs (every rank alike)
-        import torch
-
-        torch.cuda.set_device(local_rank)
-        peaks.update(measure_gemm_peaks())
-        peaks["gemm_peaks_source"] = "measured in this run"
-    except Exception as e:  # noqa: BLE001 -- no torch, or no room: fall back to the stated cross-check
-        peaks.update({"tf32_tflops": peaks["bf16_tflops"] / 2, "tf32_tflops_sustained": peaks["bf16_tflops_sustained"] / 2,
-                      "fp32_tflops": 74.0, "fp32_tflops_sustained": 74.0,
-                      "gemm_peaks_source": f"not measured ({type(e).__name__}); TF32 taken as measured bf16 / 2, FP32 as the "
-                                           f"nominal 148 SMs x 128 lanes x 2 x 1.965 GHz"})
     sampler = ClockSampler(local_rank).__enter__()  # runs for the whole benchmark; regions are cut out by time
     lo, hi = shard_bounds(GLOBAL_BATCH, rank, world)
     local = hi - lo
@@ -963,6 +952,18 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
     barrier()
     ms_e2e = max_over_ranks(ms_e2e)
 
+    try:  # the TF32 / FP32 denominators, measured on this GPU after the timed regions (every rank alike), so
+    # that seconds of full-power cuBLAS work cannot warm the part up under the headline numbers
+        import torch
+
+        torch.cuda.set_device(local_rank)
+        peaks.update(measure_gemm_peaks())
+        peaks["gemm_peaks_source"] = "measured in this run"
+    except Exception as e:  # noqa: BLE001 -- no torch, or no room: fall back to the stated cross-check
+        peaks.update({"tf32_tflops": peaks["bf16_tflops"] / 2, "tf32_tflops_sustained": peaks["bf16_tflops_sustained"] / 2,
+                      "fp32_tflops": 74.0, "fp32_tflops_sustained": 74.0,
+                      "gemm_peaks_source": f"not measured ({type(e).__name__}); TF32 taken as measured bf16 / 2, FP32 as the "
+                                           f"nominal 148 SMs x 128 lanes x 2 x 1.965 GHz"})
     samples = GLOBAL_BATCH * args.steps
     value = samples / (ms_resident / 1e3)
     e2e_value = samples / (ms_e2e / 1e3)

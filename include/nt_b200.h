@@ -229,6 +229,12 @@ int nt_linear(const nt_view *x, const nt_view *w, const nt_view *bias, nt_storag
  *      round-toward-zero accumulate then shows as a bias of 1e-5 of max|C| at K = 4096, 4e-5 at 16384. */
 int nt_set_matmul_mode(int mode);
 int nt_get_matmul_mode(void);
+/* In modes 1 and 3 a product of at most this many multiply-adds (batch*M*N*K, default 2^26) takes the
+ * exact FP32 kernel of mode 0 instead: below that the tensor-core path's two operand-split launches cost
+ * more than they save, and small products keep the accuracy of the reference's CUDA kernels.  0 sends
+ * every fp32 product to the tensor cores. */
+int nt_set_matmul_tc_min_macs(int64_t macs);
+int64_t nt_get_matmul_tc_min_macs(void);
 
 /* ------------------------------------------------------------------ in-place (src/cpp/ops/inplace_ops.cu:75-79); bump the version */
 int nt_add_inplace(const nt_view *out, const nt_view *other);

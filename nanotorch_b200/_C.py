@@ -605,6 +605,18 @@ def set_matmul_mode(mode: int) -> None:
     _check(_lib.nt_set_matmul_mode(int(mode)))
 
 
+_lib.nt_get_matmul_tc_min_macs.restype = C.c_int64
+
+
+def set_matmul_tc_min_macs(macs: int) -> None:
+    """Products of at most this many multiply-adds take the exact FP32 kernel in modes 1 and 3 (default 2**26)."""
+    _check(_lib.nt_set_matmul_tc_min_macs(C.c_int64(int(macs))))
+
+
+def get_matmul_tc_min_macs() -> int:
+    return _lib.nt_get_matmul_tc_min_macs()
+
+
 def get_matmul_mode() -> int:
     return _lib.nt_get_matmul_mode()
 

@@ -25,6 +25,7 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
 void gemm_tc_set_promoted(bool on);
 
 static std::atomic<int> g_matmul_mode{1};
+static std::atomic<int64_t> g_tc_min_macs{int64_t(1) << 26}; // batch*M*N*K at or below this: exact FP32 kernel
 
 constexpr int BM = 128, BN = 128, BK = 16;
 
@@ -304,6 +305,13 @@ int nt_set_matmul_mode(int mode) {
   NT_API_END
 }
 int nt_get_matmul_mode(void) { return g_matmul_mode.load(); }
+int nt_set_matmul_tc_min_macs(int64_t macs) {
+  NT_API_BEGIN
+  if (macs < 0) fail_invalid("nt_set_matmul_tc_min_macs: negative.");
+  g_tc_min_macs.store(macs);
+  NT_API_END
+}
+int64_t nt_get_matmul_tc_min_macs(void) { return g_tc_min_macs.load(); }
 
 int nt_wait_probe(void) {
   NT_API_BEGIN
@@ -356,7 +364,10 @@ static nt_storage *matmul_impl(const nt_view *x1, const nt_view *x2, const nt_vi
     g.batch = bi;
     const int mode = g_matmul_mode.load();
     bool done = false;
-    if ((mode == 1 || mode == 3) && K > 0) {
+    // Products too small to fill the tensor cores (three launches against one) take the exact FP32 kernel:
+    // faster there, and the full fp32 accuracy of the reference's own CUDA kernels on the small cases.
+    const bool big_enough = double(nbatch) * double(M) * double(N) * double(K) > double(g_tc_min_macs.load());
+    if ((mode == 1 || mode == 3) && K > 0 && big_enough) {
       // the tensor-core path takes a single (collapsed) batch stride per operand
       int64_t a_sb = 0, b_sb = 0;
       bool single = true;
