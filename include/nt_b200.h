@@ -233,6 +233,18 @@ int nt_get_matmul_mode(void);
  * exact FP32 kernel of mode 0 instead: below that the tensor-core path's two operand-split launches cost
  * more than they save, and small products keep the accuracy of the reference's CUDA kernels.  0 sends
  * every fp32 product to the tensor cores. */
+/* Mode 1 splits each fp32 operand into two TF32 planes (hi, lo) before the product.  natural != 0 (default):
+ * the planes keep the operand's own row-major order whichever of its two matrix dims has unit stride -- the
+ * kernel reads them K-major or MN-major -- so no operand is transposed on the way.  cached != 0 (default): the
+ * planes are remembered per storage and view and reused until that storage is written again through any
+ * entry point of this library (in-place ops, sgd_update, uploads, copy_view, scatter, all-reduce): an
+ * activation is split once for the forward product and the weight-gradient product, a gradient once for
+ * its two products; nt_sgd_update / nt_comm_sgd_update re-split a weight that has been an operand right
+ * behind the update.  A captured graph keeps the hit-or-miss decisions of its capture: do not write to a
+ * parameter from outside the graph between replays.  Writes through nt_storage_data() pointers are not
+ * seen.  nt_matmul_split_stats: operand-split launches and cache hits since load. */
+int nt_set_matmul_operand_planes(int natural, int cached);
+int nt_matmul_split_stats(uint64_t *split_launches, uint64_t *cache_hits);
 int nt_set_matmul_tc_min_macs(int64_t macs);
 int64_t nt_get_matmul_tc_min_macs(void);
 

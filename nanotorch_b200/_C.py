@@ -617,6 +617,19 @@ def get_matmul_tc_min_macs() -> int:
     return _lib.nt_get_matmul_tc_min_macs()
 
 
+def set_matmul_operand_planes(natural: bool = True, cached: bool = True) -> None:
+    """Mode-1 operand planes: `natural` keeps the source's row-major order (no transposing split, the kernel
+    reads either major); `cached` remembers them per storage and view until the storage is written again."""
+    _check(_lib.nt_set_matmul_operand_planes(int(bool(natural)), int(bool(cached))))
+
+
+def matmul_split_stats() -> tuple[int, int]:
+    """(operand-split launches, operand-plane cache hits) since load."""
+    a, b = C.c_uint64(0), C.c_uint64(0)
+    _check(_lib.nt_matmul_split_stats(C.byref(a), C.byref(b)))
+    return a.value, b.value
+
+
 def get_matmul_mode() -> int:
     return _lib.nt_get_matmul_mode()
 

@@ -232,6 +232,7 @@ int nt_comm_allreduce_sum(nt_storage *s) {
     comm_after_compute(); // the collective may start once everything enqueued on the compute stream so far has run
   }
   nccl_check(n.AllReduce(s->data, s->data, size_t(s->n), ncclFloat32, ncclSum, n.comm, comm_stream()), "ncclAllReduce");
+  storage_touch(s);
   count_launch();
   NT_API_END
 }

@@ -287,6 +287,7 @@ template <template <class> class F, bool ARITH_ONLY> static void inplace_impl(co
   if constexpr (ARITH_ONLY) dispatch_arith(out->storage->dtype, run);
   else dispatch_all(out->storage->dtype, run);
   out->storage->version += 1;
+  storage_touch(out->storage);
 }
 
 // fp32-only fused entry: every view must be Float32 on Cuda with the shape of `shape_of`.
@@ -488,6 +489,7 @@ int nt_copy_view(const nt_view *src, const nt_view *out) {
     const nt_view *views[2] = {out, src};
     ew_launch<IdentityF<T>, 1>(IdentityF<T>{}, views);
   });
+  storage_touch(out->storage);
   // no version bump: the reference's copy_view leaves Storage::version alone (only the *_inplace
   // family bumps it, src/cpp/ops/inplace_ops.cu:60)
   NT_API_END
@@ -565,6 +567,8 @@ int nt_sgd_update(const nt_view *param, const nt_view *grad, float lr, float gra
   const nt_view *views[3] = {param, param, grad};
   ew_launch<SgdF, 2>(SgdF{lr, grad_scale, grad_scale != 1.0f}, views);
   param->storage->version += 1;
+  storage_touch(param->storage);
+  gemm_tc_refresh(param->storage); // a weight that has been a matmul operand: its planes follow the update
   NT_API_END
 }
 

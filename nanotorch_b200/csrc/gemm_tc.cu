@@ -28,6 +28,9 @@
 // kernels, for fp32 operands.
 #include <cuda.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "nt_core.cuh"
 
 namespace ntb {
@@ -178,6 +181,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
                ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -194,16 +202,34 @@ __device__ __forceinline__ uint64_t umma_desc_sw64(uint32_t smem_addr) {
   d |= uint64_t(4) << 61;
   return d;
 }
+// MN-major operand tile of 32-bit values.  The one shared-memory layout the tensor core accepts for it is
+// the 128-byte swizzle with 32-byte atoms: a row of 128 bytes holds 32 consecutive values of the m (or n)
+// index for one k, the 32-byte chunks of a row are permuted by the row number modulo 4, so 4 rows (512
+// bytes) form one swizzle atom -- what the tensor map mode SWIZZLE_128B_ATOM_32B writes.  An instruction
+// of kind::tf32 consumes 8 values of k = two atoms, `sbo` bytes apart; the atoms of the next 32 m (or n)
+// values lie `lbo` bytes further.  Same field positions as above; layout type 1.
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr & 0x3FFFF) >> 4);
+  d |= uint64_t((lbo >> 4) & 0x3FFF) << 16;
+  d |= uint64_t((sbo >> 4) & 0x3FFF) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(1) << 61;
+  return d;
+}
 // Instruction descriptor, kind::tf32: D format F32 (1) in bits [4,6); A and B format TF32 (2) in [7,10) and
 // [10,13); A and B K-major (0) in bits 15, 16; N >> 3 in [17,23); M >> 4 in [24,29).
 constexpr uint32_t TC_IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (uint32_t(TC_BN >> 3) << 17) | (uint32_t(TC_BM >> 4) << 24);
 
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+__device__ __forceinline__ void umma_tf32_idesc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n\t.reg .pred p;\n\t"
                "setp.ne.b32 p, %4, 0;\n\t"
                "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(accumulate)
+               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
                : "memory");
+}
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  umma_tf32_idesc(tmem_d, adesc, bdesc, TC_IDESC, accumulate);
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -219,6 +245,7 @@ struct TcArgs {
   int64_t bias_stride;
   int *error_flag;
   long long wait_limit; // SM clocks a pipeline wait may take before the kernel gives up
+  uint32_t mn_lbo, mn_sbo; // byte offsets of the MN-major descriptors (see umma_desc_mn_sw128)
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -410,8 +437,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
       : "memory");
 }
 
+// A_MN / B_MN: the operand's planes keep the source tensor's own row-major order and the contraction
+// index k runs down the rows (A seen as its transpose, B as stored): the tile arrives through a 4-D
+// tensor map {32 m|n, k, (m|n)/32, plane} into 128-byte-swizzle / 32-byte-atom rows and the instruction
+// reads it MN-major.  Otherwise k runs along the rows (K-major): 3-D map, 64-byte swizzle.  Every combination is
+// one instantiation, so forward (A K-major, B MN-major), input gradient (both K-major) and weight
+// gradient (both MN-major) all read planes that were split once, without a transpose.
+template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(320, 1)
 gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
+  constexpr uint32_t IDESC = TC_IDESC | (A_MN ? (1u << 15) : 0u) | (B_MN ? (1u << 16) : 0u);
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = smem_base + TC_STAGES * TC_STAGE_BYTES;
@@ -458,10 +493,20 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         const uint32_t st = smem_base + s * TC_STAGE_BYTES;
         mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
         const int k = kb * TC_BK;
-        tma_load_3d(st, &map_a, full0 + 8 * s, k, m0, b);
-        tma_load_3d(st + TC_A_PLANE_BYTES, &map_a, full0 + 8 * s, k, m0, g.batch + b);
-        tma_load_3d(st + 2 * TC_A_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, b);
-        tma_load_3d(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, g.batch + b);
+        if constexpr (A_MN) {
+          tma_load_4d(st, &map_a, full0 + 8 * s, 0, k, m0 >> 5, b);
+          tma_load_4d(st + TC_A_PLANE_BYTES, &map_a, full0 + 8 * s, 0, k, m0 >> 5, g.batch + b);
+        } else {
+          tma_load_3d(st, &map_a, full0 + 8 * s, k, m0, b);
+          tma_load_3d(st + TC_A_PLANE_BYTES, &map_a, full0 + 8 * s, k, m0, g.batch + b);
+        }
+        if constexpr (B_MN) {
+          tma_load_4d(st + 2 * TC_A_PLANE_BYTES, &map_b, full0 + 8 * s, 0, k, n0 >> 5, b);
+          tma_load_4d(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES, &map_b, full0 + 8 * s, 0, k, n0 >> 5, g.batch + b);
+        } else {
+          tma_load_3d(st + 2 * TC_A_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, b);
+          tma_load_3d(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES, &map_b, full0 + 8 * s, k, n0, g.batch + b);
+        }
         if (++s == TC_STAGES) {
           s = 0;
           phase ^= 1;
@@ -495,15 +540,21 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
           const uint32_t st = smem_base + s * TC_STAGE_BYTES;
 #pragma unroll
           for (int ks = 0; ks < TC_BK / TC_UMMA_K; ++ks) {
-            const uint32_t koff = ks * TC_UMMA_K * 4;
-            const uint64_t a_hi = umma_desc_sw64(st + koff);
-            const uint64_t a_lo = umma_desc_sw64(st + TC_A_PLANE_BYTES + koff);
-            const uint64_t b_hi = umma_desc_sw64(st + 2 * TC_A_PLANE_BYTES + koff);
-            const uint64_t b_lo = umma_desc_sw64(st + 2 * TC_A_PLANE_BYTES + TC_B_PLANE_BYTES + koff);
+            // one instruction consumes 8 values of k: 32 bytes along a K-major row, 8 rows of 128 bytes
+            // of an MN-major tile
+            const uint32_t a_off = A_MN ? ks * 1024u : ks * TC_UMMA_K * 4u;
+            const uint32_t b_off = B_MN ? ks * 1024u : ks * TC_UMMA_K * 4u;
+            const uint32_t pa = st + a_off, pb = st + 2 * TC_A_PLANE_BYTES + b_off;
+            const uint64_t a_hi = A_MN ? umma_desc_mn_sw128(pa, g.mn_lbo, g.mn_sbo) : umma_desc_sw64(pa);
+            const uint64_t a_lo = A_MN ? umma_desc_mn_sw128(pa + TC_A_PLANE_BYTES, g.mn_lbo, g.mn_sbo)
+                                       : umma_desc_sw64(pa + TC_A_PLANE_BYTES);
+            const uint64_t b_hi = B_MN ? umma_desc_mn_sw128(pb, g.mn_lbo, g.mn_sbo) : umma_desc_sw64(pb);
+            const uint64_t b_lo = B_MN ? umma_desc_mn_sw128(pb + TC_B_PLANE_BYTES, g.mn_lbo, g.mn_sbo)
+                                       : umma_desc_sw64(pb + TC_B_PLANE_BYTES);
             // small terms first, the large one last
-            umma_tf32(d, a_hi, b_lo, first ? 0u : 1u);
-            umma_tf32(d, a_lo, b_hi, 1);
-            umma_tf32(d, a_hi, b_hi, 1);
+            umma_tf32_idesc(d, a_hi, b_lo, IDESC, first ? 0u : 1u);
+            umma_tf32_idesc(d, a_lo, b_hi, IDESC, 1);
+            umma_tf32_idesc(d, a_hi, b_hi, IDESC, 1);
             first = false;
           }
           umma_commit(empty0 + 8 * s);
@@ -670,7 +721,7 @@ void gemm_tc_prepare() {
   static bool configured = false;
   if (!configured) {
     NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(TC_SMEM_BYTES)));
-    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_promoted_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_promoted_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        int(TC_SMEM_BYTES)));
     configured = true;
   }
@@ -695,8 +746,273 @@ void gemm_tc_wait_probe() {
   check_launch("wait_probe_kernel");
 }
 
+// ---------------------------------------------------------------------------------------------
+// Natural-layout operand planes and their cache.
+//
+// An operand whose matrix has unit stride along one of its two dims is split in the source's own row-major
+// order: rows = the strided dim, columns = the unit-stride dim, hi and lo planes [2][batch][R][Cp] with
+// Cp = C rounded up to 32 and the padding zeroed.  No transpose on the way: whether the contraction index
+// is the column (K-major) or the row (MN-major) of the planes is told to the GEMM kernel instead.  The
+// planes are remembered per storage and view geometry: an activation is split once for the forward
+// product and found again by the weight-gradient product, a gradient once for both of its products, a
+// weight once per update.  An entry is valid while the storage's mutation counter and the epoch (see
+// gemm_tc_new_epoch) are the ones it was written under; a stale entry is re-split into the same buffer.
+struct NatSplitArgs {
+  const float *src;
+  float *hi, *lo;
+  int64_t R, C, Cp, s_r, s_b;
+  int vec; // rows of the source may be read 128 bits at a time
+};
+
+__global__ void __launch_bounds__(256) split_planes(NatSplitArgs a) {
+  const int64_t c = (int64_t(blockIdx.x) * 64 + (threadIdx.x & 63)) * 4;
+  if (c >= a.Cp) return;
+  const int64_t r0 = int64_t(blockIdx.y) * 16 + (threadIdx.x >> 6);
+  const float *src = a.src + int64_t(blockIdx.z) * a.s_b;
+  const int64_t plane = int64_t(blockIdx.z) * a.R * a.Cp;
+  float4 x[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { // rows r0, r0 + 4, r0 + 8, r0 + 12: all loads issued before the first use
+    const int64_t r = r0 + 4 * i;
+    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (r < a.R) {
+      const float *p = src + r * a.s_r + c;
+      if (a.vec && c + 3 < a.C) {
+        x[i] = __ldg(reinterpret_cast<const float4 *>(p));
+      } else {
+        if (c + 0 < a.C) x[i].x = p[0];
+        if (c + 1 < a.C) x[i].y = p[1];
+        if (c + 2 < a.C) x[i].z = p[2];
+        if (c + 3 < a.C) x[i].w = p[3];
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t r = r0 + 4 * i;
+    if (r < a.R) {
+      const int64_t idx = plane + r * a.Cp + c;
+      const float h0 = split_hi(x[i].x), h1 = split_hi(x[i].y), h2 = split_hi(x[i].z), h3 = split_hi(x[i].w);
+      *reinterpret_cast<float4 *>(a.hi + idx) = make_float4(h0, h1, h2, h3);
+      *reinterpret_cast<float4 *>(a.lo + idx) =
+          make_float4(split_lo(x[i].x, h0), split_lo(x[i].y, h1), split_lo(x[i].z, h2), split_lo(x[i].w, h3));
+    }
+  }
+}
+
+struct PlaneEntry {
+  int64_t offset, batch, s_b, R, C, s_r; // the view: element offset, batch count / stride, rows, columns, row stride
+  int64_t Cp;
+  float *planes;
+  size_t rounded;
+  uint64_t mutation, epoch;
+};
+static std::mutex g_plane_mu;
+static std::unordered_map<nt_storage *, std::vector<PlaneEntry>> g_plane_cache;
+static uint64_t g_plane_epoch = 1;
+static std::atomic<int> g_operand_cache{1};
+static std::atomic<uint64_t> g_split_launches{0}, g_split_hits{0};
+
+static void run_split(const nt_storage *s, const PlaneEntry &e) {
+  NatSplitArgs a{};
+  a.src = static_cast<const float *>(s->data) + e.offset;
+  a.hi = e.planes;
+  a.lo = e.planes + e.batch * e.R * e.Cp;
+  a.R = e.R;
+  a.C = e.C;
+  a.Cp = e.Cp;
+  a.s_r = e.s_r;
+  a.s_b = e.s_b;
+  a.vec = ((reinterpret_cast<uintptr_t>(a.src) & 15) == 0 && e.s_r % 4 == 0 && e.s_b % 4 == 0) ? 1 : 0;
+  dim3 grid{unsigned(ceil_div(e.Cp, 256)), unsigned(ceil_div(e.R, 16)), unsigned(e.batch)};
+  split_planes<<<grid, 256, 0, stream()>>>(a);
+  check_launch("split_planes");
+  g_split_launches.fetch_add(1, std::memory_order_relaxed);
+}
+
+// Planes of the view (rows R, columns C with unit stride, row stride s_r, `batch` matrices s_b apart) of
+// storage s.  `owned` is set when the caller must free them after its launch (cache off).
+static float *natural_planes(nt_storage *s, int64_t offset, int64_t batch, int64_t s_b, int64_t R, int64_t C, int64_t s_r,
+                             int64_t *Cp_out, size_t *owned_rounded) {
+  const int64_t Cp = ceil_div(C, 32) * 32;
+  *Cp_out = Cp;
+  *owned_rounded = 0;
+  const size_t bytes = size_t(2 * batch * R * Cp) * 4;
+  if (!g_operand_cache.load()) {
+    PlaneEntry e{offset, batch, s_b, R, C, s_r, Cp, nullptr, 0, 0, 0};
+    e.planes = static_cast<float *>(device_alloc(bytes, &e.rounded));
+    *owned_rounded = e.rounded;
+    run_split(s, e);
+    return e.planes;
+  }
+  std::lock_guard<std::mutex> lk(g_plane_mu);
+  auto &list = g_plane_cache[s];
+  for (PlaneEntry &e : list) {
+    if (e.offset == offset && e.batch == batch && e.s_b == s_b && e.R == R && e.C == C && e.s_r == s_r) {
+      if (e.mutation == s->mutation && e.epoch == g_plane_epoch) {
+        g_split_hits.fetch_add(1, std::memory_order_relaxed);
+        return e.planes;
+      }
+      e.mutation = s->mutation;
+      e.epoch = g_plane_epoch;
+      run_split(s, e); // same buffer: a captured graph that reads it keeps reading the right place
+      return e.planes;
+    }
+  }
+  PlaneEntry e{offset, batch, s_b, R, C, s_r, Cp, nullptr, 0, s->mutation, g_plane_epoch};
+  e.planes = static_cast<float *>(device_alloc(bytes, &e.rounded));
+  run_split(s, e);
+  list.push_back(e);
+  return e.planes;
+}
+
+void gemm_tc_forget(nt_storage *s) {
+  std::vector<PlaneEntry> dead;
+  {
+    std::lock_guard<std::mutex> lk(g_plane_mu);
+    if (g_plane_cache.empty()) return;
+    auto it = g_plane_cache.find(s);
+    if (it == g_plane_cache.end()) return;
+    dead.swap(it->second);
+    g_plane_cache.erase(it);
+  }
+  for (PlaneEntry &e : dead) device_free(e.planes, e.rounded);
+}
+
+void gemm_tc_refresh(nt_storage *s) {
+  std::lock_guard<std::mutex> lk(g_plane_mu);
+  if (g_plane_cache.empty()) return;
+  auto it = g_plane_cache.find(s);
+  if (it == g_plane_cache.end()) return;
+  for (PlaneEntry &e : it->second) {
+    e.mutation = s->mutation;
+    e.epoch = g_plane_epoch;
+    run_split(s, e);
+  }
+}
+
+void gemm_tc_new_epoch() {
+  std::lock_guard<std::mutex> lk(g_plane_mu);
+  g_plane_epoch += 1;
+}
+
+void gemm_tc_set_operand_cache(bool on) { g_operand_cache.store(on ? 1 : 0); }
+void gemm_tc_split_stats(uint64_t *launches, uint64_t *hits) {
+  *launches = g_split_launches.load();
+  *hits = g_split_hits.load();
+}
+
+// 4-D map over MN-major planes [2 * batch][R = k][Cp]: {32 m|n, k, (m|n) / 32, plane}; box = 32 x 16 x box_mn/32.
+static CUtensorMap make_map_mn(float *planes, int64_t rows_k, int64_t Cp, int64_t batch2, uint32_t box_mn) {
+  CUtensorMap m;
+  cuuint64_t dims[4] = {32, cuuint64_t(rows_k), cuuint64_t(Cp / 32), cuuint64_t(batch2)};
+  cuuint64_t strides[3] = {cuuint64_t(Cp) * 4, 128, cuuint64_t(rows_k) * cuuint64_t(Cp) * 4};
+  cuuint32_t box[4] = {32, TC_BK, box_mn / 32, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult rc = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, planes, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) fail_runtime("cuTensorMapEncodeTiled (MN-major planes) failed with code " + std::to_string(int(rc)));
+  return m;
+}
+// 3-D map over K-major planes [2 * batch][R = m|n][Cp], k extent K (reads past it are zero filled).
+static CUtensorMap make_map_k(float *planes, int64_t rows, int64_t K, int64_t Cp, int64_t batch2, uint32_t box_rows) {
+  CUtensorMap m;
+  cuuint64_t dims[3] = {cuuint64_t(K), cuuint64_t(rows), cuuint64_t(batch2)};
+  cuuint64_t strides[2] = {cuuint64_t(Cp) * 4, cuuint64_t(rows) * cuuint64_t(Cp) * 4};
+  cuuint32_t box[3] = {TC_BK, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = encode_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, planes, dims, strides, box, estr,
+                            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS) fail_runtime("cuTensorMapEncodeTiled (K-major planes) failed with code " + std::to_string(int(rc)));
+  return m;
+}
+
 static std::atomic<int> g_promoted{1};
 void gemm_tc_set_promoted(bool on) { g_promoted.store(on ? 1 : 0); }
+
+// MN-major tiles as the 4-D map lays them down: [32-wide m|n chunk][16 k rows][128 bytes]
+constexpr uint32_t TC_MN_LBO = TC_BK * 128; // next 32 values of m|n
+constexpr uint32_t TC_MN_SBO = 4 * 128;     // next swizzle atom (4 rows of k)
+
+template <bool A_MN, bool B_MN>
+static void launch_promoted(const CUtensorMap &ma, const CUtensorMap &mb, const TcArgs &g, dim3 grid) {
+  static bool configured = false;
+  if (!configured) {
+    NT_CUDA_CHECK(cudaFuncSetAttribute(gemm_3xtf32_promoted_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       int(TC_SMEM_BYTES)));
+    configured = true;
+  }
+  gemm_3xtf32_promoted_kernel<A_MN, B_MN><<<grid, 320, TC_SMEM_BYTES, stream()>>>(ma, mb, g);
+}
+
+// How an operand matrix [P][Q] (strides s_p, s_q) is laid out: unit stride along Q, along P, or neither.
+static int unit_dim(int64_t P, int64_t Q, int64_t s_p, int64_t s_q) {
+  if (s_q == 1 || Q == 1) return 1; // rows = P, columns = Q
+  if (s_p == 1 || P == 1) return 0; // rows = Q, columns = P
+  return -1;
+}
+
+// The promoted-accumulation kernel over natural-layout planes.  Returns false when an operand has no
+// unit-stride matrix dim (the caller then takes the transposing split below).
+bool gemm_3xtf32_natural(nt_storage *sa, int64_t a_off, nt_storage *sb, int64_t b_off, float *C, int64_t batch, int64_t M,
+                         int64_t N, int64_t K, int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk,
+                         int64_t b_sn, const float *bias, int64_t bias_stride, bool *bias_done) {
+  if (bias_done) *bias_done = false;
+  if (!g_promoted.load()) return false;
+  if (batch < 1 || batch > 32767 || M < 1 || N < 1 || K < 1) return false;
+  if (ceil_div(M, TC_BM) > 65535 || ceil_div(N, TC_BN) > 0x7fffffff) return false;
+  if (M >= (int64_t(1) << 31) || N >= (int64_t(1) << 31) || K >= (int64_t(1) << 31)) return false;
+  const int ua = unit_dim(M, K, a_sm, a_sk), ub = unit_dim(K, N, b_sk, b_sn);
+  if (ua < 0 || ub < 0) return false;
+  if (a_sm < 0 || a_sk < 0 || b_sk < 0 || b_sn < 0 || a_sb < 0 || b_sb < 0) return false;
+  const bool a_mn = (ua == 0), b_mn = (ub == 1); // A: columns = m; B: columns = n
+  // natural rows / columns / row stride of each operand
+  const int64_t aR = a_mn ? K : M, aC = a_mn ? M : K, a_sr = a_mn ? a_sk : a_sm;
+  const int64_t bR = b_mn ? K : N, bC = b_mn ? N : K, b_sr = b_mn ? b_sk : b_sn;
+  if (ceil_div(aR, 16) > 65535 || ceil_div(bR, 16) > 65535) return false; // grid.y of split_planes
+  gemm_tc_prepare();
+  int64_t aCp = 0, bCp = 0;
+  size_t a_owned = 0, b_owned = 0;
+  float *pa = natural_planes(sa, a_off, batch, batch > 1 ? a_sb : 0, aR, aC, a_sr, &aCp, &a_owned);
+  float *pb = nullptr;
+  try {
+    pb = natural_planes(sb, b_off, batch, batch > 1 ? b_sb : 0, bR, bC, b_sr, &bCp, &b_owned);
+    CUtensorMap map_a = a_mn ? make_map_mn(pa, aR, aCp, 2 * batch, TC_BM) : make_map_k(pa, aR, K, aCp, 2 * batch, TC_BM);
+    CUtensorMap map_b = b_mn ? make_map_mn(pb, bR, bCp, 2 * batch, TC_BN) : make_map_k(pb, bR, K, bCp, 2 * batch, TC_BN);
+    TcArgs g{};
+    g.C = C;
+    g.M = M;
+    g.N = N;
+    g.num_kb = int32_t(ceil_div(K, TC_BK));
+    g.batch = int32_t(batch);
+    g.c_vec = (N % 4 == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) ? 1 : 0;
+    g.error_flag = error_flag_ptr();
+    g.wait_limit = wait_limit_clocks();
+    g.mn_lbo = TC_MN_LBO;
+    g.mn_sbo = TC_MN_SBO;
+    g.bias = bias;
+    g.bias_stride = bias ? bias_stride : 0;
+    if (bias && bias_done) *bias_done = true;
+    dim3 grid{unsigned(ceil_div(N, TC_BN)), unsigned(ceil_div(M, TC_BM)), unsigned(batch)};
+    matmul_profile_begin();
+    if (a_mn && b_mn) launch_promoted<true, true>(map_a, map_b, g, grid);
+    else if (a_mn) launch_promoted<true, false>(map_a, map_b, g, grid);
+    else if (b_mn) launch_promoted<false, true>(map_a, map_b, g, grid);
+    else launch_promoted<false, false>(map_a, map_b, g, grid);
+    matmul_profile_end();
+    check_launch("gemm_3xtf32_promoted_kernel");
+  } catch (...) {
+    if (a_owned) device_free(pa, a_owned);
+    if (b_owned && pb) device_free(pb, b_owned);
+    throw;
+  }
+  if (a_owned) device_free(pa, a_owned);
+  if (b_owned) device_free(pb, b_owned);
+  return true;
+}
+
 
 // `bias` (N values, element stride bias_stride) is added in the epilogue of the promoted kernel only;
 // *bias_done tells the caller whether it was.
@@ -737,7 +1053,7 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
     dim3 grid{unsigned(ceil_div(N, TC_BN)), unsigned(ceil_div(M, TC_BM)), unsigned(batch)};
     matmul_profile_begin();
     if (g_promoted.load())
-      gemm_3xtf32_promoted_kernel<<<grid, 320, TC_SMEM_BYTES, stream()>>>(map_a, map_b, g);
+      gemm_3xtf32_promoted_kernel<false, false><<<grid, 320, TC_SMEM_BYTES, stream()>>>(map_a, map_b, g);
     else
       gemm_3xtf32_kernel<<<grid, 192, TC_SMEM_BYTES, stream()>>>(map_a, map_b, g);
     matmul_profile_end();

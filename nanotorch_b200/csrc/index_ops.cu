@@ -368,6 +368,7 @@ int nt_scatter_to_axes(const nt_view *src, const nt_view *out, const int64_t *fa
       launch_width<3>(pl, pl.lin_base, to, scratch + span);
     }
   }
+  storage_touch(out->storage);
   NT_API_END
 }
 

@@ -23,6 +23,13 @@ bool gemm_3xtf32(const float *A, const float *B, float *C, int64_t batch, int64_
                  int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk, int64_t b_sn,
                  const float *bias, int64_t bias_stride, bool *bias_done);
 void gemm_tc_set_promoted(bool on);
+// mode 1 over natural-layout, cached operand planes; false when an operand has no unit-stride matrix dim
+bool gemm_3xtf32_natural(nt_storage *sa, int64_t a_off, nt_storage *sb, int64_t b_off, float *C, int64_t batch, int64_t M,
+                         int64_t N, int64_t K, int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk,
+                         int64_t b_sn, const float *bias, int64_t bias_stride, bool *bias_done);
+void gemm_tc_set_operand_cache(bool on);
+void gemm_tc_split_stats(uint64_t *launches, uint64_t *hits);
+static std::atomic<int> g_natural_planes{1};
 
 static std::atomic<int> g_matmul_mode{1};
 static std::atomic<int64_t> g_tc_min_macs{int64_t(1) << 26}; // batch*M*N*K at or below this: exact FP32 kernel
@@ -313,6 +320,17 @@ int nt_set_matmul_tc_min_macs(int64_t macs) {
 }
 int64_t nt_get_matmul_tc_min_macs(void) { return g_tc_min_macs.load(); }
 
+int nt_set_matmul_operand_planes(int natural, int cached) {
+  NT_API_BEGIN
+  g_natural_planes.store(natural ? 1 : 0);
+  gemm_tc_set_operand_cache(cached != 0);
+  NT_API_END
+}
+int nt_matmul_split_stats(uint64_t *split_launches, uint64_t *cache_hits) {
+  NT_API_BEGIN
+  gemm_tc_split_stats(split_launches, cache_hits);
+  NT_API_END
+}
 int nt_wait_probe(void) {
   NT_API_BEGIN
   gemm_tc_wait_probe();
@@ -384,7 +402,10 @@ static nt_storage *matmul_impl(const nt_view *x1, const nt_view *x2, const nt_vi
         b_sb = bi.b_strides[bi.ndim - 1];
       }
       const float *bp = bias ? static_cast<const float *>(bias->storage->data) + bias->offset : nullptr;
-      if (single)
+      if (single && mode == 1 && g_natural_planes.load())
+        done = gemm_3xtf32_natural(x1->storage, x1->offset, x2->storage, x2->offset, g.C, nbatch, M, N, K, a_sb, a_sm,
+                                   a_sk, b_sb, b_sk, b_sn, bp, bias ? bias->strides[0] : 0, &bias_done);
+      if (single && !done)
         done = gemm_3xtf32(g.A, g.B, g.C, nbatch, M, N, K, a_sb, a_sm, a_sk, b_sb, b_sk, b_sn, bp,
                            bias ? bias->strides[0] : 0, &bias_done);
     }

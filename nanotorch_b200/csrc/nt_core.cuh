@@ -145,7 +145,9 @@ struct nt_storage {
   int dtype = NT_FLOAT32;
   int device = NT_CPU;
   bool pinned = false;
-  uint64_t version = 0;
+  uint64_t version = 0;  // the reference's counter: bumped by the in-place ops only
+  uint64_t mutation = 0; // bumped by EVERY entry point that writes into an existing storage (in-place ops,
+                         // uploads, copy_view, scatter, all-reduce): what cached derived data is checked against
 };
 
 namespace ntb {
@@ -153,6 +155,15 @@ namespace ntb {
 nt_storage *storage_new(int64_t n, int dtype, int device);
 inline void storage_retain(nt_storage *s) { s->refs.fetch_add(1, std::memory_order_relaxed); }
 void storage_release(nt_storage *s);
+inline void storage_touch(nt_storage *s) { s->mutation += 1; }
+// Cached operand planes of the tensor-core GEMM (gemm_tc.cu) die with the storage they were split from.
+void gemm_tc_forget(nt_storage *s);
+// Re-split, on the current stream(), every cached plane set of `s` (called right after a parameter
+// update, so that the next forward pass finds its operand ready).
+void gemm_tc_refresh(nt_storage *s);
+// Cached planes written by work that was only captured, or overwritten by a graph replay behind the
+// host's back, must not be trusted by later eager calls: a new epoch invalidates all of them.
+void gemm_tc_new_epoch();
 
 // RAII holder used while an entry point builds its result.
 struct StorageRef {

@@ -339,6 +339,7 @@ nt_storage *storage_new(int64_t n, int dtype, int device) {
 void storage_release(nt_storage *s) {
   if (!s) return;
   if (s->refs.fetch_sub(1, std::memory_order_acq_rel) == 1) {
+    if (s->device == NT_CUDA) gemm_tc_forget(s);
     if (s->device == NT_CUDA)
       device_free(s->data, s->rounded);
     else
@@ -706,6 +707,7 @@ int nt_graph_end_capture(int graph_id) {
   std::lock_guard<std::mutex> lk(r.mu);
   if (r.capturing != graph_id || graph_id == 0) fail_runtime("nt_graph_end_capture: not the graph being captured.");
   r.capturing = 0;
+  gemm_tc_new_epoch(); // what the captured calls "computed" does not exist on the device yet
   cudaGraph_t graph = nullptr;
   cudaError_t e = cudaStreamEndCapture(r.compute, &graph);
   if (e != cudaSuccess || !graph) {
@@ -729,6 +731,7 @@ int nt_graph_launch(int graph_id) {
   auto it = r.graph_exec.find(graph_id);
   if (it == r.graph_exec.end()) fail_invalid("nt_graph_launch: unknown graph.");
   NT_CUDA_CHECK(cudaGraphLaunch(it->second, st));
+  gemm_tc_new_epoch(); // the replay rewrites storages behind the host's counters
   count_launch();
   NT_API_END
 }
@@ -750,6 +753,7 @@ int nt_storage_upload_async(nt_storage *dst, const void *host_src, int64_t nbyte
   NT_CUDA_CHECK(cudaEventRecord(r.copy_gate, st));
   NT_CUDA_CHECK(cudaStreamWaitEvent(r.copy, r.copy_gate, 0));
   if (nbytes) NT_CUDA_CHECK(cudaMemcpyAsync(dst->data, host_src, size_t(nbytes), cudaMemcpyHostToDevice, r.copy));
+  storage_touch(dst);
   NT_API_END
 }
 int nt_upload_fence(void) {
@@ -869,6 +873,7 @@ int nt_storage_upload(nt_storage *dst, const void *host_src, int64_t nbytes) {
     NT_CUDA_CHECK(cudaMemcpyAsync(dst->data, host_src, size_t(nbytes), cudaMemcpyHostToDevice, st));
     NT_CUDA_CHECK(cudaStreamSynchronize(st));
   }
+  storage_touch(dst);
   NT_API_END
 }
 

@@ -272,3 +272,112 @@ def test_small_products_take_the_exact_kernel_by_default(nt):
         _C.set_matmul_tc_min_macs(0)
     assert_bit_exact(routed, exact, "default routing of a small product")
     assert np.abs(tensor_core - exact).max() <= 2e-6 * (np.abs(a.numpy()) @ np.abs(b.numpy())).max()
+
+
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(256, 512, 64), (384, 520, 200), (130, 70, 1000), (1, 300, 257), (513, 1, 96)])
+def test_every_operand_major_of_the_tensor_core_kernel(nt, shape):
+    """The 3xTF32 kernel reads each operand's planes K-major or MN-major, whichever the operand's own row-major
+    order makes it: all four combinations, ragged extents included, give the same bits (the planes hold the
+    same values, only their walk differs) and are within 2e-6 (|A||B|) of the fp64 product."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    A, B = rng.uniform(-1, 1, (M, K)).astype(np.float32), rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    bound = np.abs(A).astype(np.float64) @ np.abs(B).astype(np.float64)
+    tA, tB = dev(nt, A), dev(nt, B)
+    tAt, tBt = dev(nt, np.ascontiguousarray(A.T)), dev(nt, np.ascontiguousarray(B.T))
+    outs = [(a @ b).numpy() for a, b in ((tA, tB), (tA, tBt.T), (tAt.T, tB), (tAt.T, tBt.T))]
+    for got in outs:
+        assert_scaled(got, ref, bound, 2e-6, f"{shape}")
+        assert_bit_exact(got, outs[0], "same bits whatever the operand order")
+
+
+def test_operand_plane_cache_follows_every_write(nt):
+    """Cached operand planes are dropped by anything that writes the storage they came from: an in-place op,
+    a setitem (copy_view), an upload, an SGD update, a graph replay; and they are found again when nothing
+    was written (the second product of an unchanged operand launches no split)."""
+    _C = nt._C
+    rng = np.random.default_rng(17)
+    x_np = rng.standard_normal((300, 200)).astype(np.float32)
+    w_np = rng.standard_normal((200, 260)).astype(np.float32)
+    x, w = dev(nt, x_np), dev(nt, w_np)
+
+    def check(what):
+        got = (x @ w).numpy()
+        ref = x.numpy().astype(np.float64) @ w.numpy().astype(np.float64)
+        bound = np.abs(x.numpy()).astype(np.float64) @ np.abs(w.numpy()).astype(np.float64)
+        assert_scaled(got, ref, bound, 2e-6, what)
+
+    check("first use")
+    s0, h0 = _C.matmul_split_stats()
+    check("second use")
+    s1, h1 = _C.matmul_split_stats()
+    assert s1 == s0 and h1 == h0 + 2, "an unchanged operand is not split again"
+    with nt.no_grad():
+        x += 1.5
+    check("after an in-place add")
+    x[5:9, ::2] = dev(nt, np.full((4, 100), 7.0, np.float32))
+    check("after a setitem")
+    fresh = rng.standard_normal((300, 200)).astype(np.float32)
+    x.storage.upload(fresh.ctypes.data, fresh.nbytes)
+    check("after an upload into the same storage")
+    g = dev(nt, rng.standard_normal((200, 260)).astype(np.float32))
+    s2, _ = _C.matmul_split_stats()
+    _C.sgd_update(w._C_view, g._C_view, 0.5, 1.0)
+    s3, h3 = _C.matmul_split_stats()
+    assert s3 == s2 + 1, "the update re-splits the weight's planes behind itself"
+    check("after an SGD update")
+    assert _C.matmul_split_stats()[1] == h3 + 2, "and the next product finds both operands ready"
+    # a graph replay rewrites storages behind the host's counters: eager calls must not trust old planes
+    y = dev(nt, np.zeros((300, 200), np.float32))
+    graph = _C.Graph()
+    with graph.capture():
+        with nt.no_grad():
+            x += 1.0
+    graph.replay()
+    graph.replay()
+    check("after graph replays that modified an operand")
+    graph.close()
+    _C.set_matmul_operand_planes(True, False)
+    try:
+        s4, h4 = _C.matmul_split_stats()
+        check("cache off")
+        assert _C.matmul_split_stats() == (s4 + 2, h4)
+    finally:
+        _C.set_matmul_operand_planes(True, True)
+    _C.set_matmul_operand_planes(False, False)
+    try:
+        check("transposing split (natural planes off)")
+    finally:
+        _C.set_matmul_operand_planes(True, True)
+
+
+def test_a_training_step_splits_each_tensor_once(nt):
+    """Linear -> Tanh -> Linear -> Tanh -> Linear with 3xTF32 products: 8 products per step (3 forward, 3 weight
+    gradients, 2 input gradients) over 3 inputs, 3 weights and 3 output gradients: with natural-layout cached
+    planes that is 9 operand splits per step instead of 16, and the SGD update re-splits the weights itself."""
+    import nanotorch_b200.nn as nn
+
+    _C = nt._C
+    nt.manual_seed(0)
+    model = nn.Sequential(nn.Linear(256, 384), nn.Tanh(), nn.Linear(384, 384), nn.Tanh(), nn.Linear(384, 128)).to("cuda")
+    X = dev(nt, np.random.default_rng(1).standard_normal((512, 256)).astype(np.float32))
+    Y = dev(nt, np.random.default_rng(2).standard_normal((512, 128)).astype(np.float32))
+    opt = nn.GradientDescent(model.parameters(), lr=1e-2)
+
+    def step():
+        loss = nt.mean((model(X) - Y) ** 2)
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return loss
+
+    step()
+    s0, h0 = _C.matmul_split_stats()
+    step()
+    s1, h1 = _C.matmul_split_stats()
+    # X is unchanged (hit), the 2 hidden activations and 3 gradients are new (5 splits), the weights were
+    # re-split by the previous update (hits) and are re-split by this one (3 splits)
+    assert s1 - s0 == 8, s1 - s0
+    assert h1 - h0 == 16 - 5, h1 - h0
