@@ -1055,7 +1055,7 @@ GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (15 * 939.5e6 + 8 * 1140.9e6) / 23
 PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
                  "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows", "gemm_step_shapes",
                  "sgemm4096", "max_backward8192_dim0", "sum_short_rows", "sgd4096", "cast4096", "scatter8192_ordered", "add_sliced_3d",
-                 "mean8192_dim1")
+                 "mean8192_dim1", "mlp_step_16384", "mlp_step_2048")
 
 
 def profile_case(name: str, launches: int = 3) -> None:
@@ -1100,6 +1100,26 @@ def profile_case(name: str, launches: int = 3) -> None:
         fn = lambda: _C.gather_from_axes(  # noqa: E731
             x=x._C_view, new_shape=[8192, 8192], fancy_dims_in_src=[0], fancy_dims_data=[perm._C_view],
             out_axis_is_fancy=[True, False], out_axis_target=[0, 1], checked=True)
+    elif name in ("mlp_step_16384", "mlp_step_2048"):
+        # the benchmark's training step at the 1-GPU batch and at the per-rank batch of the 8-GPU run
+        # (one rank, no collective): two warm-up steps, then `launches` steps for the profiler's launch list
+        import nanotorch_b200.nn as nn
+        from nanotorch_b200.dp import Communicator, DataParallelSGD
+
+        rows = int(name.rsplit("_", 1)[1])
+        model = build_model(nt, nn)
+        opt = DataParallelSGD(model.parameters(), LR, Communicator(0, 1, None))
+        X, Y = dev(r(40).standard_normal((rows, WIDTH))), dev(r(41).standard_normal((rows, WIDTH)))
+        launches = 1
+
+        def fn():
+            loss = nt.mean((model(X) - Y) ** 2)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            return loss
+
+        fn()
     elif name == "sgemm4096":  # the exact-FP32 SIMT kernel (matmul mode 0)
         a, b = dev(r(30).uniform(-1, 1, (4096, 4096))), dev(r(31).uniform(-1, 1, (4096, 4096)))
         _C.set_matmul_mode(0)

@@ -244,6 +244,11 @@ int nt_get_matmul_mode(void);
  * parameter from outside the graph between replays.  Writes through nt_storage_data() pointers are not
  * seen.  nt_matmul_split_stats: operand-split launches and cache hits since load. */
 int nt_set_matmul_operand_planes(int natural, int cached);
+/* on != 0 (default): nt_tanh and nt_tanh_backward, when their result is a dense 2-D Float32 matrix of at
+ * least 2^20 elements whose rows are whole 128-byte lines, also write the result's TF32 planes and register
+ * them in the cache above -- an activation or its gradient is then never read back by an operand split.
+ * Costs 8 extra bytes written per element if no product ever uses the result. */
+int nt_set_producer_planes(int on);
 int nt_matmul_split_stats(uint64_t *split_launches, uint64_t *cache_hits);
 int nt_set_matmul_tc_min_macs(int64_t macs);
 int64_t nt_get_matmul_tc_min_macs(void);
@@ -308,8 +313,9 @@ int nt_sgd_update(const nt_view *param, const nt_view *grad, float lr, float gra
 #define NT_COMM_ID_BYTES 128
 int nt_comm_unique_id(uint8_t id[NT_COMM_ID_BYTES]);
 /* The rendezvous waits for every rank; it is bounded: NT_ERR_RUNTIME after NT_COMM_TIMEOUT_MS (default
- * 300 000) or the explicit limit, instead of hanging on a rank that never joins.  NT_NCCL_MAX_CTAS in the
- * environment caps the CTAs NCCL may use per collective (they share the SMs with the backward GEMMs). */
+ * 300 000) or the explicit limit, instead of hanging on a rank that never joins.  NCCL is capped at 16 CTAs
+ * per collective (they take whole SMs from the backward GEMMs they overlap); NT_NCCL_MAX_CTAS in the
+ * environment overrides that, 0 leaves the choice to NCCL. */
 int nt_comm_init(int rank, int world, const uint8_t id[NT_COMM_ID_BYTES]);
 int nt_comm_init_timeout(int rank, int world, const uint8_t id[NT_COMM_ID_BYTES], int64_t timeout_ms);
 /* A bucket: nt_comm_group_begin orders the communication stream after everything enqueued on the compute

@@ -623,6 +623,11 @@ def set_matmul_operand_planes(natural: bool = True, cached: bool = True) -> None
     _check(_lib.nt_set_matmul_operand_planes(int(bool(natural)), int(bool(cached))))
 
 
+def set_producer_planes(on: bool = True) -> None:
+    """tanh / tanh_backward write the TF32 planes of a large dense 2-D result themselves (see the header)."""
+    _check(_lib.nt_set_producer_planes(int(bool(on))))
+
+
 def matmul_split_stats() -> tuple[int, int]:
     """(operand-split launches, operand-plane cache hits) since load."""
     a, b = C.c_uint64(0), C.c_uint64(0)

@@ -148,7 +148,10 @@ int nt_comm_init_timeout(int rank, int world, const uint8_t id[NT_COMM_ID_BYTES]
   NT_CUDA_CHECK(cudaGetDevice(&device));
   ncclUniqueId uid;
   std::memcpy(&uid, id, sizeof(uid));
-  int max_ctas = 0;
+  // NCCL's CTAs take whole SMs from the backward GEMMs they overlap (a GEMM CTA fills an SM): 16 was the
+  // best trade at 8 ranks on NVSwitch -- 8 exposes the exchange, NCCL's own choice slows the GEMMs more than
+  // it gains.  NT_NCCL_MAX_CTAS overrides it; 0 leaves the choice to NCCL.
+  int max_ctas = 16;
   if (const char *e = std::getenv("NT_NCCL_MAX_CTAS")) max_ctas = std::atoi(e);
   // The rendezvous blocks until every rank has joined.  It runs on a helper thread so that a rank
   // that never arrives turns into an error here after `timeout_ms` instead of a hang; the helper

@@ -309,6 +309,35 @@ template <class F> static nt_storage *fused2(F f, const nt_view *a, const nt_vie
   return out.release();
 }
 
+// A producer of GEMM operands (an activation, its gradient): a dense 2-D fp32 result, large enough for the
+// tensor-core path, with rows that are whole 128-byte lines -- it writes its own TF32 planes (ew_contig_planes)
+// and registers them in the operand-plane cache, so the products that follow find them ready.
+static std::atomic<int> g_producer_planes{1};
+static bool dense_2d(const nt_view *v) {
+  return v->ndim == 2 && v->strides[1] == 1 && v->strides[0] == v->shape[1] && v->storage->dtype == NT_FLOAT32 &&
+         v->storage->device == NT_CUDA;
+}
+template <class F, int NIN> static nt_storage *produce_with_planes(F f, const nt_view *a, const nt_view *b) {
+  if (!g_producer_planes.load() || nt_get_matmul_mode() != 1 || !dense_2d(a)) return nullptr;
+  const int64_t R = a->shape[0], C = a->shape[1];
+  if (C % 32 != 0 || R * C < (int64_t(1) << 20)) return nullptr;
+  const float *pa = static_cast<const float *>(a->storage->data) + a->offset, *pb = nullptr;
+  if (!aligned16(pa)) return nullptr;
+  if constexpr (NIN == 2) {
+    if (!dense_2d(b) || b->shape[0] != R || b->shape[1] != C) return nullptr;
+    pb = static_cast<const float *>(b->storage->data) + b->offset;
+    if (!aligned16(pb)) return nullptr;
+  }
+  StorageRef out(storage_new(R * C, NT_FLOAT32, NT_CUDA));
+  float *hi = gemm_tc_adopt_planes(out.s, R, C);
+  if (!hi) return nullptr;
+  const int64_t n = R * C;
+  ew_contig_planes<F, NIN><<<unsigned(ceil_div(n >> 2, 256 * 4)), 256, 0, stream()>>>(f, static_cast<float *>(out->data), pa, pb, n,
+                                                                                      hi, hi + n);
+  check_launch("ew_contig_planes");
+  return out.release();
+}
+
 // equality flag for nt_equals
 template <class T> struct NeqFlagF {
   using in_t = T;
@@ -404,7 +433,14 @@ int nt_sqrt(const nt_view *x, nt_storage **out) {
 }
 int nt_tanh(const nt_view *x, nt_storage **out) {
   NT_API_BEGIN
+  check_view(x, "tanh");
+  if (g_tanh_mode.load() == 0 && (*out = produce_with_planes<TanhF<float>, 1>(TanhF<float>{}, x, nullptr))) return NT_OK;
   *out = (g_tanh_mode.load() == 1) ? unary_impl<TanhExactF, 0>(x, "tanh") : unary_impl<TanhF, 0>(x, "tanh");
+  NT_API_END
+}
+int nt_set_producer_planes(int on) {
+  NT_API_BEGIN
+  g_producer_planes.store(on ? 1 : 0);
   NT_API_END
 }
 int nt_set_tanh_mode(int mode) {
@@ -518,6 +554,11 @@ int nt_relu_backward(const nt_view *g, const nt_view *y, nt_storage **out) {
 }
 int nt_tanh_backward(const nt_view *g, const nt_view *t, nt_storage **out) {
   NT_API_BEGIN
+  {
+    const nt_view *chk[2] = {g, t};
+    fused_checks(chk, 2, "tanh_backward");
+  }
+  if ((*out = produce_with_planes<TanhBwdF, 2>(TanhBwdF{}, g, t))) return NT_OK;
   *out = fused2(TanhBwdF{}, g, t, "tanh_backward");
   NT_API_END
 }

@@ -18,6 +18,7 @@
 #pragma once
 
 #include "nt_core.cuh"
+#include "tf32_split.cuh"
 
 namespace ntb {
 
@@ -90,6 +91,40 @@ __global__ void __launch_bounds__(256) ew_contig(F f, typename F::out_t *out, co
     if constexpr (NIN == 1) out[i] = f(a[i]);
     if constexpr (NIN == 2) out[i] = f(a[i], b[i]);
     if constexpr (NIN == 3) out[i] = f(a[i], b[i], c[i]);
+  }
+}
+
+// ew_contig for an fp32 result that the next kernel will multiply on the tensor cores: besides the result it
+// writes the result's two TF32 planes (hi at `hi`, lo at `lo`, same indexing as `out`), so that the
+// GEMM's operand split -- a read of the result and a write of both planes in a launch of its own --
+// never runs.  n is a multiple of 4.
+template <class F, int NIN>
+__global__ void __launch_bounds__(256) ew_contig_planes(F f, float *out, const float *a, const float *b, int64_t n,
+                                                        float *hi, float *lo) {
+  constexpr int UNROLL = 4;
+  const int64_t nvec = n >> 2;
+  const int64_t base = (int64_t(blockIdx.x) * UNROLL) * blockDim.x + threadIdx.x;
+  float4 va[UNROLL], vb[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    int64_t i = base + int64_t(u) * blockDim.x;
+    if (i < nvec) {
+      va[u] = ld_stream(reinterpret_cast<const float4 *>(a) + i);
+      if constexpr (NIN >= 2) vb[u] = ld_stream(reinterpret_cast<const float4 *>(b) + i);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    int64_t i = base + int64_t(u) * blockDim.x;
+    if (i < nvec) {
+      float4 r;
+      if constexpr (NIN == 1) r = make_float4(f(va[u].x), f(va[u].y), f(va[u].z), f(va[u].w));
+      else r = make_float4(f(va[u].x, vb[u].x), f(va[u].y, vb[u].y), f(va[u].z, vb[u].z), f(va[u].w, vb[u].w));
+      reinterpret_cast<float4 *>(out)[i] = r; // read again soon (backward, the next product): no streaming hint
+      const float h0 = split_hi(r.x), h1 = split_hi(r.y), h2 = split_hi(r.z), h3 = split_hi(r.w);
+      reinterpret_cast<float4 *>(hi)[i] = make_float4(h0, h1, h2, h3);
+      reinterpret_cast<float4 *>(lo)[i] = make_float4(split_lo(r.x, h0), split_lo(r.y, h1), split_lo(r.z, h2), split_lo(r.w, h3));
+    }
   }
 }
 

@@ -32,6 +32,7 @@
 #include <unordered_map>
 
 #include "nt_core.cuh"
+#include "tf32_split.cuh"
 
 namespace ntb {
 
@@ -48,12 +49,6 @@ constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*align*/ +
 
 // ---------------------------------------------------------------------------------------------
 // split_pack
-__device__ __forceinline__ float tf32_round(float x) {
-  uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-  return __uint_as_float(r);
-}
-
 struct SplitArgs {
   const float *src;
   float *hi, *lo;       // [batch][R][Kp]
@@ -62,17 +57,6 @@ struct SplitArgs {
   int mode;              // 0 generic, 1 unit stride along k (128-bit), 2 unit stride along r (128-bit + transpose)
 };
 
-// hi = tf32(x), except that a finite x whose rounding would overflow to infinity keeps the largest
-// finite TF32 value (the remainder then fits in lo); lo = tf32(x - hi), or 0 when x is not finite
-// (inf - inf would turn an infinity into a NaN before any product is formed).
-__device__ __forceinline__ float split_hi(float x) {
-  float h = tf32_round(x);
-  if (isinf(h) && !isinf(x)) h = copysignf(__uint_as_float(0x7F7FE000u), x);
-  return h;
-}
-__device__ __forceinline__ float split_lo(float x, float h) {
-  return (__float_as_uint(h) & 0x7F800000u) == 0x7F800000u ? 0.0f : tf32_round(x - h);
-}
 __device__ __forceinline__ void split_store4(const SplitArgs &a, int64_t idx, float x0, float x1, float x2, float x3) {
   const float h0 = split_hi(x0), h1 = split_hi(x1), h2 = split_hi(x2), h3 = split_hi(x3);
   __stcs(reinterpret_cast<float4 *>(a.hi + idx), make_float4(h0, h1, h2, h3));
@@ -862,6 +846,19 @@ static float *natural_planes(nt_storage *s, int64_t offset, int64_t batch, int64
   PlaneEntry e{offset, batch, s_b, R, C, s_r, Cp, nullptr, 0, s->mutation, g_plane_epoch};
   e.planes = static_cast<float *>(device_alloc(bytes, &e.rounded));
   run_split(s, e);
+  list.push_back(e);
+  return e.planes;
+}
+
+// Planes that a producer kernel fills itself while it still holds its output in registers: registers a
+// valid entry for the dense [R][C] view of `s` (C a multiple of 32, so the planes index like the output)
+// and returns its hi plane (lo follows R * C values later); nullptr when the cache is off.
+float *gemm_tc_adopt_planes(nt_storage *s, int64_t R, int64_t C) {
+  if (!g_operand_cache.load() || C % 32 != 0) return nullptr;
+  std::lock_guard<std::mutex> lk(g_plane_mu);
+  auto &list = g_plane_cache[s];
+  PlaneEntry e{0, 1, 0, R, C, C, C, nullptr, 0, s->mutation, g_plane_epoch};
+  e.planes = static_cast<float *>(device_alloc(size_t(2 * R * C) * 4, &e.rounded));
   list.push_back(e);
   return e.planes;
 }

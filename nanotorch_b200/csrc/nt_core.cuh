@@ -164,6 +164,7 @@ void gemm_tc_refresh(nt_storage *s);
 // Cached planes written by work that was only captured, or overwritten by a graph replay behind the
 // host's back, must not be trusted by later eager calls: a new epoch invalidates all of them.
 void gemm_tc_new_epoch();
+float *gemm_tc_adopt_planes(nt_storage *s, int64_t R, int64_t C); // see gemm_tc.cu
 
 // RAII holder used while an entry point builds its result.
 struct StorageRef {

@@ -1,6 +1,7 @@
 // Runtime half of the C ABI: error string, stream, caching arena, storage lifecycle, host<->device
 // moves, on-device dtype cast, factories and the host RNG stream.
 // Replaces src/cpp/{storage.cpp,allocator.cpp,factory.cu,random.h,cuda.cpp} of the reference.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <random>
@@ -74,8 +75,18 @@ static void ensure_streams_locked(Runtime &r) {
   if (!r.have_cuda) fail_runtime("CUDA device required: no usable GPU found (this library has no CPU compute path).");
   if (r.compute) return;
   NT_CUDA_CHECK(cudaSetDevice(r.device));
-  NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.compute, cudaStreamNonBlocking));
-  NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.comm, cudaStreamNonBlocking));
+  // NT_STREAM_PRIORITY=1: the compute stream gets the highest priority and the communication stream the
+  // lowest, so that CTAs of the backward GEMMs are placed before those of the exchange and of the
+  // parameter updates that run beside them
+  int least = 0, greatest = 0;
+  const char *prio = std::getenv("NT_STREAM_PRIORITY");
+  if (prio && prio[0] == '1' && cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess) {
+    NT_CUDA_CHECK(cudaStreamCreateWithPriority(&r.compute, cudaStreamNonBlocking, greatest));
+    NT_CUDA_CHECK(cudaStreamCreateWithPriority(&r.comm, cudaStreamNonBlocking, least));
+  } else {
+    NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.compute, cudaStreamNonBlocking));
+    NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.comm, cudaStreamNonBlocking));
+  }
   NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.copy, cudaStreamNonBlocking));
   NT_CUDA_CHECK(cudaEventCreateWithFlags(&r.copy_gate, cudaEventDisableTiming));
   NT_CUDA_CHECK(cudaEventCreateWithFlags(&r.copy_done, cudaEventDisableTiming));

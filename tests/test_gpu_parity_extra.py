@@ -381,3 +381,31 @@ def test_a_training_step_splits_each_tensor_once(nt):
     # re-split by the previous update (hits) and are re-split by this one (3 splits)
     assert s1 - s0 == 8, s1 - s0
     assert h1 - h0 == 16 - 5, h1 - h0
+
+
+def test_producers_write_their_own_planes(nt):
+    """tanh and tanh_backward on a large dense matrix also write the result's TF32 planes: same result bits as
+    the plain kernels, the following products launch no split for that operand, and the products are right."""
+    _C = nt._C
+    rng = np.random.default_rng(23)
+    z_np = rng.standard_normal((1024, 1024)).astype(np.float32)
+    w_np = (rng.standard_normal((1024, 512)) * 0.05).astype(np.float32)
+    g_np = rng.standard_normal((1024, 1024)).astype(np.float32)
+    z, w, g = dev(nt, z_np), dev(nt, w_np), dev(nt, g_np)
+    _C.set_producer_planes(False)
+    h_plain = nt.tanh(z)
+    d_plain = nt.Tensor._new_contiguous(_C.tanh_backward(g._C_view, h_plain._C_view), (1024, 1024))
+    _C.set_producer_planes(True)
+    (dev(nt, z_np[:64]) @ w).numpy()                     # w's planes exist from here on
+    s0, h0 = _C.matmul_split_stats()
+    h = nt.tanh(z)
+    d = nt.Tensor._new_contiguous(_C.tanh_backward(g._C_view, h._C_view), (1024, 1024))
+    assert_bit_exact(h.numpy(), h_plain.numpy(), "tanh")
+    assert_bit_exact(d.numpy(), d_plain.numpy(), "tanh backward")
+    y1 = (h @ w).numpy()            # K-major use of h's planes
+    y2 = (h.T @ d).numpy()          # MN-major use of h's and d's planes
+    s1, h1 = _C.matmul_split_stats()
+    assert s1 == s0 and h1 == h0 + 4, (s1 - s0, h1 - h0)
+    hn, dn = h.numpy().astype(np.float64), d.numpy().astype(np.float64)
+    assert_scaled(y1, hn @ w_np.astype(np.float64), np.abs(hn) @ np.abs(w_np.astype(np.float64)), 2e-6, "h @ w")
+    assert_scaled(y2, hn.T @ dn, np.abs(hn.T) @ np.abs(dn), 2e-6, "h^T @ d")
