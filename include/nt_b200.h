@@ -324,11 +324,12 @@ int nt_comm_init_timeout(int rank, int world, const uint8_t id[NT_COMM_ID_BYTES]
 int nt_comm_group_begin(void);
 int nt_comm_group_end(void);
 int nt_comm_allreduce_sum(nt_storage *s);       /* in place, fp32, on the communication stream; ordered after prior work */
-/* nt_sgd_update enqueued on the communication stream, behind the collectives issued so far: the update of
- * one layer overlaps the backward kernels of the layers below it.  The caller vouches that no kernel still
+/* nt_sgd_update enqueued on the update stream (a third stream, of the lowest priority, so that its CTAs fill
+ * idle SMs instead of delaying the GEMM tiles of the compute stream), behind the collectives issued so far
+ * on the communication stream: the update of one layer overlaps the backward kernels of the layers below it.  The caller vouches that no kernel still
  * to be enqueued on the compute stream before the next nt_comm_wait reads the parameter. */
 int nt_comm_sgd_update(const nt_view *param, const nt_view *grad, float lr, float grad_scale);
-int nt_comm_wait(void);                         /* make the compute stream wait for the communication stream (device-side join) */
+int nt_comm_wait(void);                         /* make the compute stream wait for the communication and update streams (device-side join) */
 /* Host-side wait for the communication stream with a time limit.  Past it the communicator is aborted
  * (ncclCommAbort takes the stuck collective kernels down, so the stream drains) and NT_ERR_RUNTIME is
  * returned: a peer that died between steps shows up here instead of as a hang. */

@@ -56,7 +56,8 @@ struct Nccl {
   int rank = 0, world = 1;
   bool in_group = false;
   bool side_work = false; // something was enqueued on the communication stream since the last join
-  cudaEvent_t ready = nullptr, done = nullptr;
+  cudaEvent_t ready = nullptr, done = nullptr, exchanged = nullptr, updated = nullptr;
+  bool update_work = false; // something was enqueued on the update stream since the last join
 };
 static Nccl &nccl() {
   static Nccl n;
@@ -97,6 +98,8 @@ static void ensure_events() {
   if (!n.ready) {
     NT_CUDA_CHECK(cudaEventCreateWithFlags(&n.ready, cudaEventDisableTiming));
     NT_CUDA_CHECK(cudaEventCreateWithFlags(&n.done, cudaEventDisableTiming));
+    NT_CUDA_CHECK(cudaEventCreateWithFlags(&n.exchanged, cudaEventDisableTiming));
+    NT_CUDA_CHECK(cudaEventCreateWithFlags(&n.updated, cudaEventDisableTiming));
   }
 }
 
@@ -241,24 +244,35 @@ int nt_comm_allreduce_sum(nt_storage *s) {
 }
 
 int nt_comm_sgd_update(const nt_view *param, const nt_view *grad, float lr, float grad_scale) {
-  // same kernel and checks as nt_sgd_update, enqueued on the communication stream
+  // same kernel and checks as nt_sgd_update, enqueued on the update stream: behind the collectives issued so
+  // far on the communication stream (which itself is behind the kernels that produced the gradient)
+  Nccl &n = nccl();
   try {
-    comm_after_compute(); // after the kernels that produced the gradient, whatever else is queued there
+    comm_after_compute();
+    NT_CUDA_CHECK(cudaEventRecord(n.exchanged, comm_stream()));
+    NT_CUDA_CHECK(cudaStreamWaitEvent(update_stream(), n.exchanged, 0));
+    n.update_work = true;
   } catch (const Error &e) {
     set_last_error(e.msg);
     return e.code;
   }
-  StreamRedirect redirect(comm_stream());
+  StreamRedirect redirect(update_stream());
   return nt_sgd_update(param, grad, lr, grad_scale);
 }
 
 int nt_comm_wait(void) {
   NT_API_BEGIN
   Nccl &n = nccl();
-  if (!n.side_work) return NT_OK;
-  NT_CUDA_CHECK(cudaEventRecord(n.done, comm_stream()));
-  NT_CUDA_CHECK(cudaStreamWaitEvent(compute_stream(), n.done, 0));
-  n.side_work = false;
+  if (n.side_work) {
+    NT_CUDA_CHECK(cudaEventRecord(n.done, comm_stream()));
+    NT_CUDA_CHECK(cudaStreamWaitEvent(compute_stream(), n.done, 0));
+    n.side_work = false;
+  }
+  if (n.update_work) {
+    NT_CUDA_CHECK(cudaEventRecord(n.updated, update_stream()));
+    NT_CUDA_CHECK(cudaStreamWaitEvent(compute_stream(), n.updated, 0));
+    n.update_work = false;
+  }
   NT_API_END
 }
 
@@ -314,6 +328,7 @@ int nt_comm_destroy(void) {
     destroy_all_graphs();
     cudaStreamSynchronize(compute_stream());
     cudaStreamSynchronize(comm_stream());
+    cudaStreamSynchronize(update_stream());
     n.CommDestroy(n.comm);
     n.comm = nullptr;
   }

@@ -97,7 +97,8 @@ template <class F> auto dispatch_float(int dt, F &&f) {
 // ------------------------------------------------------------------------------------------
 // Runtime singletons
 cudaStream_t stream();       // the one compute stream (non-blocking)
-cudaStream_t comm_stream();  // collectives, and the parameter updates that follow them
+cudaStream_t comm_stream();  // collectives
+cudaStream_t update_stream(); // the parameter updates that follow the collectives (lowest priority)
 cudaStream_t compute_stream(); // the compute stream itself, whatever redirection is active
 // While one of these lives, stream() returns `to`: kernels launched by the ordinary entry points go to
 // that stream instead (used to run a parameter update on the communication stream, right behind the

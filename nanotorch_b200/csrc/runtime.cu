@@ -24,6 +24,7 @@ struct Runtime {
   int sms = 148;
   cudaStream_t compute = nullptr;
   cudaStream_t comm = nullptr;
+  cudaStream_t update = nullptr;
   cudaStream_t copy = nullptr;
   cudaStream_t redirect = nullptr;                     // when set, stream() hands this one out (StreamRedirect)
   cudaEvent_t copy_gate = nullptr, copy_done = nullptr;
@@ -75,17 +76,22 @@ static void ensure_streams_locked(Runtime &r) {
   if (!r.have_cuda) fail_runtime("CUDA device required: no usable GPU found (this library has no CPU compute path).");
   if (r.compute) return;
   NT_CUDA_CHECK(cudaSetDevice(r.device));
-  // NT_STREAM_PRIORITY=1: the compute stream gets the highest priority and the communication stream the
-  // lowest, so that CTAs of the backward GEMMs are placed before those of the exchange and of the
-  // parameter updates that run beside them
+  // Three streams.  The compute stream and the communication stream (NCCL) run at the highest priority;
+  // the update stream -- parameter updates and the re-split of their operand planes, issued behind each
+  // bucket's exchange -- at the lowest, so that its CTAs fill SMs the backward GEMMs leave idle instead
+  // of delaying their tiles.  NT_STREAM_PRIORITY=0 creates all three alike.
   int least = 0, greatest = 0;
   const char *prio = std::getenv("NT_STREAM_PRIORITY");
-  if (prio && prio[0] == '1' && cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess) {
+  const bool flat = prio && prio[0] == '0';
+  if (!flat && cudaDeviceGetStreamPriorityRange(&least, &greatest) == cudaSuccess && least != greatest) {
     NT_CUDA_CHECK(cudaStreamCreateWithPriority(&r.compute, cudaStreamNonBlocking, greatest));
-    NT_CUDA_CHECK(cudaStreamCreateWithPriority(&r.comm, cudaStreamNonBlocking, least));
+    NT_CUDA_CHECK(cudaStreamCreateWithPriority(&r.comm, cudaStreamNonBlocking, greatest));
+    NT_CUDA_CHECK(cudaStreamCreateWithPriority(&r.update, cudaStreamNonBlocking, least));
   } else {
+    cudaGetLastError();
     NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.compute, cudaStreamNonBlocking));
     NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.comm, cudaStreamNonBlocking));
+    NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.update, cudaStreamNonBlocking));
   }
   NT_CUDA_CHECK(cudaStreamCreateWithFlags(&r.copy, cudaStreamNonBlocking));
   NT_CUDA_CHECK(cudaEventCreateWithFlags(&r.copy_gate, cudaEventDisableTiming));
@@ -129,6 +135,12 @@ cudaStream_t comm_stream() {
   std::lock_guard<std::mutex> lk(r.mu);
   ensure_streams_locked(r);
   return r.comm;
+}
+cudaStream_t update_stream() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  ensure_streams_locked(r);
+  return r.update;
 }
 bool is_capturing() {
   Runtime &r = rt();
@@ -561,6 +573,7 @@ int nt_cuda_sync(void) {
   if (cuda_ok()) {
     NT_CUDA_CHECK(cudaStreamSynchronize(stream()));
     NT_CUDA_CHECK(cudaStreamSynchronize(comm_stream()));
+    NT_CUDA_CHECK(cudaStreamSynchronize(update_stream()));
     NT_CUDA_CHECK(cudaStreamSynchronize(rt().copy));
     check_device_errors();
   }

@@ -6,11 +6,11 @@ gradient of the global-batch mean is the average of the local gradients.
 
 Parameters are grouped into buckets in declaration order (a Linear's weight and bias share one).  The
 moment backward has finished the last gradient of a bucket, the bucket's all-reduces (NCCL sum over
-NVLink, issued as one NCCL group, i.e. one launch) go to the communication stream, followed on that
-same stream by the bucket's SGD kernels with the 1/world factor folded in.  Exchange and update of one
-layer thus overlap the backward kernels of the layers below it; `step` only makes the compute stream
-wait for the communication stream.  With one rank there is no collective, and the updates still run
-on the side stream, behind the kernels that produced their gradients.
+NVLink, issued as one NCCL group, i.e. one launch) go to the communication stream, followed -- on a third,
+lowest-priority stream, behind the exchange -- by the bucket's SGD kernels with the 1/world factor folded
+in.  Exchange and update of one layer thus overlap the backward kernels of the layers below it; `step`
+only makes the compute stream wait for the other two.  With one rank there is no collective, and the
+updates still run on the side stream, behind the kernels that produced their gradients.
 """
 
 from __future__ import annotations
