@@ -372,14 +372,13 @@ def time_ops(nt, peaks: dict) -> dict:
         av = [t._C_view for t in A[:k]]
         record("pow2.backward", stream_time([lambda i=i: _C.pow_backward(gv[i], av[i], 2.0) for i in range(k)]),
                3 * numel * 4)
-        # binary backward: mul' = (x2*g, x1*g), div' = (g/x2, ((-x1)/x2^2)*g): g, x1, x2 -> dx1, dx2 = 5 N floats
+        # binary backward, one launch: mul' = (x2*g, x1*g), div' = (g/x2, ((-x1)/x2^2)*g): g, x1, x2 -> dx1, dx2 = 5 N floats
         Bk = copies(dev(host["b"].astype(np.float32)), k)
         Dk = copies(dev(host["d"].astype(np.float32)), k)
         bv, dv2 = [t._C_view for t in Bk], [t._C_view for t in Dk]
-        record("mul.backward", stream_time(
-            [lambda i=i: (_C.multiply(bv[i], gv[i]), _C.multiply(av[i], gv[i])) for i in range(k)]), 5 * numel * 4)
-        record("truediv.backward", stream_time(
-            [lambda i=i: (_C.divide(gv[i], dv2[i]), _C.div_backward_x2(gv[i], av[i], dv2[i])) for i in range(k)]), 5 * numel * 4)
+        record("mul.backward", stream_time([lambda i=i: _C.mul_backward(gv[i], av[i], bv[i]) for i in range(k)]), 5 * numel * 4)
+        record("truediv.backward", stream_time([lambda i=i: _C.div_backward(gv[i], av[i], dv2[i]) for i in range(k)]),
+               5 * numel * 4)
         # one operand seen through a transposed view: its gradient x1*g is written in x2's own (transposed) order
         bt = [t.T._C_view for t in Bk]
         record("mul.transposed.backward", stream_time(

@@ -301,6 +301,12 @@ int nt_log_backward(const nt_view *g, const nt_view *x, nt_storage **out);     /
 int nt_sqrt_backward(const nt_view *g, const nt_view *r, nt_storage **out);    /* (g*0.5) * powf(r,-1)         autograd/ops_unary.py:142-144 */
 int nt_pow_backward(const nt_view *g, const nt_view *x, float exponent, nt_storage **out); /* (g*e) * powf(x,e-1)  autograd/ops_unary.py:264-266 */
 int nt_div_backward_x2(const nt_view *g, const nt_view *x1, const nt_view *x2, nt_storage **out); /* ((-x1)/powf(x2,2))*g  autograd/ops_binary.py:197-202 */
+/* Both gradients of x1 * x2 (x2*g, x1*g; autograd/ops_binary.py:150-156) or of x1 / x2 (g/x2, ((-x1)/powf(x2,2))*g;
+ * autograd/ops_binary.py:192-202) in one pass over g, x1, x2 -- 20 bytes per element instead of the 24 of two
+ * launches.  For three equally shaped dense views; otherwise both results stay NULL and the caller composes
+ * the single-gradient kernels. */
+int nt_mul_backward(const nt_view *g, const nt_view *x1, const nt_view *x2, nt_storage **dx1, nt_storage **dx2);
+int nt_div_backward(const nt_view *g, const nt_view *x1, const nt_view *x2, nt_storage **dx1, nt_storage **dx2);
 /* Max/Min backward: g_expanded * mask where mask = (x == m_expanded) and zero on every tied slice
  * (integer-division quirk of the reference, autograd/ops_reduction.py:201-212, 275-286). */
 int nt_extremum_backward(const nt_view *g_expanded, const nt_view *x, const nt_view *m_expanded,

@@ -660,6 +660,18 @@ def extremum_backward(g_expanded: TensorView, x: TensorView, m_expanded: TensorV
     return _ret_storage(_lib.nt_extremum_backward, _vref(g_expanded), _vref(x), _vref(m_expanded), arr, C.c_int32(n))
 
 
+def _backward_both(fn):
+    def op(g: TensorView, x1: TensorView, x2: TensorView):
+        a, b = C.c_void_p(), C.c_void_p()
+        _check(fn(_vref(g), _vref(x1), _vref(x2), C.byref(a), C.byref(b)))
+        return (Storage._wrap(a.value), Storage._wrap(b.value)) if a.value else None
+    return op
+
+
+mul_backward = _backward_both(_lib.nt_mul_backward)   # (x2*g, x1*g) in one pass, or None
+div_backward = _backward_both(_lib.nt_div_backward)   # (g/x2, ((-x1)/x2**2)*g) in one pass, or None
+
+
 def sgd_update(param: TensorView, grad: TensorView, lr: float, grad_scale: float = 1.0) -> None:
     _check(_lib.nt_sgd_update(_vref(param), _vref(grad), C.c_float(lr), C.c_float(grad_scale)))
 

@@ -225,6 +225,10 @@ class MulOp(_BinaryOp):
 
     def backward(self, g):
         x1, x2 = self.saved_tensors
+        if _need(self, 0) and _need(self, 1) and _fused(g, x1, x2) and g.shape == x1.shape == x2.shape:
+            both = _C.mul_backward(g._C_view, x1._C_view, x2._C_view)   # one pass when all three are dense
+            if both is not None:
+                return Tensor._new_contiguous(both[0], g.shape), Tensor._new_contiguous(both[1], g.shape)
         return (unbroadcast(x2 * g, x1.shape) if _need(self, 0) else None,
                 unbroadcast(x1 * g, x2.shape) if _need(self, 1) else None)
 
@@ -236,6 +240,10 @@ class TrueDivOp(_BinaryOp):
 
     def backward(self, g):
         x1, x2 = self.saved_tensors
+        if _need(self, 0) and _need(self, 1) and _fused(g, x1, x2) and g.shape == x1.shape == x2.shape:
+            both = _C.div_backward(g._C_view, x1._C_view, x2._C_view)
+            if both is not None:
+                return Tensor._new_contiguous(both[0], g.shape), Tensor._new_contiguous(both[1], g.shape)
         g1 = g2 = None
         if _need(self, 0):
             g1 = unbroadcast(g / x2, x1.shape)

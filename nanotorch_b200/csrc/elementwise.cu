@@ -207,6 +207,20 @@ struct DivBwdX2F { // ((-x1) / x2**2) * g
     return ((-x1) / d) * g;
   }
 };
+// both gradients of a product / a quotient, each the reference's own expression (one rounding per step)
+struct MulBwdBothF { // x2 * g, x1 * g                          autograd/ops_binary.py:150-156
+  __device__ __forceinline__ void operator()(float g, float x1, float x2, float *d1, float *d2) const {
+    *d1 = x2 * g;
+    *d2 = x1 * g;
+  }
+};
+struct DivBwdBothF { // g / x2, ((-x1) / x2**2) * g             autograd/ops_binary.py:192-202
+  __device__ __forceinline__ void operator()(float g, float x1, float x2, float *d1, float *d2) const {
+    *d1 = g / x2;
+    float d = x2 * x2;
+    *d2 = ((-x1) / d) * g;
+  }
+};
 struct SgdF { // p - (g * lr)  [optionally (g * scale) first]
   using in_t = float;
   using out_t = float;
@@ -348,6 +362,33 @@ template <class T> struct NeqFlagF {
     return a;
   }
 };
+
+// Both gradients in one launch; *out1 stays NULL when the three views are not equally shaped dense fp32
+// runs (the caller then composes the single-gradient kernels).
+template <class F> static void binary_backward_both(F f, const nt_view *g, const nt_view *x1, const nt_view *x2,
+                                                    nt_storage **out1, nt_storage **out2, const char *fname) {
+  *out1 = *out2 = nullptr;
+  const nt_view *chk[3] = {g, x1, x2};
+  fused_checks(chk, 3, fname);
+  const int64_t n = view_numel(*g);
+  const float *p[3];
+  for (int i = 0; i < 3; ++i) {
+    int64_t acc = 1; // dense row-major?
+    for (int d = chk[i]->ndim - 1; d >= 0; --d) {
+      if (chk[i]->shape[d] != 1 && chk[i]->strides[d] != acc) return;
+      acc *= chk[i]->shape[d];
+    }
+    p[i] = static_cast<const float *>(chk[i]->storage->data) + chk[i]->offset;
+    if (!aligned16(p[i])) return;
+  }
+  if (n < 4) return;
+  StorageRef o1(storage_new(n, NT_FLOAT32, NT_CUDA)), o2(storage_new(n, NT_FLOAT32, NT_CUDA));
+  ew_contig_two<F><<<unsigned(ceil_div(n >> 2, 256 * 2)), 256, 0, stream()>>>(f, static_cast<float *>(o1->data),
+                                                                            static_cast<float *>(o2->data), p[0], p[1], p[2], n);
+  check_launch("ew_contig_two");
+  *out1 = o1.release();
+  *out2 = o2.release();
+}
 
 } // namespace ntb
 
@@ -598,6 +639,17 @@ int nt_div_backward_x2(const nt_view *g, const nt_view *x1, const nt_view *x2, n
   const nt_view *views[4] = {&ov, g, x1, x2};
   ew_launch<DivBwdX2F, 3>(DivBwdX2F{}, views);
   *out = o.release();
+  NT_API_END
+}
+
+int nt_mul_backward(const nt_view *g, const nt_view *x1, const nt_view *x2, nt_storage **dx1, nt_storage **dx2) {
+  NT_API_BEGIN
+  binary_backward_both(MulBwdBothF{}, g, x1, x2, dx1, dx2, "mul_backward");
+  NT_API_END
+}
+int nt_div_backward(const nt_view *g, const nt_view *x1, const nt_view *x2, nt_storage **dx1, nt_storage **dx2) {
+  NT_API_BEGIN
+  binary_backward_both(DivBwdBothF{}, g, x1, x2, dx1, dx2, "div_backward");
   NT_API_END
 }
 

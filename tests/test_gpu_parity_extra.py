@@ -409,3 +409,27 @@ def test_producers_write_their_own_planes(nt):
     hn, dn = h.numpy().astype(np.float64), d.numpy().astype(np.float64)
     assert_scaled(y1, hn @ w_np.astype(np.float64), np.abs(hn) @ np.abs(w_np.astype(np.float64)), 2e-6, "h @ w")
     assert_scaled(y2, hn.T @ dn, np.abs(hn.T) @ np.abs(dn), 2e-6, "h^T @ d")
+
+
+@pytest.mark.parametrize("op", ["mul", "div"])
+def test_binary_backward_both_gradients_in_one_pass(nt, port, op):
+    """x1*x2 and x1/x2 at 4096^2: both gradients come from one launch over g, x1, x2.  mul: bit-exact against the
+    oracle's chain; div: dx1 = g/x2 bit-exact, dx2 = ((-x1)/x2^2)*g within 2^-22 of the largest intermediate
+    (x2*x2 stands in for powf(x2, 2), at most 1 ulp apart).  A non-dense operand takes the composed kernels."""
+    rng = np.random.default_rng(31)
+    n = 4096
+    x1 = rng.uniform(-1, 1, (n, n)).astype(np.float32)
+    x2 = rng.uniform(0.5, 2, (n, n)).astype(np.float32)
+    g = rng.standard_normal((n, n)).astype(np.float32)
+    t1, t2 = dev(nt, x1, True), dev(nt, x2, True)
+    res = t1 * t2 if op == "mul" else t1 / t2
+    (res * dev(nt, g)).sum().backward()
+    if op == "mul":
+        assert_bit_exact(t1.grad.numpy(), port.binary("multiply", x2, g), "dx1")
+        assert_bit_exact(t2.grad.numpy(), port.binary("multiply", x1, g), "dx2")
+    else:
+        assert_bit_exact(t1.grad.numpy(), port.binary("divide", g, x2), "dx1")
+        want = O.div_backward_x2(port, g, x1, x2)
+        assert_scaled(t2.grad.numpy(), want, np.abs(want) + 1e-30, 2.0 ** -21, "dx2")
+    both = getattr(nt._C, f"{op}_backward")(dev(nt, g)._C_view, t1._C_view, t2.T._C_view)
+    assert both is None, "a transposed operand is not a dense run: the composed kernels take it"
