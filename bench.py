@@ -329,6 +329,9 @@ def time_ops(nt, peaks: dict) -> dict:
     v_ = dev(r(13).uniform(-1, 1, (N,)).astype(np.float32))
     dv_ = dev(r(17).uniform(0.5, 2, (N,)).astype(np.float32))
 
+    # each op is timed as itself: tanh / tanh_backward without the TF32 planes they add for a following
+    # product (8 more bytes written per element); the rows named "+planes" time that form
+    _C.set_producer_planes(False)
     with nt.no_grad():
         # ---- binary forward: contiguous, row broadcast, transposed operand
         k = nsets(3 * numel * 4)
@@ -369,6 +372,13 @@ def time_ops(nt, peaks: dict) -> dict:
             sv = [t._C_view for t in saved[name]]
             record(f"{name}.backward", stream_time([lambda i=i: kern(gv[i], sv[i]) for i in range(k)]), 3 * numel * 4)
             saved[name] = None
+        _C.set_producer_planes(True)
+        tsv = [nt.tanh(t) for t in Nn[:k]]
+        record("tanh.forward+planes", stream_time([lambda i=i: _C.tanh(Nn[i]._C_view) for i in range(k)]), 4 * numel * 4)
+        record("tanh.backward+planes", stream_time([lambda i=i: _C.tanh_backward(gv[i], tsv[i]._C_view) for i in range(k)]),
+               5 * numel * 4)
+        _C.set_producer_planes(False)
+        del tsv
         av = [t._C_view for t in A[:k]]
         record("pow2.backward", stream_time([lambda i=i: _C.pow_backward(gv[i], av[i], 2.0) for i in range(k)]),
                3 * numel * 4)
@@ -519,6 +529,7 @@ def time_ops(nt, peaks: dict) -> dict:
                 finally:
                     _C.set_matmul_mode(1)
             del Am, Bm, Gc
+    _C.set_producer_planes(True)
     out["mlp_784_256_10"] = time_config_1(nt)
     out["_notes"] = ("HBM-bound ops: back-to-back launches through the _C boundary over rotating buffer sets larger "
                      "than 4x L2, one event pair around 40 launches; bytes are the reference's mem_bytes() accounting "

@@ -229,10 +229,10 @@ int nt_linear(const nt_view *x, const nt_view *w, const nt_view *bias, nt_storag
  *      round-toward-zero accumulate then shows as a bias of 1e-5 of max|C| at K = 4096, 4e-5 at 16384. */
 int nt_set_matmul_mode(int mode);
 int nt_get_matmul_mode(void);
-/* In modes 1 and 3 a product of at most this many multiply-adds (batch*M*N*K, default 2^26) takes the
- * exact FP32 kernel of mode 0 instead: below that the tensor-core path's two operand-split launches cost
- * more than they save, and small products keep the accuracy of the reference's CUDA kernels.  0 sends
- * every fp32 product to the tensor cores. */
+/* In modes 1 and 3 a product of at most this many multiply-adds (batch*M*N*K, default 2^21) takes the
+ * exact FP32 kernel of mode 0 instead: that small, the tensor-core path's operand-split launches cost more
+ * than they save, and tiny products keep the accuracy of the reference's CUDA kernels.  0 sends every fp32
+ * product to the tensor cores. */
 /* Mode 1 splits each fp32 operand into two TF32 planes (hi, lo) before the product.  natural != 0 (default):
  * the planes keep the operand's own row-major order whichever of its two matrix dims has unit stride -- the
  * kernel reads them K-major or MN-major -- so no operand is transposed on the way.  cached != 0 (default): the

@@ -609,7 +609,7 @@ _lib.nt_get_matmul_tc_min_macs.restype = C.c_int64
 
 
 def set_matmul_tc_min_macs(macs: int) -> None:
-    """Products of at most this many multiply-adds take the exact FP32 kernel in modes 1 and 3 (default 2**26)."""
+    """Products of at most this many multiply-adds take the exact FP32 kernel in modes 1 and 3 (default 2**21)."""
     _check(_lib.nt_set_matmul_tc_min_macs(C.c_int64(int(macs))))
 
 

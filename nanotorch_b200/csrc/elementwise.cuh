@@ -319,19 +319,14 @@ __global__ void __launch_bounds__(256, 4) ew_tile2d(F f, EwParams p) {
     }
   }
 
-  // A warp covers 4 rows x 32 columns (8 lanes x 4 values): with the odd tile pitch both the row-wise
-  // stores of the staging pass and the column-wise reads of the transposed pass then touch 32 distinct
-  // banks (bank = 4 tx + ty + e mod 32).  Pass r handles row half r >> 1 and column half r & 1 of the tile.
-  const int tx = threadIdx.x & 7, ty = threadIdx.x >> 3;
-#define NT_TROW(r) (ty + 32 * ((r) >> 1))
-#define NT_TCOL(r) (4 * tx + 32 * ((r) & 1))
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
 
   // (1) row-major operands: this thread's output-order values (rows ty+16r, columns 4tx..4tx+3), loaded now
   TI v[4][NIN][4];
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int64_t i = i0 + NT_TROW(r);
-    const int64_t j = j0 + NT_TCOL(r);
+    const int64_t i = i0 + ty + 16 * r;
+    const int64_t j = j0 + 4 * tx;
     const bool live = i < nI && j < nJ;
     const bool full = (j + 3 < nJ);
 #pragma unroll
@@ -366,25 +361,25 @@ __global__ void __launch_bounds__(256, 4) ew_tile2d(F f, EwParams p) {
       bool vec[4];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        const int64_t j = j0 + NT_TROW(r);
-        const int64_t i = i0 + NT_TCOL(r);
+        const int64_t j = j0 + ty + 16 * r;
+        const int64_t i = i0 + 4 * tx;
         vec[r] = j < nJ && p.vec_mode[o + 1] == 1 && i + 3 < nI;
         if (vec[r]) x[r] = __ldcs(reinterpret_cast<const float4 *>(src + j * sJ + i));
       }
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
-        const int64_t j = j0 + NT_TROW(r);
-        const int64_t i = i0 + NT_TCOL(r);
+        const int64_t j = j0 + ty + 16 * r;
+        const int64_t i = i0 + 4 * tx;
         if (j >= nJ) continue;
         if (vec[r]) {
           const TI *px = reinterpret_cast<const TI *>(&x[r]);
 #pragma unroll
-          for (int e = 0; e < 4; ++e) tile[slot][NT_TROW(r)][NT_TCOL(r) + e] = px[e];
+          for (int e = 0; e < 4; ++e) tile[slot][ty + 16 * r][4 * tx + e] = px[e];
         } else {
           const TI *q = src + j * sJ + i;
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            if (i + e < nI) tile[slot][NT_TROW(r)][NT_TCOL(r) + e] = q[e];
+            if (i + e < nI) tile[slot][ty + 16 * r][4 * tx + e] = q[e];
         }
       }
     }
@@ -396,8 +391,8 @@ __global__ void __launch_bounds__(256, 4) ew_tile2d(F f, EwParams p) {
   const int64_t oI = p.strides[0][dI], oJ = p.strides[0][dJ];
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int64_t i = i0 + NT_TROW(r);
-    const int64_t j = j0 + NT_TCOL(r);
+    const int64_t i = i0 + ty + 16 * r;
+    const int64_t j = j0 + 4 * tx;
     if (i >= nI || j >= nJ) continue;
     const bool full = (j + 3 < nJ);
 #pragma unroll
@@ -405,7 +400,7 @@ __global__ void __launch_bounds__(256, 4) ew_tile2d(F f, EwParams p) {
       if (p.col_major[o + 1]) {
         const int slot = p.col_major[o + 1] - 1;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[r][o][e] = tile[slot][NT_TCOL(r) + e][NT_TROW(r)];
+        for (int e = 0; e < 4; ++e) v[r][o][e] = tile[slot][4 * tx + e][ty + 16 * r];
       }
     }
     TO res[4];
@@ -425,8 +420,6 @@ __global__ void __launch_bounds__(256, 4) ew_tile2d(F f, EwParams p) {
     }
   }
 }
-#undef NT_TROW
-#undef NT_TCOL
 
 // ---------------------------------------------------------------------------------------------
 // Host-side planner + launcher.

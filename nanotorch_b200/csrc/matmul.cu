@@ -32,7 +32,7 @@ void gemm_tc_split_stats(uint64_t *launches, uint64_t *hits);
 static std::atomic<int> g_natural_planes{1};
 
 static std::atomic<int> g_matmul_mode{1};
-static std::atomic<int64_t> g_tc_min_macs{int64_t(1) << 26}; // batch*M*N*K at or below this: exact FP32 kernel
+static std::atomic<int64_t> g_tc_min_macs{int64_t(1) << 21}; // batch*M*N*K at or below this: exact FP32 kernel
 
 constexpr int BM = 128, BN = 128, BK = 16;
 
@@ -382,8 +382,8 @@ static nt_storage *matmul_impl(const nt_view *x1, const nt_view *x2, const nt_vi
     g.batch = bi;
     const int mode = g_matmul_mode.load();
     bool done = false;
-    // Products too small to fill the tensor cores (three launches against one) take the exact FP32 kernel:
-    // faster there, and the full fp32 accuracy of the reference's own CUDA kernels on the small cases.
+    // Tiny products (a single tile of the exact kernel) take the exact FP32 kernel: one launch instead of
+    // up to three, and the full fp32 accuracy of the reference's own CUDA kernels on the small cases.
     const bool big_enough = double(nbatch) * double(M) * double(N) * double(K) > double(g_tc_min_macs.load());
     if ((mode == 1 || mode == 3) && K > 0 && big_enough) {
       // the tensor-core path takes a single (collapsed) batch stride per operand

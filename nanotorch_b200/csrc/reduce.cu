@@ -264,6 +264,97 @@ __global__ void __launch_bounds__(256) reduce_cols(const float *__restrict__ in,
   if (threadIdx.x == 0) tickets[tile_id] = 0;
 }
 
+// Column reduction for wide matrices (C >= 1024, 128-bit alignment): a CTA streams whole 4 KB row segments --
+// its 8 warps sit side by side, each thread owns 4 columns of every row of the CTA's row range, 8 rows in
+// flight per thread -- so DRAM sees long sequential bursts instead of the 512-byte strips of reduce_cols, and
+// no cross-warp step is needed.  grid.x = 1024-column tile, grid.y = row split, grid.z = outer kept index.
+template <class Op>
+__global__ void __launch_bounds__(256) reduce_cols_wide(const float *__restrict__ in, float *__restrict__ out,
+                                                        float *__restrict__ partials, unsigned *__restrict__ tickets,
+                                                        KeepIndex keep_outer, int64_t R, int64_t C, int64_t sR,
+                                                        int64_t rows_per_split, float divisor) {
+  __shared__ bool is_last;
+  const int64_t c0 = int64_t(blockIdx.x) * 1024 + threadIdx.x * 4;
+  const int S = gridDim.y, split = blockIdx.y;
+  const int64_t z = blockIdx.z;
+  const float *base = in + keep_offset(keep_outer, z) + c0;
+  int64_t r_lo = int64_t(split) * rows_per_split, r_hi = r_lo + rows_per_split;
+  if (r_hi > R) r_hi = R;
+  const bool live = c0 < C; // C is a multiple of 4: a live thread owns 4 valid columns
+  float4 acc = make_float4(Op::neutral(), Op::neutral(), Op::neutral(), Op::neutral());
+  if (live) {
+    int64_t r = r_lo;
+    for (; r + 7 < r_hi; r += 8) {
+      float4 b[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) b[u] = __ldcs(reinterpret_cast<const float4 *>(base + (r + u) * sR));
+      // fixed tree over the 8 rows, then into the running value: the order never depends on the grid
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        b[u].x = Op::combine(b[u].x, b[u + 4].x);
+        b[u].y = Op::combine(b[u].y, b[u + 4].y);
+        b[u].z = Op::combine(b[u].z, b[u + 4].z);
+        b[u].w = Op::combine(b[u].w, b[u + 4].w);
+      }
+      acc.x = Op::combine(acc.x, Op::combine(Op::combine(b[0].x, b[1].x), Op::combine(b[2].x, b[3].x)));
+      acc.y = Op::combine(acc.y, Op::combine(Op::combine(b[0].y, b[1].y), Op::combine(b[2].y, b[3].y)));
+      acc.z = Op::combine(acc.z, Op::combine(Op::combine(b[0].z, b[1].z), Op::combine(b[2].z, b[3].z)));
+      acc.w = Op::combine(acc.w, Op::combine(Op::combine(b[0].w, b[1].w), Op::combine(b[2].w, b[3].w)));
+    }
+    for (; r < r_hi; ++r) {
+      float4 b = __ldcs(reinterpret_cast<const float4 *>(base + r * sR));
+      acc.x = Op::combine(acc.x, b.x);
+      acc.y = Op::combine(acc.y, b.y);
+      acc.z = Op::combine(acc.z, b.z);
+      acc.w = Op::combine(acc.w, b.w);
+    }
+  }
+  float *o = out + z * C + c0;
+  if (S == 1) {
+    if (live) {
+      if (divisor != 0.0f) acc = make_float4(acc.x / divisor, acc.y / divisor, acc.z / divisor, acc.w / divisor);
+      *reinterpret_cast<float4 *>(o) = acc;
+    }
+    return;
+  }
+  if (live) *reinterpret_cast<float4 *>(partials + (z * S + split) * C + c0) = acc;
+  __threadfence();
+  __syncthreads();
+  const int64_t tile_id = z * gridDim.x + blockIdx.x;
+  if (threadIdx.x == 0) {
+    unsigned t = atomicAdd(&tickets[tile_id], 1u);
+    is_last = (t == unsigned(S - 1));
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  if (live) {
+    float4 a = make_float4(Op::neutral(), Op::neutral(), Op::neutral(), Op::neutral());
+    const float *pp = partials + z * S * C + c0;
+    int s = 0;
+    for (; s + 3 < S; s += 4) { // partial sums in split order, four loads in flight
+      float4 p0 = __ldcg(reinterpret_cast<const float4 *>(pp + int64_t(s) * C));
+      float4 p1 = __ldcg(reinterpret_cast<const float4 *>(pp + int64_t(s + 1) * C));
+      float4 p2 = __ldcg(reinterpret_cast<const float4 *>(pp + int64_t(s + 2) * C));
+      float4 p3 = __ldcg(reinterpret_cast<const float4 *>(pp + int64_t(s + 3) * C));
+      a.x = Op::combine(Op::combine(Op::combine(Op::combine(a.x, p0.x), p1.x), p2.x), p3.x);
+      a.y = Op::combine(Op::combine(Op::combine(Op::combine(a.y, p0.y), p1.y), p2.y), p3.y);
+      a.z = Op::combine(Op::combine(Op::combine(Op::combine(a.z, p0.z), p1.z), p2.z), p3.z);
+      a.w = Op::combine(Op::combine(Op::combine(Op::combine(a.w, p0.w), p1.w), p2.w), p3.w);
+    }
+    for (; s < S; ++s) {
+      float4 p0 = __ldcg(reinterpret_cast<const float4 *>(pp + int64_t(s) * C));
+      a.x = Op::combine(a.x, p0.x);
+      a.y = Op::combine(a.y, p0.y);
+      a.z = Op::combine(a.z, p0.z);
+      a.w = Op::combine(a.w, p0.w);
+    }
+    if (divisor != 0.0f) a = make_float4(a.x / divisor, a.y / divisor, a.z / divisor, a.w / divisor);
+    *reinterpret_cast<float4 *>(o) = a;
+  }
+  if (threadIdx.x == 0) tickets[tile_id] = 0;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Generic path: the reference's (index, value) combiner, any dtype pair.
 template <class O> struct Item {
@@ -444,6 +535,28 @@ template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, f
     if (Z > 65535) return false;
     bool vec = (C % 4 == 0) && (sR % 4 == 0) && aligned16(in);
     for (int d = 0; d < outer.ndim; ++d) vec = vec && (outer.strides[d] % 4 == 0);
+    if (vec && C >= 1024 && aligned16(out)) {
+      const int64_t tiles = ceil_div(C, 1024);
+      int64_t S = ceil_div(int64_t(sms) * 4, tiles * Z);
+      int64_t max_s = ceil_div(R, 32);
+      if (S > max_s) S = max_s;
+      if (S > 65535) S = 65535;
+      if (S < 1) S = 1;
+      int64_t rows_per_split = ceil_div(ceil_div(R, S), 8) * 8;
+      S = ceil_div(R, rows_per_split);
+      float *partials = nullptr;
+      unsigned *tk = nullptr;
+      size_t rounded = 0;
+      if (S > 1) {
+        partials = static_cast<float *>(device_alloc(size_t(Z * S * C) * sizeof(float), &rounded));
+        tk = tickets(Z * tiles);
+      }
+      dim3 grid{unsigned(tiles), unsigned(S), unsigned(Z)};
+      reduce_cols_wide<Op><<<grid, 256, 0, st>>>(in, out, partials, tk, outer, R, C, sR, rows_per_split, divisor);
+      if (partials) device_free(partials, rounded);
+      check_launch("reduce_cols_wide");
+      return true;
+    }
     const int TW = vec ? 128 : 32;
     const int64_t tiles = ceil_div(C, TW);
     if (tiles > 0x7fffffffLL) return false;
