@@ -1065,7 +1065,7 @@ GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (15 * 939.5e6 + 8 * 1140.9e6) / 23
 PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
                  "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows", "gemm_step_shapes",
                  "sgemm4096", "max_backward8192_dim0", "sum_short_rows", "sgd4096", "cast4096", "scatter8192_ordered", "add_sliced_3d",
-                 "mean8192_dim1", "mlp_step_16384", "mlp_step_2048")
+                 "mean8192_dim1", "mlp_step_16384", "mlp_step_2048", "mul_backward4096")
 
 
 def profile_case(name: str, launches: int = 3) -> None:
@@ -1146,6 +1146,10 @@ def profile_case(name: str, launches: int = 3) -> None:
     elif name == "mean8192_dim1":  # the sum kernel with the division in its finish
         x = dev(r(20).standard_normal((8192, 8192)))
         fn = lambda: _C.mean_f32(x._C_view, [1], 8192)  # noqa: E731
+    elif name == "mul_backward4096":  # both gradients of a product in one launch (ew_contig_two)
+        a, b = dev(r(10).uniform(-1, 1, (4096, 4096))), dev(r(11).uniform(-1, 1, (4096, 4096)))
+        g = dev(r(16).standard_normal((4096, 4096)))
+        fn = lambda: _C.mul_backward(g._C_view, a._C_view, b._C_view)  # noqa: E731
     elif name == "sgd4096":
         p_, g_ = dev(r(31).uniform(-0.04, 0.04, (4096, 4096))), dev(r(32).standard_normal((4096, 4096)))
         fn = lambda: _C.sgd_update(p_._C_view, g_._C_view, 1e-3, 0.125)  # noqa: E731
