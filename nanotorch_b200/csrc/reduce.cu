@@ -151,28 +151,47 @@ __global__ void __launch_bounds__(256) reduce_rows(const float *__restrict__ in,
   }
 }
 
-// Short rows: one warp per row, eight rows per CTA.
+// Short rows: a warp takes four rows at a time (their loads are issued together, so that a lane has four
+// 128-bit loads in flight instead of one), 32 rows per CTA.
 template <class Op>
 __global__ void __launch_bounds__(256) reduce_rows_warp(const float *__restrict__ in, float *__restrict__ out,
                                                         KeepIndex keep, int64_t n_rows, int64_t L, float divisor) {
-  const int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (row >= n_rows) return;
+  const int64_t row0 = (int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5)) * 4;
+  if (row0 >= n_rows) return;
   const int lane = threadIdx.x & 31;
-  const float *p = in + keep_offset(keep, row);
-  float a = Op::neutral();
-  if ((reinterpret_cast<uintptr_t>(p) & 15) == 0) {
-    const int64_t nvec = L >> 2;
-    const float4 *pv = reinterpret_cast<const float4 *>(p);
-    for (int64_t i = lane; i < nvec; i += 32) {
-      float4 v = pv[i];
-      a = Op::combine(a, Op::combine(Op::combine(v.x, v.y), Op::combine(v.z, v.w)));
-    }
-    for (int64_t j = (nvec << 2) + lane; j < L; j += 32) a = Op::combine(a, p[j]);
-  } else {
-    for (int64_t j = lane; j < L; j += 32) a = Op::combine(a, p[j]);
+  const float *p[4];
+  bool vec = true;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int64_t row = (row0 + r < n_rows) ? row0 + r : n_rows - 1; // a row past the end re-reads the last one, unused
+    p[r] = in + keep_offset(keep, row);
+    vec = vec && ((reinterpret_cast<uintptr_t>(p[r]) & 15) == 0);
   }
-  a = warp_reduce<Op>(a);
-  if (lane == 0) out[row] = (divisor != 0.0f) ? a / divisor : a;
+  float a[4] = {Op::neutral(), Op::neutral(), Op::neutral(), Op::neutral()};
+  if (vec) {
+    const int64_t nvec = L >> 2;
+    for (int64_t i = lane; i < nvec; i += 32) {
+      float4 v[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) v[r] = __ldcs(reinterpret_cast<const float4 *>(p[r]) + i);
+#pragma unroll
+      for (int r = 0; r < 4; ++r) a[r] = Op::combine(a[r], Op::combine(Op::combine(v[r].x, v[r].y), Op::combine(v[r].z, v[r].w)));
+    }
+    for (int64_t j = (nvec << 2) + lane; j < L; j += 32) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) a[r] = Op::combine(a[r], p[r][j]);
+    }
+  } else {
+    for (int64_t j = lane; j < L; j += 32) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) a[r] = Op::combine(a[r], p[r][j]);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    a[r] = warp_reduce<Op>(a[r]);
+    if (lane == 0 && row0 + r < n_rows) out[row0 + r] = (divisor != 0.0f) ? a[r] / divisor : a[r];
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -497,7 +516,7 @@ template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, f
   if (pl.drop.ndim == 1 && pl.drop.strides[0] == 1) {
     const int64_t L = pl.n_drop, n_rows = pl.n_keep;
     if (L < 1024 && n_rows >= 64) {
-      int64_t blocks = ceil_div(n_rows, 8);
+      int64_t blocks = ceil_div(n_rows, 32);
       if (blocks > 0x7fffffffLL) return false;
       reduce_rows_warp<Op><<<unsigned(blocks), 256, 0, st>>>(in, out, pl.keep, n_rows, L, divisor);
       check_launch("reduce_rows_warp");
@@ -1014,7 +1033,7 @@ int nt_sum_rows_noalloc(const float *in, int64_t n_rows, int64_t row_len, float 
   keep.shape[0] = n_rows;
   keep.strides[0] = row_len;
   if (row_len < 1024 && n_rows >= 64) {
-    int64_t blocks = ceil_div(n_rows, 8);
+    int64_t blocks = ceil_div(n_rows, 32);
     if (blocks > 0x7fffffffLL) fail_invalid("nt_sum_rows_noalloc: too many rows for one launch.");
     reduce_rows_warp<RSum><<<unsigned(blocks), 256, 0, st>>>(in, out, keep, n_rows, row_len, 0.0f);
     check_launch("reduce_rows_warp");
