@@ -136,6 +136,11 @@ inline int pow_special(float e) {
   if (e == -2.0f) return 6;
   return 0;
 }
+struct SquareF { // pow(x, 2.0f): the exponent training uses (the MSE loss), without the general path's registers
+  using in_t = float;
+  using out_t = float;
+  __device__ __forceinline__ float operator()(float a) const { return a * a; }
+};
 template <class T> struct PowF {
   using in_t = T;
   using out_t = T;
@@ -519,8 +524,14 @@ int nt_pow(const nt_view *x, const nt_scalar *exponent, nt_storage **out) {
   dispatch_arith(dt, [&]<class T>() {
     T v = (exponent->kind == 2) ? static_cast<T>(exponent->d) : static_cast<T>(exponent->i);
     PowF<T> f{v, 0};
-    if constexpr (std::is_same_v<T, float>) f.special = pow_special(v);
     const nt_view *views[2] = {&ov, x};
+    if constexpr (std::is_same_v<T, float>) {
+      f.special = pow_special(v);
+      if (f.special == 3) {
+        ew_launch<SquareF, 1>(SquareF{}, views);
+        return;
+      }
+    }
     ew_launch<PowF<T>, 1>(f, views);
   });
   *out = o.release();
