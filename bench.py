@@ -1056,9 +1056,9 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
         dist.destroy_process_group()
 
 
-# (15 * 2760.6 MB + 8 * 2998.1 MB) / 23: forward / input-gradient shape and weight-gradient shape of the step
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = 2.843e9
-GEMM_TRAFFIC_SOURCE = "profiles/gemm_3xtf32_step_shapes_dram_traffic.md (ncu --set full, one launch per shape)"
+# (15 * 2882.6 MB + 8 * 3027.4 MB) / 23: forward / input-gradient shape and weight-gradient shape of the step
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = 2.933e9
+GEMM_TRAFFIC_SOURCE = "profiles/gemm_3xtf32_step_shapes_dram_traffic.md (ncu, second capture: one launch per shape)"
 # fp32 operands read once, hi/lo planes written and read once, output written once, same 15 : 8 weighting
 GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (15 * 939.5e6 + 8 * 1140.9e6) / 23
 
