@@ -835,6 +835,68 @@ __global__ void __launch_bounds__(256) extremum_apply_vec(const float *__restric
   __stcs(reinterpret_cast<float4 *>(out + outer * L + inner), make_float4(res[0], res[1], res[2], res[3]));
 }
 
+// Optimistic single pass for the long-slice and leading-dim cases: ties are rare, so write g * float(x == m)
+// straight away (x read once, 8 bytes per element) and count the matches per slice on the side -- one atomic per
+// match, i.e. one per slice unless it is tied.  extremum_fix_ties then revisits only the slices whose count is
+// above 1 and turns their matches into g * 0, which is what the reference's integer 1 // count leaves there.
+template <bool ROWS>
+__global__ void __launch_bounds__(256) extremum_apply_count_vec(const float *__restrict__ x, const float *__restrict__ g,
+                                                                const float *__restrict__ m, int *__restrict__ count,
+                                                                float *__restrict__ out, SliceScalars sc, int64_t L,
+                                                                int64_t sR, int chunks) {
+  const int64_t outer = blockIdx.x / chunks;
+  const int64_t inner = int64_t(blockIdx.x - outer * chunks) * 1024 + threadIdx.x * 4;
+  if (inner >= L) return;
+  const float *px = ROWS ? x + slice_offset(sc.x_keep, outer) + inner : x + outer * sR + inner;
+  const float4 v = __ldcs(reinterpret_cast<const float4 *>(px));
+  const float xv[4] = {v.x, v.y, v.z, v.w};
+  float res[4];
+  if (ROWS) {
+    const float gv = g[slice_offset(sc.g_keep, outer)], mv = m[slice_offset(sc.m_keep, outer)];
+    int hits = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool eq = xv[e] == mv;
+      hits += eq ? 1 : 0;
+      res[e] = gv * (eq ? 1.0f : 0.0f);
+    }
+    if (hits) atomicAdd(count + outer, hits);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t c = inner + e;
+      const float gv = g[slice_offset(sc.g_keep, c)], mv = m[slice_offset(sc.m_keep, c)];
+      const bool eq = xv[e] == mv;
+      if (eq) atomicAdd(count + c, 1);
+      res[e] = gv * (eq ? 1.0f : 0.0f);
+    }
+  }
+  __stcs(reinterpret_cast<float4 *>(out + outer * L + inner), make_float4(res[0], res[1], res[2], res[3]));
+}
+
+// ROWS: one CTA per slice (n_slices CTAs), COLS: one thread per column.  Slices with a unique extremum -- all of
+// them, normally -- cost one read of their counter.
+template <bool ROWS>
+__global__ void __launch_bounds__(256) extremum_fix_ties(const float *__restrict__ x, const float *__restrict__ g,
+                                                         const float *__restrict__ m, const int *__restrict__ count,
+                                                         float *__restrict__ out, SliceScalars sc, int64_t n_slices,
+                                                         int64_t n_drop, int64_t sR) {
+  if (ROWS) {
+    const int64_t slice = blockIdx.x;
+    if (count[slice] <= 1) return;
+    const float *px = x + slice_offset(sc.x_keep, slice);
+    const float gv = g[slice_offset(sc.g_keep, slice)], mv = m[slice_offset(sc.m_keep, slice)];
+    for (int64_t j = threadIdx.x; j < n_drop; j += 256)
+      if (px[j] == mv) out[slice * n_drop + j] = gv * 0.0f;
+  } else {
+    const int64_t c = int64_t(blockIdx.x) * 256 + threadIdx.x;
+    if (c >= n_slices || count[c] <= 1) return;
+    const float gv = g[slice_offset(sc.g_keep, c)], mv = m[slice_offset(sc.m_keep, c)];
+    for (int64_t r = 0; r < n_drop; ++r)
+      if (x[r * sR + c] == mv) out[r * n_slices + c] = gv * 0.0f;
+  }
+}
+
 // One pass for ROWS slices of at most 16384 elements: a CTA keeps its whole slice in registers (VPT
 // 128-bit vectors per thread), counts the positions equal to the extremum, and writes the gradient from
 // the registers -- x is read once: 8 bytes per element instead of 12, no counter array, one launch.
@@ -949,16 +1011,20 @@ static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt
       device_free(count, rounded);
       return false;
     }
-    extremum_count_rows<<<unsigned(pl.n_keep * chunks), 256, 0, st>>>(xp, mp, count, sc, L, int(chunks), chunk);
-    check_launch("extremum_count_rows");
     bool vec = (L % 4 == 0) && aligned16(xp) && aligned16(out);
     for (int k = 0; k < sc.x_keep.ndim; ++k) vec = vec && (sc.x_keep.strides[k] % 4 == 0);
     const int64_t vchunks = ceil_div(L, 1024);
-    if (vec && pl.n_keep * vchunks <= 0x7fffffffLL)
-      extremum_apply_vec<true><<<unsigned(pl.n_keep * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, L, 0, int(vchunks));
-    else
+    if (vec && pl.n_keep * vchunks <= 0x7fffffffLL) {
+      extremum_apply_count_vec<true><<<unsigned(pl.n_keep * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, L, 0, int(vchunks));
+      check_launch("extremum_apply_count_vec");
+      extremum_fix_ties<true><<<unsigned(pl.n_keep), 256, 0, st>>>(xp, gp, mp, count, out, sc, pl.n_keep, L, 0);
+      check_launch("extremum_fix_ties");
+    } else {
+      extremum_count_rows<<<unsigned(pl.n_keep * chunks), 256, 0, st>>>(xp, mp, count, sc, L, int(chunks), chunk);
+      check_launch("extremum_count_rows");
       extremum_apply<true><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, pl.n_keep, L, 0, vec ? 1 : 0);
-    check_launch("extremum_apply");
+      check_launch("extremum_apply");
+    }
   } else {
     const int64_t R = pl.n_drop, C = pl.n_keep, sR = pl.drop.strides[0];
     const bool vec = (C % 4 == 0) && (sR % 4 == 0) && aligned16(xp) && aligned16(out);
@@ -974,14 +1040,18 @@ static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt
       return false;
     }
     dim3 grid{unsigned(tiles), unsigned(row_blocks), 1};
-    extremum_count_cols<<<grid, 256, 0, st>>>(xp, mp, count, sc, R, C, sR, rows_per_block, vec ? 1 : 0);
-    check_launch("extremum_count_cols");
     const int64_t vchunks = ceil_div(C, 1024);
-    if (vec && R * vchunks <= 0x7fffffffLL)
-      extremum_apply_vec<false><<<unsigned(R * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, C, sR, int(vchunks));
-    else
+    if (vec && R * vchunks <= 0x7fffffffLL) {
+      extremum_apply_count_vec<false><<<unsigned(R * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, C, sR, int(vchunks));
+      check_launch("extremum_apply_count_vec");
+      extremum_fix_ties<false><<<unsigned(ceil_div(C, 256)), 256, 0, st>>>(xp, gp, mp, count, out, sc, C, R, sR);
+      check_launch("extremum_fix_ties");
+    } else {
+      extremum_count_cols<<<grid, 256, 0, st>>>(xp, mp, count, sc, R, C, sR, rows_per_block, vec ? 1 : 0);
+      check_launch("extremum_count_cols");
       extremum_apply<false><<<unsigned(apply_blocks), 256, 0, st>>>(xp, gp, mp, count, out, sc, R, C, sR, vec ? 1 : 0);
-    check_launch("extremum_apply");
+      check_launch("extremum_apply");
+    }
   }
   device_free(count, rounded);
   return true;

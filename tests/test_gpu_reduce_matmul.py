@@ -302,3 +302,37 @@ def test_extremum_backward_row_slices_with_ties(nt, port, L):
                                    np.broadcast_to(m[:, None], xs.shape), [1])
         assert_bit_exact(t.grad.numpy(), want, f"{name} backward, L={L}")
         assert (want[tied] == 0).all() and (np.abs(want[~tied]).sum(axis=1) > 0).all()
+
+
+@pytest.mark.parametrize("axes", [(0,), (0, 1)])
+def test_extremum_backward_leading_dim_and_full_with_ties(nt, port, axes):
+    """Max/min backward over the leading dim and over the whole tensor: one optimistic pass writes g * (x == m)
+    while counting the matches per slice, a second launch revisits only the tied slices (zero gradient there, the
+    reference's integer-division quirk).  A third of the columns carry a tied extremum; for the full reduction
+    both the tied and the unique case are run."""
+    rng = np.random.default_rng(len(axes) + 40)
+    R, C = 3000, 2048
+    for tie_everything in ((False, True) if axes == (0, 1) else (False,)):
+        x = rng.standard_normal((R, C)).astype(np.float32)
+        if axes == (0,):
+            tied = rng.random(C) < 0.33
+            for c in np.flatnonzero(tied):
+                i, j = rng.choice(R, 2, replace=False)
+                x[i, c] = x[j, c] = 9.0
+        elif tie_everything:
+            x[17, 33] = x[2999, 2047] = 9.0
+        else:
+            x[17, 33] = 9.0
+        g_np = rng.standard_normal((C,) if axes == (0,) else ()).astype(np.float32)
+        for name, sign in (("max", 1.0), ("min", -1.0)):
+            xs = (x * sign).astype(np.float32)
+            t = dev(nt, xs, True)
+            red = getattr(t, name)(axes)
+            (red * dev(nt, g_np)).sum().backward()
+            m = getattr(xs, name)(axis=axes)
+            want = O.extremum_backward(port, np.broadcast_to(g_np, xs.shape), xs, np.broadcast_to(m, xs.shape), list(axes))
+            assert_bit_exact(t.grad.numpy(), want, f"{name} backward over {axes}, tie={tie_everything}")
+            if axes == (0,):
+                assert (want[:, tied] == 0).all() and (np.abs(want[:, ~tied]).sum(axis=0) > 0).all()
+            else:
+                assert (np.abs(want).sum() == 0) == tie_everything
