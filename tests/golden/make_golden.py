@@ -327,7 +327,7 @@ def extra_cases(nt, out: dict):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("NT_REFERENCE", "/root/reference"),
+    ap.add_argument("--ref", default=os.environ.get("NT_REFERENCE", str(REPO.parent / "reference")),
                     help="path of the reference checkout (or set NT_REFERENCE)")
     args = ap.parse_args()
     nt = import_reference(Path(args.ref))

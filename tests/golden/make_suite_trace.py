@@ -164,7 +164,7 @@ class Recorder:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default=os.environ.get("NT_REFERENCE", "/root/reference"))
+    ap.add_argument("--ref", default=os.environ.get("NT_REFERENCE", str(REPO.parent / "reference")))
     args = ap.parse_args()
     ref = Path(args.ref)
     from make_golden import import_reference

@@ -31,7 +31,7 @@ from pathlib import Path
 import pytest
 
 REPO = Path(__file__).resolve().parent.parent
-REFERENCE = Path(os.environ.get("NT_REFERENCE", "/root/reference"))
+REFERENCE = Path(os.environ.get("NT_REFERENCE", str(REPO.parent / "reference")))  # a checkout beside this repository
 
 ALIAS = '''
 import sys
@@ -116,7 +116,7 @@ def test_on_the_reference_cpu_backend_everything_passes(tmp_path):
 
 
 def test_the_references_python_layer_runs_on_this_librarys_shim(tmp_path):
-    """The other direction (option B): the reference's OWN Python package, its files
+    """The other direction (the ctypes shim dropped in as ``nanotorch/_C.py``): the reference's OWN Python package, its files
     linked in place, with ``nanotorch/_C.py`` forwarding to ``nanotorch_b200._C`` instead of the pybind11
     module.  Its tests build Cpu tensors, so whatever reaches a kernel fails with "requires Cuda"; nothing
     else may fail -- Dtype/Device enum behaviour, Storage's buffer protocol, from_iterable, TensorView,
