@@ -278,7 +278,7 @@ int nt_clone_contiguous_view_from(const nt_view *src, nt_storage **out);     /* 
  * Scatter: where several source positions address one destination, the destination ends with the
  * value of the last of them in row-major order of `src`, as the reference's sequential loop leaves
  * it; NT_INDEX_UNIQUE (the caller vouches that destinations are distinct) skips the ordering pass
- * and its scratch of 16 bytes per destination element.  Storage::version is not bumped, as in the
+ * and its scratch (8 bytes per 16-byte destination item, 16 beyond 2^31 items).  Storage::version is not bumped, as in the
  * reference. */
 #define NT_INDEX_CHECKED 1u
 #define NT_INDEX_UNIQUE 2u

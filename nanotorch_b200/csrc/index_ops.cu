@@ -75,6 +75,8 @@ __device__ __forceinline__ void ix_offsets(const IndexParams &p, IDX lin, int64_
 // MODE 3: scatter copy pass that only lets the recorded owner write.
 template <class V, class IDX, int MODE, int NF>
 __global__ void __launch_bounds__(256) index_copy(IndexParams p, const V *from, V *to, unsigned long long *owner) {
+  // owner entries are as wide as the work-item index: 32 bits whenever the launch has fewer than 2^31 items
+  using OW = std::conditional_t<sizeof(IDX) == 4, unsigned int, unsigned long long>;
   const int nf = NF > 0 ? NF : p.n_fancy;
   const int64_t base = (int64_t(blockIdx.x) * IX_UNROLL) * blockDim.x + threadIdx.x;
   int64_t lin_off[IX_UNROLL], ix_off[IX_UNROLL];
@@ -99,14 +101,14 @@ __global__ void __launch_bounds__(256) index_copy(IndexParams p, const V *from, 
   if constexpr (MODE == 2) {
 #pragma unroll
     for (int u = 0; u < IX_UNROLL; ++u)
-      if (live[u]) atomicMax(owner + ix_off[u], (unsigned long long)(base + int64_t(u) * blockDim.x) + 1ull);
+      if (live[u]) atomicMax(reinterpret_cast<OW *>(owner) + ix_off[u], OW(base + int64_t(u) * blockDim.x) + OW(1));
     return;
   }
   V val[IX_UNROLL];
 #pragma unroll
   for (int u = 0; u < IX_UNROLL; ++u) {
     if constexpr (MODE == 3) {
-      if (live[u]) live[u] = owner[ix_off[u]] == (unsigned long long)(base + int64_t(u) * blockDim.x) + 1ull;
+      if (live[u]) live[u] = reinterpret_cast<const OW *>(owner)[ix_off[u]] == OW(base + int64_t(u) * blockDim.x) + OW(1);
     }
     if (live[u]) val[u] = (MODE == 0) ? from[ix_off[u]] : from[lin_off[u]];
   }
@@ -355,17 +357,19 @@ int nt_scatter_to_axes(const nt_view *src, const nt_view *out, const int64_t *fa
       // owner[] is addressed like the indexed operand (relative to its view offset, in work items);
       // negative strides can reach below the offset, so the scratch spans the whole storage twice over
       // and the pointer handed to the kernel sits at its middle
-      const int64_t span = pl.ix_storage_elems / pl.vec + 1;
+      const int64_t span = (pl.ix_storage_elems / pl.vec + 2) & ~int64_t(1); // even: the middle stays 8-byte aligned
+      const size_t width = (pl.p.items < (int64_t(1) << 31)) ? 4 : 8;          // as index_copy's IDX (launch_mode)
       size_t rounded = 0;
-      auto *scratch = static_cast<unsigned long long *>(device_alloc(size_t(2 * span) * 8, &rounded));
+      auto *scratch = static_cast<char *>(device_alloc(size_t(2 * span) * width, &rounded));
       struct Guard {
         void *p;
         size_t r;
         ~Guard() { device_free(p, r); }
       } guard{scratch, rounded};
-      NT_CUDA_CHECK(cudaMemsetAsync(scratch, 0, size_t(2 * span) * 8, stream()));
-      launch_width<2>(pl, pl.lin_base, to, scratch + span);
-      launch_width<3>(pl, pl.lin_base, to, scratch + span);
+      NT_CUDA_CHECK(cudaMemsetAsync(scratch, 0, size_t(2 * span) * width, stream()));
+      auto *middle = reinterpret_cast<unsigned long long *>(scratch + size_t(span) * width);
+      launch_width<2>(pl, pl.lin_base, to, middle);
+      launch_width<3>(pl, pl.lin_base, to, middle);
     }
   }
   storage_touch(out->storage);

@@ -843,35 +843,53 @@ template <bool ROWS>
 __global__ void __launch_bounds__(256) extremum_apply_count_vec(const float *__restrict__ x, const float *__restrict__ g,
                                                                 const float *__restrict__ m, int *__restrict__ count,
                                                                 float *__restrict__ out, SliceScalars sc, int64_t L,
-                                                                int64_t sR, int chunks) {
+                                                                int64_t sR, int chunks, int gm_vec) {
+  // a CTA owns 4096 consecutive elements of ONE outer index (a slice for ROWS, a matrix row for COLS); a thread
+  // owns four 128-bit vectors 1024 elements apart, all loaded before the first use
   const int64_t outer = blockIdx.x / chunks;
-  const int64_t inner = int64_t(blockIdx.x - outer * chunks) * 1024 + threadIdx.x * 4;
-  if (inner >= L) return;
-  const float *px = ROWS ? x + slice_offset(sc.x_keep, outer) + inner : x + outer * sR + inner;
-  const float4 v = __ldcs(reinterpret_cast<const float4 *>(px));
-  const float xv[4] = {v.x, v.y, v.z, v.w};
-  float res[4];
+  const int64_t base = int64_t(blockIdx.x - outer * chunks) * 4096 + threadIdx.x * 4;
+  const float *px = ROWS ? x + slice_offset(sc.x_keep, outer) : x + outer * sR;
+  float4 v[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u)
+    if (base + u * 1024 < L) v[u] = __ldcs(reinterpret_cast<const float4 *>(px + base + u * 1024));
+  float gs = 0.0f, ms = 0.0f;
   if (ROWS) {
-    const float gv = g[slice_offset(sc.g_keep, outer)], mv = m[slice_offset(sc.m_keep, outer)];
-    int hits = 0;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const bool eq = xv[e] == mv;
-      hits += eq ? 1 : 0;
-      res[e] = gv * (eq ? 1.0f : 0.0f);
-    }
-    if (hits) atomicAdd(count + outer, hits);
-  } else {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t c = inner + e;
-      const float gv = g[slice_offset(sc.g_keep, c)], mv = m[slice_offset(sc.m_keep, c)];
-      const bool eq = xv[e] == mv;
-      if (eq) atomicAdd(count + c, 1);
-      res[e] = gv * (eq ? 1.0f : 0.0f);
-    }
+    gs = g[slice_offset(sc.g_keep, outer)];
+    ms = m[slice_offset(sc.m_keep, outer)];
   }
-  __stcs(reinterpret_cast<float4 *>(out + outer * L + inner), make_float4(res[0], res[1], res[2], res[3]));
+  int hits = 0;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int64_t inner = base + u * 1024;
+    if (inner >= L) break;
+    const float xv[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+    float gv[4], mv[4];
+    if (ROWS) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) gv[e] = gs, mv[e] = ms;
+    } else if (gm_vec) { // g and m are dense vectors over the columns: one 128-bit load each
+      const float4 g4 = __ldg(reinterpret_cast<const float4 *>(g + inner)), m4 = __ldg(reinterpret_cast<const float4 *>(m + inner));
+      gv[0] = g4.x, gv[1] = g4.y, gv[2] = g4.z, gv[3] = g4.w;
+      mv[0] = m4.x, mv[1] = m4.y, mv[2] = m4.z, mv[3] = m4.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        gv[e] = g[slice_offset(sc.g_keep, inner + e)];
+        mv[e] = m[slice_offset(sc.m_keep, inner + e)];
+      }
+    }
+    float res[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const bool eq = xv[e] == mv[e];
+      if (ROWS) hits += eq ? 1 : 0;
+      else if (eq) atomicAdd(count + inner + e, 1);
+      res[e] = gv[e] * (eq ? 1.0f : 0.0f);
+    }
+    __stcs(reinterpret_cast<float4 *>(out + outer * L + inner), make_float4(res[0], res[1], res[2], res[3]));
+  }
+  if (ROWS && hits) atomicAdd(count + outer, hits);
 }
 
 // ROWS: one CTA per slice (n_slices CTAs), COLS: one thread per column.  Slices with a unique extremum -- all of
@@ -1013,9 +1031,9 @@ static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt
     }
     bool vec = (L % 4 == 0) && aligned16(xp) && aligned16(out);
     for (int k = 0; k < sc.x_keep.ndim; ++k) vec = vec && (sc.x_keep.strides[k] % 4 == 0);
-    const int64_t vchunks = ceil_div(L, 1024);
+    const int64_t vchunks = ceil_div(L, 4096);
     if (vec && pl.n_keep * vchunks <= 0x7fffffffLL) {
-      extremum_apply_count_vec<true><<<unsigned(pl.n_keep * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, L, 0, int(vchunks));
+      extremum_apply_count_vec<true><<<unsigned(pl.n_keep * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, L, 0, int(vchunks), 0);
       check_launch("extremum_apply_count_vec");
       extremum_fix_ties<true><<<unsigned(pl.n_keep), 256, 0, st>>>(xp, gp, mp, count, out, sc, pl.n_keep, L, 0);
       check_launch("extremum_fix_ties");
@@ -1040,9 +1058,11 @@ static bool extremum_backward_fused(const nt_view *g, const nt_view *x, const nt
       return false;
     }
     dim3 grid{unsigned(tiles), unsigned(row_blocks), 1};
-    const int64_t vchunks = ceil_div(C, 1024);
+    const int64_t vchunks = ceil_div(C, 4096);
     if (vec && R * vchunks <= 0x7fffffffLL) {
-      extremum_apply_count_vec<false><<<unsigned(R * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, C, sR, int(vchunks));
+      const int gm_vec = (sc.g_keep.ndim == 1 && sc.g_keep.strides[0] == 1 && sc.m_keep.ndim == 1 && sc.m_keep.strides[0] == 1 &&
+                          aligned16(gp) && aligned16(mp)) ? 1 : 0;
+      extremum_apply_count_vec<false><<<unsigned(R * vchunks), 256, 0, st>>>(xp, gp, mp, count, out, sc, C, sR, int(vchunks), gm_vec);
       check_launch("extremum_apply_count_vec");
       extremum_fix_ties<false><<<unsigned(ceil_div(C, 256)), 256, 0, st>>>(xp, gp, mp, count, out, sc, C, R, sR);
       check_launch("extremum_fix_ties");
