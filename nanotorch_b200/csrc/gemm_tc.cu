@@ -741,6 +741,12 @@ void gemm_tc_wait_probe() {
 // product and found again by the weight-gradient product, a gradient once for both of its products, a
 // weight once per update.  An entry is valid while the storage's mutation counter and the epoch (see
 // gemm_tc_new_epoch) are the ones it was written under; a stale entry is re-split into the same buffer.
+// Inside a graph capture an entry is trusted only if it was split within that same capture, or if it is
+// `maintained` -- last written by gemm_tc_refresh, i.e. it belongs to a parameter whose every update re-splits
+// it, inside the graph too.  Anything else (an input batch split by an eager warm-up step) is split again
+// inside the capture, so that a replay sees whatever the buffer holds by then.
+// A storage keeps at most PLANE_ENTRIES_PER_STORAGE entries (views at different offsets of one big tensor
+// would otherwise pile up); the oldest entry that no capture has used makes room.
 struct NatSplitArgs {
   const float *src;
   float *hi, *lo;
@@ -790,7 +796,10 @@ struct PlaneEntry {
   float *planes;
   size_t rounded;
   uint64_t mutation, epoch;
+  int capture = 0;         // id of the capture that last split it, 0 = split eagerly
+  bool maintained = false; // last written by gemm_tc_refresh
 };
+constexpr size_t PLANE_ENTRIES_PER_STORAGE = 32;
 static std::mutex g_plane_mu;
 static std::unordered_map<nt_storage *, std::vector<PlaneEntry>> g_plane_cache;
 static uint64_t g_plane_epoch = 1;
@@ -829,21 +838,34 @@ static float *natural_planes(nt_storage *s, int64_t offset, int64_t batch, int64
     run_split(s, e);
     return e.planes;
   }
+  const int cid = capture_id();
   std::lock_guard<std::mutex> lk(g_plane_mu);
   auto &list = g_plane_cache[s];
   for (PlaneEntry &e : list) {
     if (e.offset == offset && e.batch == batch && e.s_b == s_b && e.R == R && e.C == C && e.s_r == s_r) {
-      if (e.mutation == s->mutation && e.epoch == g_plane_epoch) {
+      const bool current = e.mutation == s->mutation && e.epoch == g_plane_epoch;
+      if (current && (cid == 0 || e.capture == cid || e.maintained)) {
         g_split_hits.fetch_add(1, std::memory_order_relaxed);
         return e.planes;
       }
       e.mutation = s->mutation;
       e.epoch = g_plane_epoch;
+      e.capture = cid;
+      e.maintained = false;
       run_split(s, e); // same buffer: a captured graph that reads it keeps reading the right place
       return e.planes;
     }
   }
-  PlaneEntry e{offset, batch, s_b, R, C, s_r, Cp, nullptr, 0, s->mutation, g_plane_epoch};
+  if (list.size() >= PLANE_ENTRIES_PER_STORAGE) {
+    for (size_t i = 0; i < list.size(); ++i) {
+      if (list[i].capture == 0 && !list[i].maintained) {
+        device_free(list[i].planes, list[i].rounded); // stream-ordered: earlier readers are already queued
+        list.erase(list.begin() + i);
+        break;
+      }
+    }
+  }
+  PlaneEntry e{offset, batch, s_b, R, C, s_r, Cp, nullptr, 0, s->mutation, g_plane_epoch, cid, false};
   e.planes = static_cast<float *>(device_alloc(bytes, &e.rounded));
   run_split(s, e);
   list.push_back(e);
@@ -855,9 +877,10 @@ static float *natural_planes(nt_storage *s, int64_t offset, int64_t batch, int64
 // and returns its hi plane (lo follows R * C values later); nullptr when the cache is off.
 float *gemm_tc_adopt_planes(nt_storage *s, int64_t R, int64_t C) {
   if (!g_operand_cache.load() || C % 32 != 0) return nullptr;
+  const int cid = capture_id();
   std::lock_guard<std::mutex> lk(g_plane_mu);
   auto &list = g_plane_cache[s];
-  PlaneEntry e{0, 1, 0, R, C, C, C, nullptr, 0, s->mutation, g_plane_epoch};
+  PlaneEntry e{0, 1, 0, R, C, C, C, nullptr, 0, s->mutation, g_plane_epoch, cid, false};
   e.planes = static_cast<float *>(device_alloc(size_t(2 * R * C) * 4, &e.rounded));
   list.push_back(e);
   return e.planes;
@@ -881,9 +904,12 @@ void gemm_tc_refresh(nt_storage *s) {
   if (g_plane_cache.empty()) return;
   auto it = g_plane_cache.find(s);
   if (it == g_plane_cache.end()) return;
+  const int cid = capture_id();
   for (PlaneEntry &e : it->second) {
     e.mutation = s->mutation;
     e.epoch = g_plane_epoch;
+    e.capture = cid;
+    e.maintained = true;
     run_split(s, e);
   }
 }

@@ -119,6 +119,7 @@ int gemm_tc_take_error();    // device-side error flag of the tensor-core GEMM (
 void check_device_errors();  // after a stream synchronisation: raises if a bounded device-side wait ran out
 long long wait_limit_clocks(); // limit of every bounded spin in device code, in SM clocks
 bool is_capturing();         // a CUDA-graph capture is in progress on the compute stream
+int capture_id();            // id of the graph being captured, 0 when none
 // Persistent device state that kernels expect to find zeroed (ticket counters of the reductions, the
 // error flag of the tensor-core GEMM) and one-off function attributes: created eagerly, never inside
 // a stream capture, where the zeroing would be recorded instead of executed.

@@ -142,6 +142,11 @@ cudaStream_t update_stream() {
   ensure_streams_locked(r);
   return r.update;
 }
+int capture_id() {
+  Runtime &r = rt();
+  std::lock_guard<std::mutex> lk(r.mu);
+  return r.capturing;
+}
 bool is_capturing() {
   Runtime &r = rt();
   std::lock_guard<std::mutex> lk(r.mu);

@@ -125,6 +125,57 @@ def test_captured_step_replays_bit_exact(nt):
         assert_bit_exact(a, b, "parameters after replayed steps")
 
 
+def test_replayed_step_reads_the_batch_its_buffers_hold_now(nt):
+    """A captured step is fed by writing the next batch into the same input buffers before each replay.
+    The split planes of an input that an eager warm-up step left behind must not be what the graph reads:
+    losses and parameters equal the eager run over the same sequence of batches, bit for bit."""
+    import nanotorch_b200.nn as nn
+
+    rng = np.random.default_rng(7)
+    xs = [rng.standard_normal((512, 640)).astype(np.float32) for _ in range(5)]
+    ys = [rng.standard_normal((512, 64)).astype(np.float32) for _ in range(5)]
+
+    def run(graph_mode: bool):
+        X = nt.Tensor.from_numpy(xs[0], "cuda")
+        Y = nt.Tensor.from_numpy(ys[0], "cuda")
+        model = build(nt, [640, 768, 64], nn.Tanh)
+        opt = nn.GradientDescent(model.parameters(), lr=1e-2)
+
+        def feed(i):
+            X.storage.upload(xs[i].ctypes.data, xs[i].nbytes)
+            Y.storage.upload(ys[i].ctypes.data, ys[i].nbytes)
+
+        def step():
+            loss = nt.mean((model(X) - Y) ** 2)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            return loss
+
+        losses = [float(step().numpy())]                  # eager warm-up on batch 0
+        if graph_mode:
+            g = nt._C.Graph()
+            with g.capture():
+                loss = step()
+            for i in range(1, 5):
+                feed(i)
+                g.replay()
+                losses.append(float(loss.numpy()))
+            g.close()
+        else:
+            for i in range(1, 5):
+                feed(i)
+                losses.append(float(step().numpy()))
+        return np.array(losses), [p.numpy() for p in model.parameters()]
+
+    eager_losses, eager_params = run(False)
+    graph_losses, graph_params = run(True)
+    assert len(set(eager_losses.tolist())) == 5
+    assert np.array_equal(eager_losses, graph_losses), (eager_losses, graph_losses)
+    for a, b in zip(eager_params, graph_params):
+        assert_bit_exact(a, b, "parameters after replays over fresh batches")
+
+
 @pytest.mark.parametrize("graph_mode", [False, True])
 def test_side_stream_update_equals_plain_sgd(nt, graph_mode):
     """DataParallelSGD with one rank: no collective, but every bucket's update runs on the communication
