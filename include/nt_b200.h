@@ -240,15 +240,24 @@ int nt_get_matmul_mode(void);
  * entry point of this library (in-place ops, sgd_update, uploads, copy_view, scatter, all-reduce): an
  * activation is split once for the forward product and the weight-gradient product, a gradient once for
  * its two products; nt_sgd_update / nt_comm_sgd_update re-split a weight that has been an operand right
- * behind the update.  A captured graph keeps the hit-or-miss decisions of its capture: do not write to a
- * parameter from outside the graph between replays.  Writes through nt_storage_data() pointers are not
- * seen.  nt_matmul_split_stats: operand-split launches and cache hits since load. */
+ * behind the update.  Inside a graph capture cached planes are trusted only when they were
+ * split inside that capture or belong to a parameter that the update keeps re-splitting; everything else
+ * (an input batch that an eager warm-up step had split) is split again inside the graph, so a replay reads
+ * what the input buffers hold at that moment.  Do not write to a parameter from outside the graph between
+ * replays other than through nt_sgd_update.  Each storage keeps at most 32 cached views.  Writes through
+ * nt_storage_data() pointers are not seen.  nt_matmul_split_stats: operand-split launches and cache hits since load. */
 int nt_set_matmul_operand_planes(int natural, int cached);
 /* on != 0 (default): nt_tanh and nt_tanh_backward, when their result is a dense 2-D Float32 matrix of at
  * least 2^20 elements whose rows are whole 128-byte lines, also write the result's TF32 planes and register
  * them in the cache above -- an activation or its gradient is then never read back by an operand split.
  * Costs 8 extra bytes written per element if no product ever uses the result. */
 int nt_set_producer_planes(int on);
+/* on != 0 (default): an elementwise op on Float32 operands of at least 2^20 elements, one of which is
+ * transposed over the last two dims (unit stride on the second-to-last), runs as a persistent kernel fed
+ * by TMA loads and drained by TMA stores when every operand fits a tensor map (16-byte aligned base and
+ * strides, no broadcast operand, at most one leading dim); 0: always the register-staged tile kernel.
+ * Same result bits either way.  Replaces the strided path of src/cpp/ops/elementwise.cu for such views. */
+int nt_set_transposed_tile_pipeline(int on);
 int nt_matmul_split_stats(uint64_t *split_launches, uint64_t *cache_hits);
 int nt_set_matmul_tc_min_macs(int64_t macs);
 int64_t nt_get_matmul_tc_min_macs(void);

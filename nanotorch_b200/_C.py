@@ -628,6 +628,12 @@ def set_producer_planes(on: bool = True) -> None:
     _check(_lib.nt_set_producer_planes(int(bool(on))))
 
 
+def set_transposed_tile_pipeline(on: bool = True) -> None:
+    """Large fp32 elementwise ops with a transposed operand: TMA-fed persistent kernel (default) or the
+    register-staged tile kernel (see the header)."""
+    _check(_lib.nt_set_transposed_tile_pipeline(int(bool(on))))
+
+
 def matmul_split_stats() -> tuple[int, int]:
     """(operand-split launches, operand-plane cache hits) since load."""
     a, b = C.c_uint64(0), C.c_uint64(0)

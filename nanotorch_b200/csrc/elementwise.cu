@@ -331,6 +331,7 @@ template <class F> static nt_storage *fused2(F f, const nt_view *a, const nt_vie
 // A producer of GEMM operands (an activation, its gradient): a dense 2-D fp32 result, large enough for the
 // tensor-core path, with rows that are whole 128-byte lines -- it writes its own TF32 planes (ew_contig_planes)
 // and registers them in the operand-plane cache, so the products that follow find them ready.
+std::atomic<int> g_tile_pipeline{1};
 static std::atomic<int> g_producer_planes{1};
 static bool dense_2d(const nt_view *v) {
   return v->ndim == 2 && v->strides[1] == 1 && v->strides[0] == v->shape[1] && v->storage->dtype == NT_FLOAT32 &&
@@ -482,6 +483,11 @@ int nt_tanh(const nt_view *x, nt_storage **out) {
   check_view(x, "tanh");
   if (g_tanh_mode.load() == 0 && (*out = produce_with_planes<TanhF<float>, 1>(TanhF<float>{}, x, nullptr))) return NT_OK;
   *out = (g_tanh_mode.load() == 1) ? unary_impl<TanhExactF, 0>(x, "tanh") : unary_impl<TanhF, 0>(x, "tanh");
+  NT_API_END
+}
+int nt_set_transposed_tile_pipeline(int on) {
+  NT_API_BEGIN
+  g_tile_pipeline.store(on ? 1 : 0);
   NT_API_END
 }
 int nt_set_producer_planes(int on) {

@@ -17,6 +17,12 @@
 // divisions per element per operand (src/cpp/tensor_view.cuh:43-52) with 4-byte accesses.
 #pragma once
 
+#include <algorithm>
+#include <atomic>
+#include <cstdlib>
+#include <type_traits>
+
+#include "ew_tile_tma.cuh"
 #include "nt_core.cuh"
 #include "tf32_split.cuh"
 
@@ -425,6 +431,69 @@ __global__ void __launch_bounds__(256, 4) ew_tile2d(F f, EwParams p) {
 // Host-side planner + launcher.
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Large fp32 operands with a transposed one among them go through the copy-engine pipeline of
+// ew_tile_tma.cuh when every operand can be described by a tensor map: unit stride along J (row-major) or
+// along I (column-major), all other strides and the base 16-byte aligned, no broadcast operand, at most one
+// leading dim.  Returns false when the case does not qualify (the register-staged tile kernel takes it).
+extern std::atomic<int> g_tile_pipeline; // nt_set_transposed_tile_pipeline
+template <class F, int NIN>
+bool ew_launch_tile_pipeline(F f, const IterSpace<NIN + 1> &it, float *out, const float *const *in, const int *col_major) {
+  if (!g_tile_pipeline.load(std::memory_order_relaxed)) return false;
+  if (it.ndim != 2 && it.ndim != 3) return false;
+  const int dI = it.ndim - 2, dJ = it.ndim - 1;
+  const int64_t nI = it.shape[dI], nJ = it.shape[dJ], lead = it.ndim == 3 ? it.shape[0] : 1;
+  if (nI < 64 || nJ < 64 || it.numel < (int64_t(1) << 20) || nI > 0x7fffffffLL || nJ > 0x7fffffffLL || lead > 0x7fffffffLL)
+    return false;
+  constexpr int64_t MAX_STRIDE = int64_t(1) << 37; // elements: 2^39 bytes, below the 2^40 of a tensor map
+  for (int o = 0; o <= NIN; ++o) {
+    const void *base = o == 0 ? static_cast<const void *>(out) : static_cast<const void *>(in[o - 1]);
+    if (!aligned16(base)) return false;
+    const bool col = o > 0 && col_major[o] != 0;
+    const int64_t unit = it.strides[o][col ? dI : dJ], other = it.strides[o][col ? dJ : dI];
+    if (unit != 1 || other <= 0 || (other & 3) != 0 || other >= MAX_STRIDE) return false;
+    if (it.ndim == 3) {
+      const int64_t ls = it.strides[o][0];
+      if (ls <= 0 || (ls & 3) != 0 || ls >= MAX_STRIDE) return false;
+    }
+  }
+  auto map_of = [&](int o) {
+    const void *base = o == 0 ? static_cast<const void *>(out) : static_cast<const void *>(in[o - 1]);
+    const bool col = o > 0 && col_major[o] != 0;
+    const int64_t other = it.strides[o][col ? dJ : dI];
+    const int64_t inner = col ? nI : nJ, rows = col ? nJ : nI;
+    const int64_t ls = it.ndim == 3 ? it.strides[o][0] : other * rows;
+    return tile_tma::make_map(base, inner, rows, lead, other, ls);
+  };
+  tile_tma::Args a{};
+  a.tiles_i = int32_t(ceil_div(nI, tile_tma::T));
+  a.tiles_j = int32_t(ceil_div(nJ, tile_tma::T));
+  static const int group_log2 = [] {
+    const char *e = getenv("NT_TILE_GROUP_LOG2");
+    const int v = (e && *e) ? atoi(e) : 2;
+    return v < 0 ? 0 : (v > 6 ? 6 : v);
+  }();
+  const int G = 1 << group_log2;
+  a.group_log2 = group_log2;
+  a.groups_j = (a.tiles_j + G - 1) / G;
+  a.slots_per_lead = int64_t(G) * G * ((a.tiles_i + G - 1) / G) * a.groups_j;
+  a.total = a.slots_per_lead * lead;
+  for (int o = 0; o < NIN; ++o) a.col[o] = col_major[o + 1] != 0;
+  a.wait_limit = wait_limit_clocks();
+  a.error_flag = pipeline_error_flag();
+  const CUtensorMap m_out = map_of(0), m0 = map_of(1), m1 = map_of(NIN == 2 ? 2 : 1);
+  const size_t smem = tile_tma::smem_bytes(NIN);
+  static bool configured = false; // one per instantiation
+  if (!configured) {
+    NT_CUDA_CHECK(cudaFuncSetAttribute(tile_tma::ew_tile_tma<F, NIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    configured = true;
+  }
+  const int64_t tiles = int64_t(a.tiles_i) * a.tiles_j * lead;
+  const unsigned grid = unsigned(std::min<int64_t>(tiles, sm_count()));
+  tile_tma::ew_tile_tma<F, NIN><<<grid, tile_tma::THREADS, smem, stream()>>>(f, m_out, m0, m1, a);
+  check_launch("ew_tile_tma");
+  return true;
+}
+
 // views[0] is the output view (for fresh outputs: contiguous, offset 0).
 template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NIN + 1]) {
   using TI = typename F::in_t;
@@ -500,6 +569,9 @@ template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NI
             p.vec_mode[o] = vec_ok(o, dI) ? 1 : 0;
           else
             p.vec_mode[o] = vec_ok(o, dJ) ? 1 : 0;
+        }
+        if constexpr (NIN <= 2 && std::is_same<TI, float>::value && std::is_same<TO, float>::value) {
+          if (ew_launch_tile_pipeline<F, NIN>(f, it, out, in, p.col_major)) return;
         }
         dim3 grid(unsigned(ceil_div(it.shape[dJ], TILE)), unsigned(ceil_div(it.shape[dI], TILE)), unsigned(lead));
         const size_t smem = size_t(n_col) * TILE * TILE_PITCH * sizeof(TI); // at most 2 slots = 33 KB: below the 48 KB default limit

@@ -28,11 +28,14 @@
 // kernels, for fp32 operands.
 #include <cuda.h>
 
+#include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
 #include "nt_core.cuh"
 #include "tf32_split.cuh"
+#include "tma.cuh"
 
 namespace ntb {
 
@@ -131,45 +134,7 @@ __global__ void __launch_bounds__(256) split_pack(SplitArgs a) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// PTX wrappers
-__device__ __forceinline__ uint32_t smem_u32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile("{\n\t.reg .pred p;\n\t"
-               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-               "selp.u32 %0, 1, 0, p;\n\t}"
-               : "=r"(ok)
-               : "r"(bar), "r"(parity)
-               : "memory");
-  return ok != 0;
-}
-// Bounded wait: returns false when the barrier did not flip within `limit` SM clocks (2^31 unless the
-// host lowered it with nt_set_wait_limit_clocks).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > limit) return false;
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-               : "memory");
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int c0, int c1, int c2, int c3) {
-  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-               : "memory");
-}
+// PTX wrappers (the mbarrier and TMA ones are in tma.cuh)
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -230,7 +195,28 @@ struct TcArgs {
   int *error_flag;
   long long wait_limit; // SM clocks a pipeline wait may take before the kernel gives up
   uint32_t mn_lbo, mn_sbo; // byte offsets of the MN-major descriptors (see umma_desc_mn_sw128)
+  int32_t panel;           // promoted kernel: tiles are walked in panels this many n-tiles wide (0 = row by row)
 };
+
+// Output tile of this CTA.  CTAs are dispatched in the order of their linear index (x fastest); walking the
+// n-tiles of a whole row before the next m-tile makes every wave of CTAs touch all of B, which at these
+// sizes (two planes of B: 134 MB for 4096 x 4096) no longer fits the L2 and is fetched from DRAM once per
+// wave.  With panels of `panel` n-tiles a wave covers more m-tiles and fewer n-tiles, and a panel's slice of
+// B stays in the L2 while the CTAs walk down the m-tiles.
+__device__ __forceinline__ void tile_of_cta(const TcArgs &g, int &tm, int &tn) {
+  tm = blockIdx.y;
+  tn = blockIdx.x;
+  if (g.panel > 0) {
+    const int tiles_n = gridDim.x, tiles_m = gridDim.y;
+    const int lin = tm * tiles_n + tn;
+    const int per_panel = g.panel * tiles_m;
+    const int p = lin / per_panel;
+    const int within = lin - p * per_panel;
+    const int pw = min(g.panel, tiles_n - p * g.panel);
+    tm = within / pw;
+    tn = p * g.panel + within % pw;
+  }
+}
 
 __global__ void __launch_bounds__(192, 1)
 gemm_3xtf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TcArgs g) {
@@ -440,7 +426,9 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   volatile int *poison_slot = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN, b = blockIdx.z;
+  int tile_m, tile_n;
+  tile_of_cta(g, tile_m, tile_n);
+  const int m0 = tile_m * TC_BM, n0 = tile_n * TC_BN, b = blockIdx.z;
   const int num_periods = (g.num_kb + TC_PERIOD_KB - 1) / TC_PERIOD_KB;
 
   if (threadIdx.x == 0) {
@@ -626,11 +614,7 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
 
 // ---------------------------------------------------------------------------------------------
 // Host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
+EncodeTiledFn tensor_map_encoder() {
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void *p = nullptr;
@@ -641,6 +625,7 @@ static EncodeTiledFn encode_fn() {
   }
   return fn;
 }
+static EncodeTiledFn encode_fn() { return tensor_map_encoder(); }
 
 // planes: [2 * batch][rows][Kp] fp32, K-major; box = 16 k x box_rows rows.
 static CUtensorMap make_map(float *planes, int64_t rows, int64_t Kp, int64_t batch2, uint32_t box_rows) {
@@ -656,7 +641,21 @@ static CUtensorMap make_map(float *planes, int64_t rows, int64_t Kp, int64_t bat
   return m;
 }
 
+// Width of the tile panels of the promoted kernel in n-tiles (8 x 256 columns: that slice of a 4096-deep B
+// is 67 MB of planes).  NT_GEMM_PANEL overrides it, 0 = off.
+static int panel_default() {
+  const char *e = getenv("NT_GEMM_PANEL");
+  if (e && *e) {
+    const int v = atoi(e);
+    return v < 0 ? 0 : v;
+  }
+  return 8;
+}
+static std::atomic<int> g_tc_panel{panel_default()};
+
 static int *g_error_flag = nullptr;
+static int *error_flag_ptr();
+int *pipeline_error_flag() { return error_flag_ptr(); }
 static int *error_flag_ptr() {
   int *&flag = g_error_flag;
   if (!flag) {
@@ -1015,6 +1014,11 @@ bool gemm_3xtf32_natural(nt_storage *sa, int64_t a_off, nt_storage *sb, int64_t 
     g.wait_limit = wait_limit_clocks();
     g.mn_lbo = TC_MN_LBO;
     g.mn_sbo = TC_MN_SBO;
+    {
+      const int64_t tiles_n = ceil_div(N, TC_BN), tiles_m = ceil_div(M, TC_BM);
+      const int panel = g_tc_panel.load(std::memory_order_relaxed);
+      g.panel = (panel > 0 && tiles_n > panel && tiles_n * tiles_m < (int64_t(1) << 30)) ? panel : 0;
+    }
     g.bias = bias;
     g.bias_stride = bias ? bias_stride : 0;
     if (bias && bias_done) *bias_done = true;

@@ -156,10 +156,11 @@ long long wait_limit_clocks() { return rt().wait_limit.load(std::memory_order_re
 void check_device_errors() {
   const int tc_err = gemm_tc_take_error();
   if (tc_err != 0)
-    fail_runtime("gemm_3xtf32: a bounded device-side wait ran out (code " + std::to_string(tc_err) +
-                 ": 1 = producer waiting for a free stage, 2 = MMA waiting for data, 3 = epilogue waiting for "
-                 "the accumulator, 4 = MMA waiting for a drained accumulator, 5 = the wait probe); results of "
-                 "the launches since the last synchronisation are invalid.");
+    fail_runtime("a bounded device-side wait ran out (code " + std::to_string(tc_err) +
+                 "; gemm_3xtf32: 1 = producer waiting for a free stage, 2 = MMA waiting for data, 3 = epilogue "
+                 "waiting for the accumulator, 4 = MMA waiting for a drained accumulator; 5 = the wait probe; "
+                 "6 = the elementwise tile pipeline waiting for a tile); results of the launches since the last "
+                 "synchronisation are invalid.");
 }
 int sm_count() {
   Runtime &r = rt();

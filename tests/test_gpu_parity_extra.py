@@ -433,3 +433,49 @@ def test_binary_backward_both_gradients_in_one_pass(nt, port, op):
         assert_scaled(t2.grad.numpy(), want, np.abs(want) + 1e-30, 2.0 ** -21, "dx2")
     both = getattr(nt._C, f"{op}_backward")(dev(nt, g)._C_view, t1._C_view, t2.T._C_view)
     assert both is None, "a transposed operand is not a dense run: the composed kernels take it"
+
+
+TILE_PIPELINE_SHAPES = [(1100, 1004), (4096, 4096), (64, 16384), (16384, 64), (3, 520, 772), (1028, 1500)]
+
+
+@pytest.mark.parametrize("shape", TILE_PIPELINE_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_transposed_operands_through_the_tile_pipeline(nt, shape):
+    """Large fp32 elementwise ops with a transposed operand (TMA-fed persistent kernel): edge tiles in both
+    dims, a leading dim, sliced operands whose row stride is not their width, one and two transposed
+    operands, unary and binary.  Bit-equal to numpy for the exact ops, and to the register-staged tile
+    kernel (pipeline off) for all of them."""
+    _C = nt._C
+    rng = np.random.default_rng(sum(shape))
+    *lead, nI, nJ = shape
+    a_np = rng.standard_normal(shape).astype(np.float32)
+    bt_np = rng.standard_normal((*lead, nJ, nI)).astype(np.float32)       # holds b transposed
+    ct_np = rng.standard_normal((*lead, nJ, nI + 8)).astype(np.float32)   # wider: sliced below
+    a, bt, ct = dev(nt, a_np), dev(nt, bt_np), dev(nt, ct_np)
+    d0, d1 = len(shape) - 2, len(shape) - 1
+    b = nt.transpose(bt, d0, d1)
+    c = nt.transpose(ct[..., 4:nI + 4], d0, d1)                                # 16-byte aligned offset, stride nI + 8
+    b_ref, c_ref = np.swapaxes(bt_np, -1, -2), np.swapaxes(ct_np[..., 4:nI + 4], -1, -2)
+
+    def run():
+        return {
+            "a+b.T": (a + b).numpy(),
+            "b.T-a": (b - a).numpy(),
+            "b.T*c.T": (b * c).numpy(),
+            "a/c.T": (a / c).numpy(),
+            "exp(b.T)": nt.exp(b).numpy(),
+            "relu(c.T)": nt.relu(c).numpy(),
+        }
+
+    on = run()
+    _C.set_transposed_tile_pipeline(False)
+    try:
+        off = run()
+    finally:
+        _C.set_transposed_tile_pipeline(True)
+    assert_bit_exact(on["a+b.T"], a_np + b_ref, "a + b.T")
+    assert_bit_exact(on["b.T-a"], b_ref - a_np, "b.T - a")
+    assert_bit_exact(on["b.T*c.T"], b_ref * c_ref, "b.T * c.T")
+    assert_bit_exact(on["a/c.T"], a_np / c_ref, "a / c.T")
+    assert_bit_exact(on["relu(c.T)"], np.maximum(c_ref, 0), "relu(c.T)")
+    for k in on:
+        assert_bit_exact(on[k], off[k], k + ": pipeline against the register-staged kernel")
