@@ -1057,12 +1057,12 @@ def product_arm(args, rank: int, local_rank: int, world: int) -> None:
 
 
 # (15 * 2882.6 MB + 8 * 3027.4 MB) / 23: forward / input-gradient shape and weight-gradient shape of the step
-GEMM_TRAFFIC_BYTES_PER_LAUNCH = 2.933e9
-GEMM_TRAFFIC_SOURCE = "profiles/gemm_3xtf32_step_shapes_dram_traffic.md (ncu, second capture: one launch per shape)"
+GEMM_TRAFFIC_BYTES_PER_LAUNCH = 2.422e9
+GEMM_TRAFFIC_SOURCE = "profiles/gemm_3xtf32_step_shapes_dram_traffic.md (ncu, third capture: one launch per shape)"
 # fp32 operands read once, hi/lo planes written and read once, output written once, same 15 : 8 weighting
 GEMM_ALGORITHMIC_BYTES_PER_LAUNCH = (15 * 939.5e6 + 8 * 1140.9e6) / 23
 
-PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
+PROFILE_CASES = ("gemm4096", "add4096", "add4096_transposed", "pow2_4096_transposed", "add4096_broadcast", "tanh4096", "tanh4096_exact", "exp4096",
                  "sigmoid4096", "sum8192_dim0", "sum8192_dim1", "sum8192_full", "max_backward8192", "gather8192_rows", "gemm_step_shapes",
                  "sgemm4096", "max_backward8192_dim0", "sum_short_rows", "sgd4096", "cast4096", "scatter8192_ordered", "add_sliced_3d",
                  "mean8192_dim1", "mlp_step_16384", "mlp_step_2048", "mul_backward4096")
@@ -1093,6 +1093,9 @@ def profile_case(name: str, launches: int = 3) -> None:
         v = dev(r(13).uniform(-1, 1, (4096,)))
         other = {"add4096": b, "add4096_transposed": b.T, "add4096_broadcast": v.expand(4096, 4096)}[name]
         fn = lambda: _C.add(a._C_view, other._C_view)  # noqa: E731
+    elif name == "pow2_4096_transposed":
+        a = dev(r(10).uniform(-1, 1, (4096, 4096)))
+        fn = lambda: _C.pow(a.T._C_view, 2.0)  # noqa: E731
     elif name == "max_backward8192":
         x = dev(r(20).standard_normal((8192, 8192)))
         m = x.max((1,)).reshape(8192, 1).expand(8192, 8192)

@@ -54,6 +54,12 @@ __device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, uint32_t sr
                ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2)
                : "memory");
 }
+// Brings a box of a tensor into the L2 only (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_l2_3d(const CUtensorMap *map, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global.tile [%0, {%1, %2, %3}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the shared-memory sources of all but the PENDING latest of this thread's committed stores have been read.
 template <int PENDING> __device__ __forceinline__ void tma_store_wait_read() {
