@@ -259,6 +259,12 @@ int nt_set_producer_planes(int on);
  * Same result bits either way.  Replaces the strided path of src/cpp/ops/elementwise.cu for such views. */
 int nt_set_transposed_tile_pipeline(int on);
 int nt_matmul_split_stats(uint64_t *split_launches, uint64_t *cache_hits);
+/* Scheduling of the mode-1 tensor-core kernel.  max_splits (1..8, default 8; NT_GEMM_SPLITK): a product with
+ * so few output tiles that most SMs would idle (tiles x splits still within one wave of CTAs) is cut along k
+ * into up to that many parts per tile, each at least 512 long; the parts' fp32 sums are added in part order
+ * by the CTA that finishes last, so the result does not depend on timing.  1 = never.  panel (default 8;
+ * NT_GEMM_PANEL): width in n-tiles of the panels the CTAs walk the output in, 0 = row by row. */
+int nt_set_matmul_schedule(int max_splits, int panel);
 int nt_set_matmul_tc_min_macs(int64_t macs);
 int64_t nt_get_matmul_tc_min_macs(void);
 

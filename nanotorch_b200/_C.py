@@ -628,6 +628,11 @@ def set_producer_planes(on: bool = True) -> None:
     _check(_lib.nt_set_producer_planes(int(bool(on))))
 
 
+def set_matmul_schedule(max_splits: int = 8, panel: int = 8) -> None:
+    """Split-K limit and tile-panel width of the mode-1 tensor-core kernel (see the header)."""
+    _check(_lib.nt_set_matmul_schedule(int(max_splits), int(panel)))
+
+
 def set_transposed_tile_pipeline(on: bool = True) -> None:
     """Large fp32 elementwise ops with a transposed operand: TMA-fed persistent kernel (default) or the
     register-staged tile kernel (see the header)."""

@@ -196,6 +196,12 @@ struct TcArgs {
   long long wait_limit; // SM clocks a pipeline wait may take before the kernel gives up
   uint32_t mn_lbo, mn_sbo; // byte offsets of the MN-major descriptors (see umma_desc_mn_sw128)
   int32_t panel;           // promoted kernel: tiles are walked in panels this many n-tiles wide (0 = row by row)
+  // promoted kernel, split-K: `splits` CTAs share an output tile, each over kb_per_split k-blocks; they leave
+  // their sums in `partials` ([tile][split][32 chunks][256 threads][4]) and the one that draws the last ticket
+  // adds them up in split order.  splits == 1: one CTA per tile, no workspace.
+  int32_t splits, kb_per_split;
+  float *partials;
+  unsigned int *tickets;
 };
 
 // Output tile of this CTA.  CTAs are dispatched in the order of their linear index (x fastest); walking the
@@ -203,11 +209,13 @@ struct TcArgs {
 // sizes (two planes of B: 134 MB for 4096 x 4096) no longer fits the L2 and is fetched from DRAM once per
 // wave.  With panels of `panel` n-tiles a wave covers more m-tiles and fewer n-tiles, and a panel's slice of
 // B stays in the L2 while the CTAs walk down the m-tiles.
-__device__ __forceinline__ void tile_of_cta(const TcArgs &g, int &tm, int &tn) {
+__device__ __forceinline__ void tile_of_cta(const TcArgs &g, int &tm, int &tn, int &split) {
+  const int splits = g.splits > 1 ? g.splits : 1;
   tm = blockIdx.y;
-  tn = blockIdx.x;
+  tn = blockIdx.x / splits; // the CTAs of one tile are neighbours in the dispatch order: their partial sums meet in the L2
+  split = blockIdx.x - tn * splits;
   if (g.panel > 0) {
-    const int tiles_n = gridDim.x, tiles_m = gridDim.y;
+    const int tiles_n = gridDim.x / splits, tiles_m = gridDim.y;
     const int lin = tm * tiles_n + tn;
     const int per_panel = g.panel * tiles_m;
     const int p = lin / per_panel;
@@ -426,10 +434,13 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   volatile int *poison_slot = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int tile_m, tile_n;
-  tile_of_cta(g, tile_m, tile_n);
+  int tile_m, tile_n, split;
+  tile_of_cta(g, tile_m, tile_n, split);
   const int m0 = tile_m * TC_BM, n0 = tile_n * TC_BN, b = blockIdx.z;
-  const int num_periods = (g.num_kb + TC_PERIOD_KB - 1) / TC_PERIOD_KB;
+  // this CTA's share of the contraction: k-blocks [kb0, kb0 + nkb)
+  const int kb0 = g.splits > 1 ? split * g.kb_per_split : 0;
+  const int nkb = g.splits > 1 ? min(g.kb_per_split, g.num_kb - kb0) : g.num_kb;
+  const int num_periods = (nkb + TC_PERIOD_KB - 1) / TC_PERIOD_KB;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < TC_STAGES; ++s) {
@@ -442,6 +453,7 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     *poison_slot = *reinterpret_cast<volatile int *>(g.error_flag); // see gemm_3xtf32_kernel
+    poison_slot[1] = 0; // split-K: an epilogue warp gave up
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
@@ -457,14 +469,14 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     if (lane == 0 && !poisoned) {
       uint32_t phase = 0;
       int s = 0;
-      for (int kb = 0; kb < g.num_kb; ++kb) {
+      for (int kb = 0; kb < nkb; ++kb) {
         if (!mbar_wait(empty0 + 8 * s, phase ^ 1, g.wait_limit)) {
           atomicExch(g.error_flag, 1);
           break;
         }
         const uint32_t st = smem_base + s * TC_STAGE_BYTES;
         mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
-        const int k = kb * TC_BK;
+        const int k = (kb0 + kb) * TC_BK;
         if constexpr (A_MN) {
           tma_load_4d(st, &map_a, full0 + 8 * s, 0, k, m0 >> 5, b);
           tma_load_4d(st + TC_A_PLANE_BYTES, &map_a, full0 + 8 * s, 0, k, m0 >> 5, g.batch + b);
@@ -500,7 +512,7 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
         }
         tcgen05_fence_after();
         const uint32_t d = tmem_acc + uint32_t(buf * TC_BN);
-        const int kb_end = min(kb + TC_PERIOD_KB, g.num_kb);
+        const int kb_end = min(kb + TC_PERIOD_KB, nkb);
         bool first = true;
         for (; kb < kb_end; ++kb) {
           if (!mbar_wait(full0 + 8 * s, phase, g.wait_limit)) {
@@ -575,6 +587,50 @@ gemm_3xtf32_promoted_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
     }
     const int64_t m = int64_t(m0) + quad * 32 + lane;
+    if (g.splits > 1 && !poisoned) {
+      // Split-K: leave this CTA's sums in the workspace; whoever draws the tile's last ticket adds the
+      // partial sums up in split order (the order never depends on which CTA finishes last).  All eight
+      // epilogue warps pass the two barriers whatever happened to them; a warp whose wait ran out says so.
+      volatile int *fail_slot = poison_slot + 1;
+      volatile unsigned int *ticket_slot = reinterpret_cast<volatile unsigned int *>(poison_slot + 2);
+      const int et = int(threadIdx.x) - 64; // 0..255 among the epilogue threads
+      const int64_t tile_lin = (int64_t(b) * gridDim.y + tile_m) * (gridDim.x / g.splits) + tile_n;
+      float *mine = g.partials + ((tile_lin * g.splits + split) * 32 * 256 + et) * 4;
+      if (!ok) *fail_slot = 1;
+      if (ok && m < g.M) {
+#pragma unroll
+        for (int q = 0; q < 32; ++q)
+          __stcg(reinterpret_cast<float4 *>(mine + q * 1024), make_float4(sum[4 * q], sum[4 * q + 1], sum[4 * q + 2], sum[4 * q + 3]));
+      }
+      __threadfence();
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (et == 0) *ticket_slot = (*fail_slot != 0) ? 0xffffffffu : atomicAdd(g.tickets + tile_lin, 1u);
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const unsigned int ticket = *ticket_slot;
+      ok = ok && ticket == unsigned(g.splits - 1);
+      if (ok) {
+        __threadfence();
+        if (m < g.M) {
+          const float *first = g.partials + (tile_lin * g.splits * 32 * 256 + et) * 4;
+#pragma unroll
+          for (int q = 0; q < 32; ++q) {
+            float4 acc = __ldcg(reinterpret_cast<const float4 *>(first + q * 1024));
+            for (int sp = 1; sp < g.splits; ++sp) {
+              const float4 v = __ldcg(reinterpret_cast<const float4 *>(first + int64_t(sp) * 32 * 256 * 4 + q * 1024));
+              acc.x += v.x;
+              acc.y += v.y;
+              acc.z += v.z;
+              acc.w += v.w;
+            }
+            sum[4 * q] = acc.x;
+            sum[4 * q + 1] = acc.y;
+            sum[4 * q + 2] = acc.z;
+            sum[4 * q + 3] = acc.w;
+          }
+        }
+        if (et == 0) g.tickets[tile_lin] = 0; // ready for the next launch
+      }
+    }
     if (ok && m < g.M) {
       float *crow = g.C + (int64_t(b) * g.M + m) * g.N;
       const int64_t n = int64_t(n0) + half * 128;
@@ -653,6 +709,20 @@ static int panel_default() {
 }
 static std::atomic<int> g_tc_panel{panel_default()};
 
+// Split-K tickets: one counter per output tile, zero between launches (the CTA that draws the last ticket of a
+// tile resets it).  GEMM launches are ordered on the compute stream, so one array serves them all.
+constexpr int64_t TC_MAX_TICKETS = 65536;
+static unsigned int *g_tickets = nullptr;
+static int max_splits_default() {
+  const char *e = getenv("NT_GEMM_SPLITK");
+  if (e && *e) {
+    const int v = atoi(e);
+    return v < 1 ? 1 : (v > 8 ? 8 : v);
+  }
+  return 8;
+}
+static std::atomic<int> g_tc_max_splits{max_splits_default()};
+
 static int *g_error_flag = nullptr;
 static int *error_flag_ptr();
 int *pipeline_error_flag() { return error_flag_ptr(); }
@@ -675,7 +745,10 @@ int gemm_tc_take_error() {
   if (!flag) return 0; // the kernel never ran
   int host = 0;
   if (cudaMemcpy(&host, flag, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
-  if (host != 0) cudaMemset(flag, 0, sizeof(int));
+  if (host != 0) {
+    cudaMemset(flag, 0, sizeof(int));
+    if (g_tickets) cudaMemset(g_tickets, 0, size_t(TC_MAX_TICKETS) * 4); // tiles that never completed left theirs behind
+  }
   return host;
 }
 
@@ -709,6 +782,13 @@ void gemm_tc_prepare() {
     configured = true;
   }
   error_flag_ptr();
+  if (!g_tickets) {
+    if (is_capturing())
+      fail_runtime("gemm_3xtf32: first use inside a graph capture; run the step once eagerly before capturing it.");
+    size_t rounded;
+    g_tickets = static_cast<unsigned int *>(device_alloc(size_t(TC_MAX_TICKETS) * 4, &rounded));
+    NT_CUDA_CHECK(cudaMemsetAsync(g_tickets, 0, size_t(TC_MAX_TICKETS) * 4, stream()));
+  }
 }
 
 // One CTA, one thread: the same bounded wait the GEMM pipeline uses, on a barrier that nothing ever
@@ -919,6 +999,10 @@ void gemm_tc_new_epoch() {
 }
 
 void gemm_tc_set_operand_cache(bool on) { g_operand_cache.store(on ? 1 : 0); }
+void gemm_tc_set_schedule(int max_splits, int panel) {
+  g_tc_max_splits.store(max_splits < 1 ? 1 : (max_splits > 8 ? 8 : max_splits));
+  g_tc_panel.store(panel < 0 ? 0 : panel);
+}
 void gemm_tc_split_stats(uint64_t *launches, uint64_t *hits) {
   *launches = g_split_launches.load();
   *hits = g_split_hits.load();
@@ -1014,21 +1098,45 @@ bool gemm_3xtf32_natural(nt_storage *sa, int64_t a_off, nt_storage *sb, int64_t 
     g.wait_limit = wait_limit_clocks();
     g.mn_lbo = TC_MN_LBO;
     g.mn_sbo = TC_MN_SBO;
+    const int64_t tiles_n = ceil_div(N, TC_BN), tiles_m = ceil_div(M, TC_BM);
     {
-      const int64_t tiles_n = ceil_div(N, TC_BN), tiles_m = ceil_div(M, TC_BM);
       const int panel = g_tc_panel.load(std::memory_order_relaxed);
       g.panel = (panel > 0 && tiles_n > panel && tiles_n * tiles_m < (int64_t(1) << 30)) ? panel : 0;
+    }
+    // Split-K for products that leave most SMs without a tile (a skinny output with a long contraction: 4
+    // tiles at 256 x 8192 x 512): up to max_splits CTAs share a tile while tiles x splits still fit one wave.
+    // Not for wave quantisation of larger products: measured on the 2048-row training step (256 tiles on 148
+    // SMs, 2 waves against 1.75 with four k-quarters) the split costs more than it saves, 10.4 ms per step
+    // against 8.3 -- four short pipelines with four epilogues and 134 MB of partial sums per launch.
+    size_t part_owned = 0;
+    g.splits = 1;
+    {
+      const int64_t tiles = tiles_m * tiles_n * batch;
+      const int sms = sm_count();
+      const int max_splits = g_tc_max_splits.load(std::memory_order_relaxed);
+      for (int sp = 2; sp <= max_splits && tiles <= TC_MAX_TICKETS; ++sp) {
+        const int per = int(ceil_div(ceil_div(int64_t(g.num_kb), int64_t(sp)), int64_t(TC_PERIOD_KB))) * TC_PERIOD_KB;
+        if (per < 2 * TC_PERIOD_KB || int64_t(sp - 1) * per >= g.num_kb) continue; // at least 512 of k each, none empty
+        if (tiles * sp > sms) break;
+        g.splits = sp;
+        g.kb_per_split = per;
+      }
+      if (g.splits > 1) {
+        g.partials = static_cast<float *>(device_alloc(size_t(tiles) * g.splits * TC_BM * TC_BN * 4, &part_owned));
+        g.tickets = g_tickets;
+      }
     }
     g.bias = bias;
     g.bias_stride = bias ? bias_stride : 0;
     if (bias && bias_done) *bias_done = true;
-    dim3 grid{unsigned(ceil_div(N, TC_BN)), unsigned(ceil_div(M, TC_BM)), unsigned(batch)};
+    dim3 grid{unsigned(tiles_n * g.splits), unsigned(tiles_m), unsigned(batch)};
     matmul_profile_begin();
     if (a_mn && b_mn) launch_promoted<true, true>(map_a, map_b, g, grid);
     else if (a_mn) launch_promoted<true, false>(map_a, map_b, g, grid);
     else if (b_mn) launch_promoted<false, true>(map_a, map_b, g, grid);
     else launch_promoted<false, false>(map_a, map_b, g, grid);
     matmul_profile_end();
+    if (part_owned) device_free(g.partials, part_owned); // stream-ordered like the operand planes
     check_launch("gemm_3xtf32_promoted_kernel");
   } catch (...) {
     if (a_owned) device_free(pa, a_owned);

@@ -28,6 +28,7 @@ bool gemm_3xtf32_natural(nt_storage *sa, int64_t a_off, nt_storage *sb, int64_t 
                          int64_t N, int64_t K, int64_t a_sb, int64_t a_sm, int64_t a_sk, int64_t b_sb, int64_t b_sk,
                          int64_t b_sn, const float *bias, int64_t bias_stride, bool *bias_done);
 void gemm_tc_set_operand_cache(bool on);
+void gemm_tc_set_schedule(int max_splits, int panel);
 void gemm_tc_split_stats(uint64_t *launches, uint64_t *hits);
 static std::atomic<int> g_natural_planes{1};
 
@@ -312,6 +313,13 @@ int nt_set_matmul_mode(int mode) {
   NT_API_END
 }
 int nt_get_matmul_mode(void) { return g_matmul_mode.load(); }
+int nt_set_matmul_schedule(int max_splits, int panel) {
+  NT_API_BEGIN
+  if (max_splits < 1 || max_splits > 8) fail_invalid("nt_set_matmul_schedule: max_splits must be 1..8.");
+  if (panel < 0) fail_invalid("nt_set_matmul_schedule: negative panel width.");
+  gemm_tc_set_schedule(max_splits, panel);
+  NT_API_END
+}
 int nt_set_matmul_tc_min_macs(int64_t macs) {
   NT_API_BEGIN
   if (macs < 0) fail_invalid("nt_set_matmul_tc_min_macs: negative.");

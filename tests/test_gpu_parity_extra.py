@@ -479,3 +479,38 @@ def test_transposed_operands_through_the_tile_pipeline(nt, shape):
     assert_bit_exact(on["relu(c.T)"], np.maximum(c_ref, 0), "relu(c.T)")
     for k in on:
         assert_bit_exact(on[k], off[k], k + ": pipeline against the register-staged kernel")
+
+
+@pytest.mark.parametrize("shape", [(512, 4096, 1024), (128, 16384, 256), (1000, 3000, 1100), (256, 8192, 512)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_split_k_products(nt, shape):
+    """Products with so few output tiles that most SMs would idle are cut along k (up to 8 parts per tile,
+    summed in part order by whichever CTA finishes last).  Against fp64 with the norm-wise bound of the
+    unsplit kernel; the same bits on every run; bias in the epilogue equal to the composed form; and close
+    to the unsplit result (the partial sums are rounded once more)."""
+    _C = nt._C
+    M, K, N = shape
+    rng = np.random.default_rng(M + N)
+    a_np = rng.standard_normal((M, K)).astype(np.float32)
+    b_np = rng.standard_normal((K, N)).astype(np.float32)
+    bias_np = rng.standard_normal((N,)).astype(np.float32)
+    a, b, bias = dev(nt, a_np), dev(nt, b_np), dev(nt, bias_np)
+    ref = a_np.astype(np.float64) @ b_np.astype(np.float64)
+    bound = np.abs(a_np).astype(np.float64) @ np.abs(b_np).astype(np.float64)
+    with nt.no_grad():
+        first = (a @ b).numpy()
+        again = (a @ b).numpy()
+        assert_scaled(first, ref, bound, 2e-6, "split-K product")
+        assert_bit_exact(first, again, "two runs of the same split-K product")
+        # a.T stored: the MN-major operand paths through the same schedule
+        at = dev(nt, np.ascontiguousarray(a_np.T))
+        assert_bit_exact((at.T @ b).numpy(), first, "A read MN-major")
+        fused = nt.Tensor._new_view(_C.linear(a._C_view, b._C_view, bias._C_view), (M, N), None, None).numpy()
+        assert_bit_exact(fused, first + bias_np, "bias in the epilogue of a split product")
+        _C.set_matmul_schedule(1, 8)
+        try:
+            unsplit = (a @ b).numpy()
+        finally:
+            _C.set_matmul_schedule(8, 8)
+    assert_scaled(unsplit, ref, bound, 2e-6, "unsplit product")
+    assert np.max(np.abs(first - unsplit) / bound) < 1e-6
