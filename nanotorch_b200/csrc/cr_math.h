@@ -1,4 +1,4 @@
-// fp32 tanh and sigmoid evaluated in double precision and rounded once.
+// fp32 tanh evaluated in double precision and rounded once.
 //
 // tanh: float(tanh(double(x))) for every float argument -- checked exhaustively on the host by
 // tests/test_tanh_restatement.py (NT_EXHAUSTIVE=1), which also finds the host libm's tanhf (what the
@@ -6,10 +6,7 @@
 // evaluation path for every finite argument:
 //     E - 1 = exp(-2|x|) - 1 from a 64-entry table of 2^(j/64) and a degree-6 polynomial, formed without
 //     cancellation near 0;  tanh|x| = -(E - 1) / (2 + (E - 1)).
-// sigmoid: 1 / (1 + exp(-x)) in double, rounded once: the reference computes the same expression in three
-// rounded fp32 steps on top of libm's expf (src/cpp/ops/unary_ops.cu:107; total error <= 1.5 ulp), so the
-// correctly rounded value is within 2 ulp of it; where expf(-x) overflows (x <= -88.7228394) the reference returns
-// 1/inf = 0 and so does this.
+// (The sigmoid lives in sigmoid_f32.h: fp32 arithmetic, the reference's three rounded steps.)
 // Only IEEE double +, *, fma, a correctly rounded fp32 reciprocal, a table look-up and integer adds on the
 // exponent field are used, so host and device return the same bits.  About 45 instructions per element
 // (the degree-13 polynomial this replaces took 99; the bit-exact restatement in tanh_exact.h takes 130).
@@ -159,7 +156,9 @@ NT_TF_HD double nt_tf_div(double num, double den) {
   return q;
 }
 
-NT_TF_HD float nt_sigmoid_f32(float xf) {
+// 1 / (1 + exp(-x)) evaluated in double and rounded once (sigmoid_f32.h uses it for the one window of
+// arguments where the reference's three fp32 steps amplify a one-ulp difference of the exponential).
+NT_TF_HD float nt_sigmoid_cr_f32(float xf) {
   if (!(xf == xf)) return xf + xf;                   // NaN
   if (xf <= -88.72283935546875f) return 0.0f;        // expf(-x) = inf in the reference from this float on: 1 / inf
   if (xf > 40.0f) return 1.0f;                       // 1 + exp(-x) rounds to 1 long before

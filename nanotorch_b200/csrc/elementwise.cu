@@ -4,6 +4,7 @@
 #include "elementwise.cuh"
 #include "tanh_exact.h"
 #include "cr_math.h"
+#include "sigmoid_f32.h"
 
 namespace ntb {
 
@@ -81,7 +82,7 @@ template <class T> struct SigmoidF {
   using in_t = T;
   using out_t = T;
   __device__ __forceinline__ T operator()(T a) const {
-    if constexpr (std::is_same_v<T, float>) return nt_sigmoid_f32(a); // correctly rounded, see cr_math.h
+    if constexpr (std::is_same_v<T, float>) return nt_sigmoid_f32(a); // the same three steps in fp32, see sigmoid_f32.h
     else return 1.0 / (1.0 + exp(-a));
   }
 };

@@ -251,7 +251,7 @@ def test_fused_backward_full_size(nt, port, big, name):
 def test_default_tanh_and_sigmoid_equal_their_host_evaluation(nt, tmp_path):
     """The default tanh and the sigmoid are proven on the HOST (tests/test_tanh_restatement.py: every
     float argument within 2 ulp of the libm-based reference).  That proof carries over to the GPU only if
-    the device evaluates the same header to the same bits: compile nanotorch_b200/csrc/cr_math.h with gcc
+    the device evaluates the same headers to the same bits: compile nanotorch_b200/csrc/cr_math.h and sigmoid_f32.h with gcc
     and compare with the kernels' output bit for bit on 2^24 N(0,1) values, a sweep of U(-100, 100), the
     small-argument region and the special values."""
     import ctypes
@@ -260,7 +260,7 @@ def test_default_tanh_and_sigmoid_equal_their_host_evaluation(nt, tmp_path):
 
     csrc = Path(nt.__file__).resolve().parent / "csrc"
     src = tmp_path / "cr_host.c"
-    src.write_text('#include "cr_math.h"\n'
+    src.write_text('#include "cr_math.h"\n#include "sigmoid_f32.h"\n'
                    "void eval(const float *x, float *t, float *s, long n) {\n"
                    "  for (long i = 0; i < n; ++i) { t[i] = nt_tanh_fast_f32(x[i]); s[i] = nt_sigmoid_f32(x[i]); }\n}\n")
     lib_path = tmp_path / "libcr_host.so"
@@ -281,4 +281,4 @@ def test_default_tanh_and_sigmoid_equal_their_host_evaluation(nt, tmp_path):
     d = dev(nt, x)
     assert nt._C.get_tanh_mode() == nt._C.TANH_CORRECTLY_ROUNDED
     assert_bit_exact(nt.tanh(d).numpy(), t, "tanh, device vs host evaluation of cr_math.h")
-    assert_bit_exact(nt.sigmoid(d).numpy(), s, "sigmoid, device vs host evaluation of cr_math.h")
+    assert_bit_exact(nt.sigmoid(d).numpy(), s, "sigmoid, device vs host evaluation of sigmoid_f32.h")

@@ -108,7 +108,7 @@ SIGMOID_SRC = r"""
 #include <math.h>
 #include <stdio.h>
 #include <stdlib.h>
-#include "cr_math.h"
+#include "sigmoid_f32.h"
 static float u2f(uint32_t u) { float f; memcpy(&f, &u, 4); return f; }
 static long key(float f) { int32_t i; memcpy(&i, &f, 4); return i < 0 ? -(long)(i & 0x7fffffff) : i; }
 int main(void) {
