@@ -265,6 +265,16 @@ int nt_matmul_split_stats(uint64_t *split_launches, uint64_t *cache_hits);
  * by the CTA that finishes last, so the result does not depend on timing.  1 = never.  panel (default 8;
  * NT_GEMM_PANEL): width in n-tiles of the panels the CTAs walk the output in, 0 = row by row. */
 int nt_set_matmul_schedule(int max_splits, int panel);
+/* Two independent products in one call, *out1 = a1 @ b1 and *out2 = a2 @ b2 -- what MatmulOp.backward computes
+ * (autograd/ops_binary.py:253-267: g @ x2^T and x1^T @ g).  Same bits as two nt_matmul calls.  In mode 1, when the
+ * second product's operand planes are already cached, its kernel can be launched as the programmatic dependent of
+ * the first: its CTAs start on the SMs that the first product's last, partly filled wave leaves idle (256 tiles on
+ * 148 SMs at a 2048-row batch) and wait for the first grid before they exit, so later work in the stream
+ * still sees both complete.  The overlap is off by default (measured gain on the training step: 0.3-0.6 % at
+ * 2048-4096 rows per GPU, none at 16384); nt_set_matmul_pair_overlap(1) or NT_GEMM_PAIR_OVERLAP=1 switches it on. */
+int nt_matmul_pair(const nt_view *a1, const nt_view *b1, const nt_view *a2, const nt_view *b2, nt_storage **out1,
+                   nt_storage **out2);
+int nt_set_matmul_pair_overlap(int on);
 int nt_set_matmul_tc_min_macs(int64_t macs);
 int64_t nt_get_matmul_tc_min_macs(void);
 

@@ -393,6 +393,19 @@ min = _reduction("min")  # noqa: A001
 argmax = _reduction("argmax")
 argmin = _reduction("argmin")
 
+def matmul_pair(a1: TensorView, b1: TensorView, a2: TensorView, b2: TensorView) -> tuple[Storage, Storage]:
+    """(a1 @ b1, a2 @ b2): two independent products, the second overlapping the first's last wave of tiles
+    (addition to the reference's surface; the bits of two `matmul` calls)."""
+    o1, o2 = C.c_void_p(), C.c_void_p()
+    _check(_lib.nt_matmul_pair(_vref(a1), _vref(b1), _vref(a2), _vref(b2), C.byref(o1), C.byref(o2)))
+    return Storage._wrap(o1.value), Storage._wrap(o2.value)
+
+
+def set_matmul_pair_overlap(on: bool = True) -> None:
+    """Launch the second product of `matmul_pair` as the programmatic dependent of the first (off by default)."""
+    _check(_lib.nt_set_matmul_pair_overlap(int(bool(on))))
+
+
 def linear(x: TensorView, w: TensorView, bias: TensorView) -> Storage:
     """x @ w + bias with the bias add fused into the GEMM epilogue (addition to the reference's surface)."""
     return _ret_storage(_lib.nt_linear, _vref(x), _vref(w), _vref(bias))

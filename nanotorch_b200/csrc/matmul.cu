@@ -29,6 +29,8 @@ bool gemm_3xtf32_natural(nt_storage *sa, int64_t a_off, nt_storage *sb, int64_t 
                          int64_t b_sn, const float *bias, int64_t bias_stride, bool *bias_done);
 void gemm_tc_set_operand_cache(bool on);
 void gemm_tc_set_schedule(int max_splits, int panel);
+void gemm_tc_pair_role(int role);
+void gemm_tc_set_pair_overlap(bool on);
 void gemm_tc_split_stats(uint64_t *launches, uint64_t *hits);
 static std::atomic<int> g_natural_planes{1};
 
@@ -459,6 +461,37 @@ static nt_storage *matmul_impl(const nt_view *x1, const nt_view *x2, const nt_vi
 int nt_matmul(const nt_view *x1, const nt_view *x2, nt_storage **out) {
   NT_API_BEGIN
   *out = matmul_impl(x1, x2, nullptr);
+  NT_API_END
+}
+
+// Two independent products in one call (the two gradients of a product: g @ b^T and a^T @ g).  In mode 1 the second
+// tensor-core launch is made the programmatic dependent of the first when nothing had to be launched in between,
+// so its first CTAs run on the SMs that the first product's last wave leaves idle.  Results are those of two
+// nt_matmul calls, bit for bit.
+int nt_matmul_pair(const nt_view *a1, const nt_view *b1, const nt_view *a2, const nt_view *b2, nt_storage **out1,
+                   nt_storage **out2) {
+  NT_API_BEGIN
+  *out1 = *out2 = nullptr;
+  struct Leave {
+    ~Leave() { gemm_tc_pair_role(0); }
+  } leave;
+  gemm_tc_pair_role(1);
+  nt_storage *first = matmul_impl(a1, b1, nullptr);
+  gemm_tc_pair_role(2);
+  nt_storage *second = nullptr;
+  try {
+    second = matmul_impl(a2, b2, nullptr);
+  } catch (...) {
+    storage_release(first);
+    throw;
+  }
+  *out1 = first;
+  *out2 = second;
+  NT_API_END
+}
+int nt_set_matmul_pair_overlap(int on) {
+  NT_API_BEGIN
+  gemm_tc_set_pair_overlap(on != 0);
   NT_API_END
 }
 

@@ -113,6 +113,8 @@ struct StreamRedirect {
 void count_launch(uint64_t n = 1);
 // matmul kernels call these around their launches (no-ops unless profiling is enabled)
 void matmul_profile_begin();
+bool matmul_profile_active();
+void matmul_profile_extend(); // the launch just made belongs to the interval opened last
 void matmul_profile_end();
 bool cuda_ok();              // a device is present and usable
 int gemm_tc_take_error();    // device-side error flag of the tensor-core GEMM (0 = none); call after a sync
@@ -120,6 +122,7 @@ void check_device_errors();  // after a stream synchronisation: raises if a boun
 long long wait_limit_clocks(); // limit of every bounded spin in device code, in SM clocks
 bool is_capturing();         // a CUDA-graph capture is in progress on the compute stream
 int capture_id();            // id of the graph being captured, 0 when none
+uint64_t launches_so_far();  // kernels counted by check_launch since load
 // Persistent device state that kernels expect to find zeroed (ticket counters of the reductions, the
 // error flag of the tensor-core GEMM) and one-off function attributes: created eagerly, never inside
 // a stream capture, where the zeroing would be recorded instead of executed.

@@ -30,6 +30,7 @@ struct Runtime {
   cudaEvent_t copy_gate = nullptr, copy_done = nullptr;
   bool mm_profile = false;
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> mm_events;
+  std::vector<int> mm_counts; // launches between each pair of events (2 for an overlapped pair of products)
   std::vector<cudaEvent_t> event_pool;
   std::map<size_t, std::vector<void *>> dev_cache;
   std::map<size_t, std::vector<void *>> pin_cache;
@@ -142,6 +143,7 @@ cudaStream_t update_stream() {
   ensure_streams_locked(r);
   return r.update;
 }
+uint64_t launches_so_far() { return rt().launches.load(); }
 int capture_id() {
   Runtime &r = rt();
   std::lock_guard<std::mutex> lk(r.mu);
@@ -212,6 +214,14 @@ void matmul_profile_begin() {
   cudaEvent_t a = pooled_event(r), b = pooled_event(r);
   NT_CUDA_CHECK(cudaEventRecord(a, r.compute));
   r.mm_events.emplace_back(a, b);
+  r.mm_counts.push_back(1);
+}
+bool matmul_profile_active() { return rt().mm_profile; }
+// One more launch belongs to the interval that was opened last (the second product of an overlapped pair).
+void matmul_profile_extend() {
+  Runtime &r = rt();
+  if (!r.mm_profile || r.mm_counts.empty()) return;
+  r.mm_counts.back() += 1;
 }
 void matmul_profile_end() {
   Runtime &r = rt();
@@ -702,11 +712,12 @@ int nt_matmul_profile_read(double *total_ms, int64_t *launches) {
     NT_CUDA_CHECK(cudaEventSynchronize(pr.second));
     NT_CUDA_CHECK(cudaEventElapsedTime(&ms, pr.first, pr.second));
     total += ms;
-    ++n;
     r.event_pool.push_back(pr.first);
     r.event_pool.push_back(pr.second);
   }
+  for (int c : r.mm_counts) n += c;
   r.mm_events.clear();
+  r.mm_counts.clear();
   *total_ms = total;
   *launches = n;
   NT_API_END

@@ -293,3 +293,47 @@ def test_fused_linear_is_the_composed_form_bit_for_bit(nt, mode):
             nt._C.linear(x._C_view, W._C_view, wide._C_view)
     finally:
         nt._C.set_matmul_mode(1)
+
+
+@pytest.mark.parametrize("graph_mode", [False, True])
+def test_overlapped_gradient_products_leave_the_step_unchanged(nt, graph_mode):
+    """Linear.backward launches its two products as an overlapping pair: six training steps, eagerly and as a
+    replayed graph, give the bits of the same steps with the overlap switched off."""
+    import nanotorch_b200.nn as nn
+
+    X = nt.Tensor.from_numpy(np.random.default_rng(1).standard_normal((2048, 1024)).astype(np.float32), "cuda")
+    Y = nt.Tensor.from_numpy(np.random.default_rng(2).standard_normal((2048, 256)).astype(np.float32), "cuda")
+
+    def run(overlap: bool):
+        nt._C.set_matmul_pair_overlap(overlap)
+        try:
+            model = build(nt, [1024, 1536, 1536, 256], nn.Tanh)
+            opt = nn.GradientDescent(model.parameters(), lr=1e-2)
+
+            def step():
+                loss = nt.mean((model(X) - Y) ** 2)
+                opt.zero_grad()
+                loss.backward()
+                opt.step()
+                return loss
+
+            losses = [float(step().numpy()) for _ in range(2)]
+            if graph_mode:
+                g = nt._C.Graph()
+                with g.capture():
+                    loss = step()
+                for _ in range(4):
+                    g.replay()
+                    losses.append(float(loss.numpy()))
+                g.close()
+            else:
+                losses += [float(step().numpy()) for _ in range(4)]
+            return np.array(losses), [p.numpy() for p in model.parameters()]
+        finally:
+            nt._C.set_matmul_pair_overlap(False)
+
+    plain_losses, plain_params = run(False)
+    pair_losses, pair_params = run(True)
+    assert np.array_equal(plain_losses, pair_losses), (plain_losses, pair_losses)
+    for a, b in zip(plain_params, pair_params):
+        assert_bit_exact(a, b, "parameters after six steps")

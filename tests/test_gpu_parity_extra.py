@@ -514,3 +514,32 @@ def test_split_k_products(nt, shape):
             _C.set_matmul_schedule(8, 8)
     assert_scaled(unsplit, ref, bound, 2e-6, "unsplit product")
     assert np.max(np.abs(first - unsplit) / bound) < 1e-6
+
+
+@pytest.mark.parametrize("mode", [1, 0])
+@pytest.mark.parametrize("shape", [(2048, 1024, 1536), (300, 200, 260), (4096, 512, 4096)], ids=lambda s: "x".join(map(str, s)))
+def test_matmul_pair_is_two_products(nt, shape, mode):
+    """Both gradients of a product in one call (the second tensor-core launch overlapping the first one's last
+    wave as its programmatic dependent): the bits of two separate products, also with the overlap switched off,
+    and a kernel queued behind the pair sees both results complete."""
+    _C = nt._C
+    M, K, N = shape
+    rng = np.random.default_rng(M + K)
+    g, x, w = (dev(nt, rng.standard_normal(s).astype(np.float32)) for s in ((M, N), (M, K), (K, N)))
+    _C.set_matmul_mode(mode)
+    try:
+        with nt.no_grad():
+            gx_ref = (g @ w.T).numpy()
+            gw_ref = (x.T @ g).numpy()
+            for overlap in (True, False, True):
+                _C.set_matmul_pair_overlap(overlap)
+                sx, sw = _C.matmul_pair(g._C_view, w.T._C_view, x.T._C_view, g._C_view)
+                gx, gw = nt.Tensor._new_contiguous(sx, (M, K)), nt.Tensor._new_contiguous(sw, (K, N))
+                total = (gx.sum() + gw.sum()).numpy()       # queued right behind the pair
+                assert_bit_exact(gx.numpy(), gx_ref, f"g @ w.T from the pair (overlap {overlap})")
+                assert_bit_exact(gw.numpy(), gw_ref, f"x.T @ g from the pair (overlap {overlap})")
+                assert_bit_exact(total, (nt.Tensor.from_numpy(gx_ref, "cuda").sum() + nt.Tensor.from_numpy(gw_ref, "cuda").sum()).numpy(),
+                                 "a reduction queued behind the pair")
+    finally:
+        _C.set_matmul_pair_overlap(False)
+        _C.set_matmul_mode(1)
