@@ -1027,6 +1027,31 @@ void gemm_tc_refresh(nt_storage *s) {
   }
 }
 
+// For a writer that rewrites a whole dense [R][C] fp32 storage and can write the TF32 planes in the same pass
+// (the SGD update): the plane buffer to write, if the storage has exactly one cached view and that view is the
+// whole storage with unpadded rows; the caller then calls gemm_tc_mark_refreshed instead of gemm_tc_refresh.
+float *gemm_tc_refresh_target(nt_storage *s, int64_t R, int64_t C) {
+  if (!g_operand_cache.load() || C % 32 != 0) return nullptr;
+  std::lock_guard<std::mutex> lk(g_plane_mu);
+  auto it = g_plane_cache.find(s);
+  if (it == g_plane_cache.end() || it->second.size() != 1) return nullptr;
+  const PlaneEntry &e = it->second.front();
+  if (e.offset != 0 || e.batch != 1 || e.R != R || e.C != C || e.s_r != C || e.Cp != C) return nullptr;
+  return e.planes;
+}
+void gemm_tc_mark_refreshed(nt_storage *s) {
+  std::lock_guard<std::mutex> lk(g_plane_mu);
+  auto it = g_plane_cache.find(s);
+  if (it == g_plane_cache.end()) return;
+  const int cid = capture_id();
+  for (PlaneEntry &e : it->second) {
+    e.mutation = s->mutation;
+    e.epoch = g_plane_epoch;
+    e.capture = cid;
+    e.maintained = true;
+  }
+}
+
 void gemm_tc_new_epoch() {
   std::lock_guard<std::mutex> lk(g_plane_mu);
   g_plane_epoch += 1;

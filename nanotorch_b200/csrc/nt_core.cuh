@@ -166,6 +166,8 @@ void gemm_tc_forget(nt_storage *s);
 // Re-split, on the current stream(), every cached plane set of `s` (called right after a parameter
 // update, so that the next forward pass finds its operand ready).
 void gemm_tc_refresh(nt_storage *s);
+float *gemm_tc_refresh_target(nt_storage *s, int64_t R, int64_t C); // see gemm_tc.cu
+void gemm_tc_mark_refreshed(nt_storage *s);
 // Cached planes written by work that was only captured, or overwritten by a graph replay behind the
 // host's back, must not be trusted by later eager calls: a new epoch invalidates all of them.
 void gemm_tc_new_epoch();

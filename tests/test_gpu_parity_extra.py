@@ -356,7 +356,7 @@ def test_operand_plane_cache_follows_every_write(nt):
 def test_a_training_step_splits_each_tensor_once(nt):
     """Linear -> Tanh -> Linear -> Tanh -> Linear with 3xTF32 products: 8 products per step (3 forward, 3 weight
     gradients, 2 input gradients) over 3 inputs, 3 weights and 3 output gradients: with natural-layout cached
-    planes that is 9 operand splits per step instead of 16, and the SGD update re-splits the weights itself."""
+    planes that is 5 operand splits per step instead of 16, and the SGD update writes the weights' planes itself."""
     import nanotorch_b200.nn as nn
 
     _C = nt._C
@@ -377,9 +377,9 @@ def test_a_training_step_splits_each_tensor_once(nt):
     s0, h0 = _C.matmul_split_stats()
     step()
     s1, h1 = _C.matmul_split_stats()
-    # X is unchanged (hit), the 2 hidden activations and 3 gradients are new (5 splits), the weights were
-    # re-split by the previous update (hits) and are re-split by this one (3 splits)
-    assert s1 - s0 == 8, s1 - s0
+    # X is unchanged (hit), the 2 hidden activations and 3 gradients are new (5 splits), the weights' planes were
+    # written by the previous update (hits) and are written again by this one, inside the update kernel (no split)
+    assert s1 - s0 == 5, s1 - s0
     assert h1 - h0 == 16 - 5, h1 - h0
 
 
