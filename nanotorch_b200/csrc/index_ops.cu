@@ -16,8 +16,9 @@
 //     reference), at the price of one synchronisation -- callers that validated on the host skip it;
 //   - scatter with colliding destinations must end with the value the reference's sequential loop
 //     writes last.  Unless the caller vouches for unique destinations, a first pass records per
-//     destination the highest source position (atomicMax) and the copy pass lets only that
-//     position write: deterministic and identical to the sequential order.
+//     destination index tuple the highest source position over the index-array dims (atomicMax) and
+//     the copy pass lets only that position write: deterministic and identical to the sequential
+//     order.  The table has one entry per destination index tuple -- per row for a row scatter.
 #include "elementwise.cuh"
 
 namespace ntb {
@@ -36,6 +37,13 @@ struct IndexParams {
   const int64_t *ind[NT_MAX_DIMS];            // index arrays, advanced by their offsets
   int64_t ind_extent[NT_MAX_DIMS];            // extent of the indexed dim (wrap + range check)
   int64_t ix_fancy_stride[NT_MAX_DIMS];       // stride of the indexed operand along that dim
+  // Ordered scatter.  Two source items can only land on the same destination element when they agree on every
+  // basic dim, and then their order in the sequential loop is the order of their coordinates on the index-array
+  // dims alone.  So the owner table has one entry per destination index tuple (key = sum of index value x
+  // key_stride), and the value compared is the item's row-major rank over the index-array dims only
+  // (rank_stride is 0 on basic dims): a row scatter keeps one entry per destination row, not per element.
+  int64_t rank_stride[NT_MAX_DIMS];
+  int64_t key_stride[NT_MAX_DIMS];
 };
 
 // First out-of-range index seen by a validation pass.
@@ -46,11 +54,12 @@ struct IndexError {
 };
 
 // NF > 0: the number of index arrays is known at compile time (their offsets stay in registers).
-template <class IDX, int NF>
+template <class IDX, int NF, bool WANT_RANK>
 __device__ __forceinline__ void ix_offsets(const IndexParams &p, IDX lin, int64_t &lin_off, int64_t &ix_off,
-                                           int64_t (&ind_off)[NF > 0 ? NF : NT_MAX_DIMS]) {
+                                           int64_t (&ind_off)[NF > 0 ? NF : NT_MAX_DIMS], int64_t &rank) {
   lin_off = 0;
   ix_off = 0;
+  rank = 0;
   const int nf = NF > 0 ? NF : p.n_fancy;
 #pragma unroll
   for (int q = 0; q < nf; ++q) ind_off[q] = 0;
@@ -65,13 +74,14 @@ __device__ __forceinline__ void ix_offsets(const IndexParams &p, IDX lin, int64_
     lin = quo;
     lin_off += r * p.lin_stride[d];
     ix_off += r * p.ix_stride[d];
+    if constexpr (WANT_RANK) rank += r * p.rank_stride[d];
 #pragma unroll
     for (int q = 0; q < nf; ++q) ind_off[q] += r * p.ind_stride[q][d];
   }
 }
 
 // MODE 0: gather  (to[lin] = from[ix]);  1: scatter (to[ix] = from[lin]);
-// MODE 2: scatter ordering pass (owner[ix] = max(owner[ix], item + 1));
+// MODE 2: scatter ordering pass (owner[key] = max(owner[key], rank + 1));
 // MODE 3: scatter copy pass that only lets the recorded owner write.
 template <class V, class IDX, int MODE, int NF>
 __global__ void __launch_bounds__(256) index_copy(IndexParams p, const V *from, V *to, unsigned long long *owner) {
@@ -79,15 +89,17 @@ __global__ void __launch_bounds__(256) index_copy(IndexParams p, const V *from, 
   using OW = std::conditional_t<sizeof(IDX) == 4, unsigned int, unsigned long long>;
   const int nf = NF > 0 ? NF : p.n_fancy;
   const int64_t base = (int64_t(blockIdx.x) * IX_UNROLL) * blockDim.x + threadIdx.x;
-  int64_t lin_off[IX_UNROLL], ix_off[IX_UNROLL];
+  constexpr bool ORDERED = MODE == 2 || MODE == 3;
+  int64_t lin_off[IX_UNROLL], ix_off[IX_UNROLL], rank[IX_UNROLL], key[IX_UNROLL];
   bool live[IX_UNROLL];
 #pragma unroll
   for (int u = 0; u < IX_UNROLL; ++u) {
     const int64_t item = base + int64_t(u) * blockDim.x;
     live[u] = item < p.items;
+    key[u] = 0;
     if (live[u]) {
       int64_t ind_off[NF > 0 ? NF : NT_MAX_DIMS];
-      ix_offsets<IDX, NF>(p, IDX(item), lin_off[u], ix_off[u], ind_off);
+      ix_offsets<IDX, NF, ORDERED>(p, IDX(item), lin_off[u], ix_off[u], ind_off, rank[u]);
 #pragma unroll
       for (int q = 0; q < nf; ++q) {
         long long c = __ldg(p.ind[q] + ind_off[q]);
@@ -95,20 +107,21 @@ __global__ void __launch_bounds__(256) index_copy(IndexParams p, const V *from, 
         if (c < 0) c += ext;
         if (c < 0 || c >= ext) live[u] = false; // reported by the validation pass; never dereferenced
         ix_off[u] += c * p.ix_fancy_stride[q];
+        if constexpr (ORDERED) key[u] += c * p.key_stride[q];
       }
     }
   }
   if constexpr (MODE == 2) {
 #pragma unroll
     for (int u = 0; u < IX_UNROLL; ++u)
-      if (live[u]) atomicMax(reinterpret_cast<OW *>(owner) + ix_off[u], OW(base + int64_t(u) * blockDim.x) + OW(1));
+      if (live[u]) atomicMax(reinterpret_cast<OW *>(owner) + key[u], OW(rank[u]) + OW(1));
     return;
   }
   V val[IX_UNROLL];
 #pragma unroll
   for (int u = 0; u < IX_UNROLL; ++u) {
     if constexpr (MODE == 3) {
-      if (live[u]) live[u] = reinterpret_cast<const OW *>(owner)[ix_off[u]] == OW(base + int64_t(u) * blockDim.x) + OW(1);
+      if (live[u]) live[u] = reinterpret_cast<const OW *>(owner)[key[u]] == OW(rank[u]) + OW(1);
     }
     if (live[u]) val[u] = (MODE == 0) ? from[ix_off[u]] : from[lin_off[u]];
   }
@@ -156,7 +169,7 @@ struct Plan {
   int vec = 1;      // elements per work item
   const char *lin_base = nullptr; // byte pointers, already advanced by the view offsets
   const char *ix_base = nullptr;
-  int64_t ix_storage_elems = 0;   // elements of the indexed operand's storage (scatter ordering scratch)
+  int64_t key_count = 1;          // destination index tuples: entries of the ordered scatter's owner table
 };
 
 [[noreturn]] void fail_index(const std::string &m) { throw Error(NT_ERR_INDEX, m); }
@@ -215,7 +228,19 @@ Plan make_plan(const char *fname, const int64_t *it_shape, int it_ndim, const in
   pl.itemsize = int(dtype_itemsize(ix->storage->dtype));
   pl.lin_base = static_cast<const char *>(lin_storage->data) + lin_offset * pl.itemsize;
   pl.ix_base = static_cast<const char *>(ix->storage->data) + ix->offset * pl.itemsize;
-  pl.ix_storage_elems = ix->storage->n;
+  {
+    int64_t acc = 1;
+    for (int d = it_ndim - 1; d >= 0; --d) {
+      p.rank_stride[d] = axis_is_fancy[d] ? acc : 0;
+      if (axis_is_fancy[d]) acc *= it_shape[d];
+    }
+    acc = 1;
+    for (int q = n_fancy - 1; q >= 0; --q) {
+      p.key_stride[q] = acc;
+      acc *= p.ind_extent[q];
+    }
+    pl.key_count = acc;
+  }
 
   // 16-byte work items when the innermost iteration dim is a basic unit-stride run on both sides
   const int vec = 16 / pl.itemsize;
@@ -354,20 +379,18 @@ int nt_scatter_to_axes(const nt_view *src, const nt_view *out, const int64_t *fa
     if (flags & NT_INDEX_UNIQUE) {
       launch_width<1>(pl, pl.lin_base, to, nullptr);
     } else {
-      // owner[] is addressed like the indexed operand (relative to its view offset, in work items);
-      // negative strides can reach below the offset, so the scratch spans the whole storage twice over
-      // and the pointer handed to the kernel sits at its middle
-      const int64_t span = (pl.ix_storage_elems / pl.vec + 2) & ~int64_t(1); // even: the middle stays 8-byte aligned
-      const size_t width = (pl.p.items < (int64_t(1) << 31)) ? 4 : 8;          // as index_copy's IDX (launch_mode)
+      // one owner entry per destination index tuple (see IndexParams), as wide as the work-item index
+      const size_t width = (pl.p.items < (int64_t(1) << 31)) ? 4 : 8; // as index_copy's IDX (launch_mode)
+      const size_t bytes = size_t(pl.key_count > 0 ? pl.key_count : 1) * width;
       size_t rounded = 0;
-      auto *scratch = static_cast<char *>(device_alloc(size_t(2 * span) * width, &rounded));
+      auto *scratch = static_cast<char *>(device_alloc(bytes, &rounded));
       struct Guard {
         void *p;
         size_t r;
         ~Guard() { device_free(p, r); }
       } guard{scratch, rounded};
-      NT_CUDA_CHECK(cudaMemsetAsync(scratch, 0, size_t(2 * span) * width, stream()));
-      auto *middle = reinterpret_cast<unsigned long long *>(scratch + size_t(span) * width);
+      NT_CUDA_CHECK(cudaMemsetAsync(scratch, 0, bytes, stream()));
+      auto *middle = reinterpret_cast<unsigned long long *>(scratch);
       launch_width<2>(pl, pl.lin_base, to, middle);
       launch_width<3>(pl, pl.lin_base, to, middle);
     }

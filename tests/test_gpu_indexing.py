@@ -101,6 +101,41 @@ def test_device_index_tensors(nt, port):
         dev(nt, np.zeros((5, 2), np.float32))[[7]]
 
 
+def test_colliding_scatter_through_views_and_broadcast_indices(nt):
+    """The ordering pass keys its owner table by the destination index tuple and compares source positions over
+    the index-array dims only: colliding rows into a reversed, strided destination view; index arrays that
+    broadcast against each other with a basic dim in between; a large colliding row scatter on the 16-byte path.
+    numpy assigns duplicates in source order, as the reference's sequential loop does."""
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((64, 48)).astype(np.float32)
+    dup = rng.integers(-10, 10, 300).astype(np.int64)
+    v = rng.standard_normal((300, 24)).astype(np.float32)
+    t = dev(nt, x)
+    t[::-1, ::2][dup.tolist()] = dev(nt, v)
+    want = x.copy()
+    want[::-1, ::2][dup] = v
+    assert_bit_exact(t.numpy(), want, "colliding rows into a reversed, strided view")
+
+    y = rng.standard_normal((12, 7, 10)).astype(np.float32)
+    i0 = rng.integers(0, 3, (40, 1)).astype(np.int64)       # many collisions
+    i2 = rng.integers(0, 2, (1, 30)).astype(np.int64)
+    v = rng.standard_normal((40, 30, 7)).astype(np.float32)
+    t = dev(nt, y)
+    t[dev(nt, i0), :, dev(nt, i2)] = dev(nt, v)
+    want = y.copy()
+    want[i0, :, i2] = v
+    assert_bit_exact(t.numpy(), want, "two broadcasting index arrays around a basic dim")
+
+    big = rng.standard_normal((2048, 1024)).astype(np.float32)
+    idx = rng.integers(0, 64, 4096).astype(np.int64)
+    v = rng.standard_normal((4096, 1024)).astype(np.float32)
+    t = dev(nt, big)
+    t[dev(nt, idx)] = dev(nt, v)
+    want = big.copy()
+    want[idx] = v
+    assert_bit_exact(t.numpy(), want, "4096 rows into 64 destinations")
+
+
 def test_raw_entry_points_check_their_plan(nt):
     _C = nt._C
     x = dev(nt, np.zeros((4, 6), np.float32))
