@@ -134,6 +134,39 @@ __global__ void __launch_bounds__(256) ew_contig_planes(F f, float *out, const f
   }
 }
 
+// [R, C] op [C]: one operand is a single row broadcast over the rows of the other (a bias, a per-column scale).
+// The contiguous kernel with the row operand indexed modulo the row length -- it stays in the L1 -- instead of the
+// general strided kernel's per-dim index arithmetic.  C % 4 == 0, fewer than 2^31 vectors.  ROW_FIRST: the row is
+// the first argument of f.
+template <class F, bool ROW_FIRST>
+__global__ void __launch_bounds__(256) ew_contig_rowbcast(F f, float *out, const float *a, const float *row, int64_t nvec,
+                                                          uint32_t cvec, uint32_t div_mul, uint32_t div_shift) {
+  constexpr int UNROLL = 4;
+  const int64_t base = (int64_t(blockIdx.x) * UNROLL) * blockDim.x + threadIdx.x;
+  float4 va[UNROLL], vr[UNROLL];
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    const int64_t i = base + int64_t(u) * blockDim.x;
+    if (i < nvec) {
+      va[u] = ld_stream(reinterpret_cast<const float4 *>(a) + i);
+      const uint32_t lin = uint32_t(i);
+      const uint32_t quo = div_mul ? (__umulhi(lin, div_mul) >> div_shift) : lin;
+      vr[u] = __ldg(reinterpret_cast<const float4 *>(row) + (lin - quo * cvec));
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    const int64_t i = base + int64_t(u) * blockDim.x;
+    if (i < nvec) {
+      const float4 x = va[u], r = vr[u];
+      float4 y;
+      if constexpr (ROW_FIRST) y = make_float4(f(r.x, x.x), f(r.y, x.y), f(r.z, x.z), f(r.w, x.w));
+      else y = make_float4(f(x.x, r.x), f(x.y, r.y), f(x.z, r.z), f(x.w, r.w));
+      st_stream(reinterpret_cast<float4 *>(out) + i, y);
+    }
+  }
+}
+
 // Two results from three contiguous fp32 inputs in one pass (the two gradients of a binary op: g, x1, x2
 // -> dx1, dx2; 20 bytes per element instead of the 24 of two launches).  f(g, x1, x2, &r1, &r2).
 template <class F>
@@ -531,6 +564,29 @@ template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NI
       ew_contig<F, NIN><<<unsigned(blocks), 256, 0, st>>>(f, out, in[0], in[1], in[2], it.numel);
       check_launch("ew_contig");
       return;
+    }
+  }
+
+  // (1b) a dense [R, C] operand against one broadcast row
+  if constexpr (NIN == 2 && std::is_same<TI, float>::value && std::is_same<TO, float>::value) {
+    if (it.ndim == 2 && (it.shape[1] & 3) == 0 && (it.numel >> 2) < (int64_t(1) << 31) && it.strides[0][0] == it.shape[1] &&
+        it.strides[0][1] == 1 && aligned16(out) && aligned16(in[0]) && aligned16(in[1])) {
+      const int64_t C = it.shape[1];
+      auto dense = [&](int o) { return it.strides[o][0] == C && it.strides[o][1] == 1; };
+      auto row = [&](int o) { return it.strides[o][0] == 0 && it.strides[o][1] == 1; };
+      const int which = (row(1) && dense(2)) ? 1 : (dense(1) && row(2)) ? 2 : 0;
+      if (which) {
+        uint32_t mul, shift;
+        ew_fast_divisor(C >> 2, &mul, &shift);
+        const int64_t nvec = it.numel >> 2;
+        const unsigned blocks = unsigned(ceil_div(nvec, 256 * 4));
+        if (which == 1)
+          ew_contig_rowbcast<F, true><<<blocks, 256, 0, st>>>(f, out, in[1], in[0], nvec, uint32_t(C >> 2), mul, shift);
+        else
+          ew_contig_rowbcast<F, false><<<blocks, 256, 0, st>>>(f, out, in[0], in[1], nvec, uint32_t(C >> 2), mul, shift);
+        check_launch("ew_contig_rowbcast");
+        return;
+      }
     }
   }
 

@@ -44,6 +44,7 @@ struct IndexParams {
   // (rank_stride is 0 on basic dims): a row scatter keeps one entry per destination row, not per element.
   int64_t rank_stride[NT_MAX_DIMS];
   int64_t key_stride[NT_MAX_DIMS];
+  int owner64; // owner entries are 64-bit (2^31 or more positions on the index-array dims)
 };
 
 // First out-of-range index seen by a validation pass.
@@ -85,8 +86,6 @@ __device__ __forceinline__ void ix_offsets(const IndexParams &p, IDX lin, int64_
 // MODE 3: scatter copy pass that only lets the recorded owner write.
 template <class V, class IDX, int MODE, int NF>
 __global__ void __launch_bounds__(256) index_copy(IndexParams p, const V *from, V *to, unsigned long long *owner) {
-  // owner entries are as wide as the work-item index: 32 bits whenever the launch has fewer than 2^31 items
-  using OW = std::conditional_t<sizeof(IDX) == 4, unsigned int, unsigned long long>;
   const int nf = NF > 0 ? NF : p.n_fancy;
   const int64_t base = (int64_t(blockIdx.x) * IX_UNROLL) * blockDim.x + threadIdx.x;
   constexpr bool ORDERED = MODE == 2 || MODE == 3;
@@ -114,14 +113,19 @@ __global__ void __launch_bounds__(256) index_copy(IndexParams p, const V *from, 
   if constexpr (MODE == 2) {
 #pragma unroll
     for (int u = 0; u < IX_UNROLL; ++u)
-      if (live[u]) atomicMax(reinterpret_cast<OW *>(owner) + key[u], OW(rank[u]) + OW(1));
+      if (live[u]) {
+        if (p.owner64) atomicMax(owner + key[u], static_cast<unsigned long long>(rank[u]) + 1ull);
+        else atomicMax(reinterpret_cast<unsigned int *>(owner) + key[u], static_cast<unsigned int>(rank[u]) + 1u);
+      }
     return;
   }
   V val[IX_UNROLL];
 #pragma unroll
   for (int u = 0; u < IX_UNROLL; ++u) {
     if constexpr (MODE == 3) {
-      if (live[u]) live[u] = reinterpret_cast<const OW *>(owner)[key[u]] == OW(rank[u]) + OW(1);
+      if (live[u])
+        live[u] = p.owner64 ? owner[key[u]] == static_cast<unsigned long long>(rank[u]) + 1ull
+                            : reinterpret_cast<const unsigned int *>(owner)[key[u]] == static_cast<unsigned int>(rank[u]) + 1u;
     }
     if (live[u]) val[u] = (MODE == 0) ? from[ix_off[u]] : from[lin_off[u]];
   }
@@ -240,6 +244,12 @@ Plan make_plan(const char *fname, const int64_t *it_shape, int it_ndim, const in
       acc *= p.ind_extent[q];
     }
     pl.key_count = acc;
+  }
+  {
+    int64_t positions = 1;
+    for (int d = 0; d < it_ndim; ++d)
+      if (axis_is_fancy[d]) positions *= it_shape[d];
+    p.owner64 = positions >= (int64_t(1) << 31) ? 1 : 0;
   }
 
   // 16-byte work items when the innermost iteration dim is a basic unit-stride run on both sides
@@ -379,8 +389,8 @@ int nt_scatter_to_axes(const nt_view *src, const nt_view *out, const int64_t *fa
     if (flags & NT_INDEX_UNIQUE) {
       launch_width<1>(pl, pl.lin_base, to, nullptr);
     } else {
-      // one owner entry per destination index tuple (see IndexParams), as wide as the work-item index
-      const size_t width = (pl.p.items < (int64_t(1) << 31)) ? 4 : 8; // as index_copy's IDX (launch_mode)
+      // one owner entry per destination index tuple (see IndexParams)
+      const size_t width = pl.p.owner64 ? 8 : 4;
       const size_t bytes = size_t(pl.key_count > 0 ? pl.key_count : 1) * width;
       size_t rounded = 0;
       auto *scratch = static_cast<char *>(device_alloc(bytes, &rounded));
@@ -391,7 +401,16 @@ int nt_scatter_to_axes(const nt_view *src, const nt_view *out, const int64_t *fa
       } guard{scratch, rounded};
       NT_CUDA_CHECK(cudaMemsetAsync(scratch, 0, bytes, stream()));
       auto *middle = reinterpret_cast<unsigned long long *>(scratch);
-      launch_width<2>(pl, pl.lin_base, to, middle);
+      // The ordering pass only needs one item per position on the index-array dims: the same plan with every
+      // basic dim shrunk to extent 1 (all items of a row would otherwise hammer one counter).
+      Plan order = pl;
+      order.p.items = 1;
+      for (int d = 0; d < order.p.ndim; ++d) {
+        if (order.p.rank_stride[d] == 0) order.p.shape[d] = 1; // a basic dim
+        order.p.items *= order.p.shape[d];
+        ew_fast_divisor(order.p.shape[d], &order.p.div_mul[d], &order.p.div_shift[d]);
+      }
+      launch_width<2>(order, pl.lin_base, to, middle);
       launch_width<3>(pl, pl.lin_base, to, middle);
     }
   }

@@ -543,3 +543,31 @@ def test_matmul_pair_is_two_products(nt, shape, mode):
     finally:
         _C.set_matmul_pair_overlap(False)
         _C.set_matmul_mode(1)
+
+
+@pytest.mark.parametrize("shape", [(1000, 1028), (5, 200, 64), (4096, 4096), (7, 4)], ids=lambda s: "x".join(map(str, s)))
+def test_row_broadcast_kernel(nt, shape):
+    """A dense operand against one broadcast row (the dedicated contiguous kernel): both argument orders of the
+    non-commutative ops, leading dims that collapse into the rows, the in-place forms -- bit-equal to numpy."""
+    rng = np.random.default_rng(sum(shape))
+    a_np = rng.uniform(0.5, 2.0, shape).astype(np.float32)
+    r_np = rng.uniform(0.5, 2.0, shape[-1:]).astype(np.float32)
+    a, r = dev(nt, a_np), dev(nt, r_np)
+    assert_bit_exact((a + r).numpy(), a_np + r_np, "a + row")
+    assert_bit_exact((r - a).numpy(), r_np - a_np, "row - a")
+    assert_bit_exact((a - r).numpy(), a_np - r_np, "a - row")
+    assert_bit_exact((a * r).numpy(), a_np * r_np, "a * row")
+    assert_bit_exact((r / a).numpy(), r_np / a_np, "row / a")
+    assert_bit_exact((a / r).numpy(), a_np / r_np, "a / row")
+    with nt.no_grad():
+        b = dev(nt, a_np.copy())
+        b -= r
+        assert_bit_exact(b.numpy(), a_np - r_np, "a -= row")
+        b = dev(nt, a_np.copy())
+        b /= r
+        assert_bit_exact(b.numpy(), a_np / r_np, "a /= row")
+    # a sliced row (offset by 4 elements: still 16-byte aligned) and one that is not aligned (falls back)
+    wide = dev(nt, np.concatenate([np.zeros(4, np.float32), r_np, np.zeros(3, np.float32)]))
+    assert_bit_exact((a + wide[4:4 + shape[-1]]).numpy(), a_np + r_np, "a + aligned slice of a longer row")
+    wide1 = dev(nt, np.concatenate([np.zeros(1, np.float32), r_np]))
+    assert_bit_exact((a + wide1[1:]).numpy(), a_np + r_np, "a + misaligned row")
