@@ -241,7 +241,8 @@ int nt_get_matmul_mode(void);
  * activation is split once for the forward product and the weight-gradient product, a gradient once for
  * its two products; nt_sgd_update / nt_comm_sgd_update write the new planes of a weight that has been an operand
  * in the same pass (a dense 2-D parameter with whole 128-byte rows) or re-split it right behind the update.
- * Inside a graph capture cached planes are trusted only when they were split inside that capture or belong to a parameter that the update keeps re-splitting; everything else
+ * Inside a graph capture cached planes are trusted only when they were split inside that capture or belong
+ * to a parameter whose update keeps them current; everything else
  * (an input batch that an eager warm-up step had split) is split again inside the graph, so a replay reads
  * what the input buffers hold at that moment.  Do not write to a parameter from outside the graph between
  * replays other than through nt_sgd_update.  Each storage keeps at most 32 cached views.  Writes through
