@@ -394,7 +394,7 @@ def time_ops(nt, peaks: dict) -> dict:
         record("mul.transposed.backward", stream_time(
             [lambda i=i: (_C.multiply(bt[i], gv[i]), _C.multiply(av[i], gv[i])) for i in range(k)]), 5 * numel * 4)
         # row-broadcast operand [N] against [N,N]: dx1 = v*g, dv = column sums of x1*g (the unbroadcast):
-        # g, x1 -> dx1, tmp -> dv.  5 N + (N + C) floats as the survey accounts them
+        # g, x1 -> dx1, tmp -> dv.  5 N + (N + C) floats by the per-op byte accounting of the reference (mem_bytes)
         vrow = v_.expand(N, N)._C_view
 
         def mul_bcast_backward(i):
