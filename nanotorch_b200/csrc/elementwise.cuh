@@ -167,6 +167,24 @@ __global__ void __launch_bounds__(256) ew_contig_rowbcast(F f, float *out, const
   }
 }
 
+// A unary op on one broadcast row: out[r][c] = f(row[c]) for every r (write-only apart from the row).
+template <class F>
+__global__ void __launch_bounds__(256) ew_contig_rowbcast1(F f, float *out, const float *row, int64_t nvec, uint32_t cvec,
+                                                           uint32_t div_mul, uint32_t div_shift) {
+  constexpr int UNROLL = 4;
+  const int64_t base = (int64_t(blockIdx.x) * UNROLL) * blockDim.x + threadIdx.x;
+#pragma unroll
+  for (int u = 0; u < UNROLL; ++u) {
+    const int64_t i = base + int64_t(u) * blockDim.x;
+    if (i < nvec) {
+      const uint32_t lin = uint32_t(i);
+      const uint32_t quo = div_mul ? (__umulhi(lin, div_mul) >> div_shift) : lin;
+      const float4 r = __ldg(reinterpret_cast<const float4 *>(row) + (lin - quo * cvec));
+      st_stream(reinterpret_cast<float4 *>(out) + i, make_float4(f(r.x), f(r.y), f(r.z), f(r.w)));
+    }
+  }
+}
+
 // Two results from three contiguous fp32 inputs in one pass (the two gradients of a binary op: g, x1, x2
 // -> dx1, dx2; 20 bytes per element instead of the 24 of two launches).  f(g, x1, x2, &r1, &r2).
 template <class F>
@@ -587,6 +605,18 @@ template <class F, int NIN> void ew_launch(F f, const nt_view *const (&views)[NI
         check_launch("ew_contig_rowbcast");
         return;
       }
+    }
+  }
+
+  if constexpr (NIN == 1 && std::is_same<TI, float>::value && std::is_same<TO, float>::value) {
+    if (it.ndim == 2 && (it.shape[1] & 3) == 0 && (it.numel >> 2) < (int64_t(1) << 31) && it.strides[0][0] == it.shape[1] &&
+        it.strides[0][1] == 1 && it.strides[1][0] == 0 && it.strides[1][1] == 1 && aligned16(out) && aligned16(in[0])) {
+      uint32_t mul, shift;
+      ew_fast_divisor(it.shape[1] >> 2, &mul, &shift);
+      const int64_t nvec = it.numel >> 2;
+      ew_contig_rowbcast1<F><<<unsigned(ceil_div(nvec, 256 * 4)), 256, 0, st>>>(f, out, in[0], nvec, uint32_t(it.shape[1] >> 2), mul, shift);
+      check_launch("ew_contig_rowbcast1");
+      return;
     }
   }
 

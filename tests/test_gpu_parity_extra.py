@@ -566,6 +566,10 @@ def test_row_broadcast_kernel(nt, shape):
         b = dev(nt, a_np.copy())
         b /= r
         assert_bit_exact(b.numpy(), a_np / r_np, "a /= row")
+    # a unary op on the expanded row itself
+    rows = int(np.prod(shape[:-1]))
+    assert_bit_exact((r.expand(rows, shape[-1]) ** 2).numpy(), np.broadcast_to(r_np * r_np, (rows, shape[-1])), "row**2 expanded")
+    assert_bit_exact(nt.relu(-r.expand(rows, shape[-1])).numpy(), np.broadcast_to(np.maximum(-r_np, 0), (rows, shape[-1])), "relu(-row) expanded")
     # a sliced row (offset by 4 elements: still 16-byte aligned) and one that is not aligned (falls back)
     wide = dev(nt, np.concatenate([np.zeros(4, np.float32), r_np, np.zeros(3, np.float32)]))
     assert_bit_exact((a + wide[4:4 + shape[-1]]).numpy(), a_np + r_np, "a + aligned slice of a longer row")
