@@ -556,7 +556,10 @@ template <class Op> static bool try_fast_f32(const nt_view *x, const Plan &pl, f
     for (int d = 0; d < outer.ndim; ++d) vec = vec && (outer.strides[d] % 4 == 0);
     if (vec && C >= 1024 && aligned16(out)) {
       const int64_t tiles = ceil_div(C, 1024);
-      int64_t S = ceil_div(int64_t(sms) * 4, tiles * Z);
+      // row splits: 4 CTAs per SM for large inputs; for inputs of up to 128 MB the finish -- one CTA per tile
+      // reading S partial rows -- weighs as much as the main pass, so half as many, longer splits
+      const int64_t per_sm = (R * C * Z * 4 <= (int64_t(128) << 20)) ? 2 : 4;
+      int64_t S = ceil_div(int64_t(sms) * per_sm, tiles * Z);
       int64_t max_s = ceil_div(R, 32);
       if (S > max_s) S = max_s;
       if (S > 65535) S = 65535;
