@@ -859,7 +859,7 @@ void gemm_tc_wait_probe() {
 // it, inside the graph too.  Anything else (an input batch split by an eager warm-up step) is split again
 // inside the capture, so that a replay sees whatever the buffer holds by then.
 // A storage keeps at most PLANE_ENTRIES_PER_STORAGE entries (views at different offsets of one big tensor
-// would otherwise pile up); the oldest entry that no capture has used makes room.
+// would otherwise pile up); the least recently used entry that no capture relies on makes room.
 struct NatSplitArgs {
   const float *src;
   float *hi, *lo;
@@ -911,7 +911,9 @@ struct PlaneEntry {
   uint64_t mutation, epoch;
   int capture = 0;         // id of the capture that last split it, 0 = split eagerly
   bool maintained = false; // last written by gemm_tc_refresh
+  uint64_t last_use = 0;   // g_plane_tick of the last look-up that returned it
 };
+static uint64_t g_plane_tick = 0; // one per look-up; the two operands of a product are consecutive look-ups
 constexpr size_t PLANE_ENTRIES_PER_STORAGE = 32;
 static std::mutex g_plane_mu;
 static std::unordered_map<nt_storage *, std::vector<PlaneEntry>> g_plane_cache;
@@ -953,10 +955,12 @@ static float *natural_planes(nt_storage *s, int64_t offset, int64_t batch, int64
   }
   const int cid = capture_id();
   std::lock_guard<std::mutex> lk(g_plane_mu);
+  const uint64_t tick = ++g_plane_tick;
   auto &list = g_plane_cache[s];
   for (PlaneEntry &e : list) {
     if (e.offset == offset && e.batch == batch && e.s_b == s_b && e.R == R && e.C == C && e.s_r == s_r) {
       const bool current = e.mutation == s->mutation && e.epoch == g_plane_epoch;
+      e.last_use = tick;
       if (current && (cid == 0 || e.capture == cid || e.maintained)) {
         g_split_hits.fetch_add(1, std::memory_order_relaxed);
         return e.planes;
@@ -970,15 +974,20 @@ static float *natural_planes(nt_storage *s, int64_t offset, int64_t batch, int64
     }
   }
   if (list.size() >= PLANE_ENTRIES_PER_STORAGE) {
+    // least recently used among the entries no capture relies on -- but never the one the previous look-up
+    // returned: it may be the other operand of the product being set up, not yet launched
+    size_t victim = list.size();
     for (size_t i = 0; i < list.size(); ++i) {
-      if (list[i].capture == 0 && !list[i].maintained) {
-        device_free(list[i].planes, list[i].rounded); // stream-ordered: earlier readers are already queued
-        list.erase(list.begin() + i);
-        break;
-      }
+      const PlaneEntry &c = list[i];
+      if (c.capture != 0 || c.maintained || c.last_use + 1 >= tick) continue;
+      if (victim == list.size() || c.last_use < list[victim].last_use) victim = i;
+    }
+    if (victim != list.size()) {
+      device_free(list[victim].planes, list[victim].rounded); // stream-ordered: earlier readers are already queued
+      list.erase(list.begin() + victim);
     }
   }
-  PlaneEntry e{offset, batch, s_b, R, C, s_r, Cp, nullptr, 0, s->mutation, g_plane_epoch, cid, false};
+  PlaneEntry e{offset, batch, s_b, R, C, s_r, Cp, nullptr, 0, s->mutation, g_plane_epoch, cid, false, tick};
   e.planes = static_cast<float *>(device_alloc(bytes, &e.rounded));
   run_split(s, e);
   list.push_back(e);
