@@ -1,13 +1,15 @@
 // Elementwise kernels over the last two collapsed dims when an operand is stored column-major there (a
 // transposed view), for large fp32 operands: a persistent, warp-specialised pipeline fed by the copy engine.
 //
-//   grid      one CTA per SM; a CTA walks 64 x 64 tiles of the output, 4 x 4 tiles (256 x 256 elements) at a
-//             time so that every operand, whichever of the two dims it is contiguous along, is read in runs
-//             of 1 KB per tile row group.
+//   grid      one CTA per SM; CTA b takes tiles b, b + grid, ... of a list that walks the 64 x 64 output tiles
+//             in groups of 4 x 4 (256 x 256 elements).  The order itself was measured to make no difference
+//             (row by row, 2 x 2 ... 16 x 16 groups); the grouping serves the L2 prefetch below, whose boxes
+//             cover four tiles side by side along an operand's contiguous dim.
 //   warp 16   lane 0 issues the tile loads: per operand two boxes of 64 rows x 32 values (128 bytes, the
 //             128-byte swizzle span), into a ring of 8 stages (one operand) or 5 (two); a column-major
 //             operand is loaded through a map whose inner dim is I, so its tile lands as [j][i].  It also
-//             leaves the tile's coordinates beside the stage, and an end marker after the last tile.
+//             leaves the tile's coordinates beside the stage, and an end marker after the last tile; with two
+//             operands it prefetches into the L2, two rounds ahead, boxes of 64 rows x 1 KB (prefetch_for).
 //   warps 0-15 run independently of one another: each waits for a stage, reads its 8 x 32 share of both
 //             layouts from shared memory (the swizzle makes the [i][j] accesses conflict free and the
 //             [j][i] ones 2-way), releases the stage, applies the functor, writes the results into its own
