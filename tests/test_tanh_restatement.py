@@ -133,3 +133,22 @@ int main(void) {
 def test_sigmoid_within_2ulp_of_the_reference_expression_on_host_libm(tmp_path):
     out = _build_and_run(tmp_path, "sigmoid_check", SIGMOID_SRC, 53)
     assert out.returncode == 0, out.stdout
+
+
+def test_sigmoid_table_is_what_its_generator_prints():
+    """The 64 {hi, lo} pairs of 2^(j/64) in sigmoid_f32.h are the output of gen_exp2f_table.py, and hi + lo
+    reproduces 2^(j/64) to better than 2^-45."""
+    import re
+    from fractions import Fraction
+
+    csrc = REPO / "nanotorch_b200" / "csrc"
+    printed = subprocess.run([sys.executable, str(csrc / "gen_exp2f_table.py")], capture_output=True, text=True, check=True).stdout
+    rows = [l.strip() for l in printed.splitlines() if l.strip().startswith("{")]
+    assert len(rows) == 64
+    header = (csrc / "sigmoid_f32.h").read_text()
+    for row in rows:
+        assert row in header, row
+    for j, row in enumerate(rows):
+        hi, lo = (float.fromhex(t.rstrip("f")) for t in re.findall(r"-?0x[0-9a-f.]+p[+-]\d+f", row))
+        exact = 2.0 ** (j / 64.0)                       # a double: 2^-53 relative
+        assert abs((Fraction(hi) + Fraction(lo)) - Fraction(exact)) < Fraction(2) ** -44
